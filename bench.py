@@ -1,0 +1,433 @@
+#!/usr/bin/env python
+"""Decode-step benchmark of the KV-cache hot path (paged-attention decode + KV
+append + block allocation) on synthetic inputs shaped like the named model.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One "step" = one decode step of the whole batch: allocate blocks for the grown
+sequences, then for each of the L layers append one token per sequence
+(store_kvcache) and run decode attention (paged_attention).  Lengths advance by
+one per step.  Prints ONE JSON line (rank 0).
+
+  value   decode tokens/s, all ranks, inputs resident in HBM, CUDA-event timed
+  e2e     the same through the public Python API with HOST inputs: per step the
+          q/k/v of every layer are copied from pinned memory and the attention
+          output is copied back, inside the timed region
+  roofline  KV GB/s of the attention kernel vs the measured HBM copy peak
+  cpu_baseline  the reference's PyTorch paged-attention loop on the host cores
+
+With N > 1 (torchrun) every rank owns its own pool, block table and batch
+(sequence sharding, no collective on the data path); the step is bracketed by
+barriers and the slowest rank's device time is used.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # BASELINE configs[2]: the configuration the tokens/s-at-1/2/4/8 metric is quoted on
+    "llama3-8b-gqa-decode": dict(cfg=3, B=256, Hq=32, Hkv=8, L=32, max_len=1536, free_frac=0.10),
+    # BASELINE configs[1]
+    "llama2-7b-mha-decode": dict(cfg=2, B=64, Hq=32, Hkv=32, L=32, max_len=768, free_frac=0.30),
+    # BASELINE configs[4], sequence-sharded form
+    "codellama-34b-gqa-decode": dict(cfg=5, B=512, Hq=64, Hkv=8, L=48, max_len=1536, free_frac=0.05),
+    # small case for profiler captures and CPU-side dry runs (pool ~1.3 GB: larger than L2)
+    "small-gqa-decode": dict(cfg=9, B=64, Hq=32, Hkv=8, L=4, max_len=1536, free_frac=0.10),
+}
+D, BS = 128, 16
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+# ----------------------------------------------------------------------------
+# synthetic workload
+# ----------------------------------------------------------------------------
+def draw_lengths_and_tables(w, rank, growth_tokens):
+    """Seeded lengths and a block table built from a shuffled free list."""
+    g = torch.Generator().manual_seed(1000 * w["cfg"] + rank)
+    lens = torch.randint(1, w["max_len"] + 1, (w["B"],), generator=g, dtype=torch.int64)
+    need = (lens + BS - 1) // BS
+    live = int(need.sum())
+    growth = w["B"] * ((growth_tokens + BS - 1) // BS + 1)
+    nb = int(np.ceil(live / (1.0 - w["free_frac"]))) + growth
+    perm = torch.randperm(nb, generator=g)
+    mbps = (w["max_len"] + growth_tokens + BS - 1) // BS + 1
+    return lens, need, nb, perm, mbps, g
+
+
+class DecodeJob:
+    """Pool, block manager and per-step inputs of one rank, on the GPU."""
+
+    def __init__(self, w, rank, growth_tokens, device):
+        import morphserve_b200 as mk
+        from types import SimpleNamespace
+        self.mk = mk
+        self.w = w
+        self.dev = device
+        lens, need, nb, perm, mbps, g = draw_lengths_and_tables(w, rank, growth_tokens)
+        B, L, Hq, Hkv = w["B"], w["L"], w["Hq"], w["Hkv"]
+        self.model_config = SimpleNamespace(num_layers=L, num_q_heads=Hq, num_kv_heads=Hkv, head_dim=D)
+        self.engine_config = SimpleNamespace(block_size=BS, max_blocks_per_seq=mbps)
+        self.bm = mk.BlockManager("GPU", nb, B, mbps, BS)
+        table = torch.full((B, mbps), -1, dtype=torch.int32)
+        used = perm[: int(need.sum())]
+        pos = 0
+        for b in range(B):
+            n = int(need[b])
+            table[b, :n] = used[pos:pos + n].to(torch.int32)
+            pos += n
+        self.bm.block_table.copy_(table)
+        self.bm.num_seq_allocated_blocks.copy_(need.to(torch.int32))
+        free = torch.ones(nb, dtype=torch.bool)
+        free[used] = False
+        self.bm.is_block_free.copy_(free)
+        self.bm.num_free_blocks = type(self.bm.num_free_blocks)(nb - len(used))
+        self.lens_host = lens.numpy().astype(np.int64).copy()
+        self.seq_ids = torch.arange(B, dtype=torch.int32, device=device)
+        self.seq_ids_list = list(range(B))
+        self.lens_dev = lens.to(torch.int32).to(device)
+        dg = torch.Generator(device=device).manual_seed(1000 * w["cfg"] + rank + 7)
+        shape = (nb, L, Hkv, BS, D)
+        self.k_cache = torch.empty(shape, dtype=torch.float16, device=device)
+        self.v_cache = torch.empty(shape, dtype=torch.float16, device=device)
+        for t in (self.k_cache, self.v_cache):       # N(0,1), filled piecewise to bound temporaries
+            flat = t.view(-1)
+            step = 1 << 28
+            for i in range(0, flat.numel(), step):
+                flat[i:i + step].normal_(generator=dg)
+        self.q = torch.randn((L, B, Hq, D), generator=dg, dtype=torch.float16, device=device)
+        self.kn = torch.randn((L, B, Hkv, D), generator=dg, dtype=torch.float16, device=device)
+        self.vn = torch.randn((L, B, Hkv, D), generator=dg, dtype=torch.float16, device=device)
+        self.o = torch.zeros((L, B, Hq * D), dtype=torch.float16, device=device)
+        self.nb = nb
+        self._z = torch.zeros(0, dtype=torch.int32, device=device)
+
+    def infer_state(self, seq_ids, lens_dev):
+        B, Hkv = self.w["B"], self.w["Hkv"]
+        max_len = int(self.lens_host.max())
+        sbs, nsb = self.mk.infer_state.seq_block_size_heuristic(Hkv, self.lens_host.tolist())
+        return self.mk.LlamaInferState(
+            batch_size=B, num_tokens=B, seq_ids=seq_ids, softmax_scale=D ** -0.5, num_prefill_seqs=0,
+            num_prefill_tokens=0, prefill_seq_start_locs=self._z, prefill_seq_start_locs_with_end=self._z,
+            prefill_seq_lens=self._z, max_prefill_len=0, num_decoding_seqs=B, decoding_seq_lens=lens_dev,
+            max_decoding_len=max_len, seq_block_size=sbs, num_seq_blocks=nsb, num_blocks_org=self.nb,
+            kv_cache_new_block_size=0, org_layer_param_size=0, position_cos=self._z, position_sin=self._z,
+            ignore_kvcache=False)
+
+    def layers(self, st, q, kn, vn, o):
+        mk, mc, ec, bt = self.mk, self.model_config, self.engine_config, self.bm.block_table
+        for layer in range(self.w["L"]):
+            mk.store_kvcache(kn[layer], vn[layer], self.k_cache, self.v_cache, [], [], bt, mc, ec, st, layer)
+            mk.paged_attention(q[layer], self.k_cache, self.v_cache, [], [], bt, mc, ec, st, layer, o[layer])
+
+    def step_resident(self):
+        """One decode step with every input already in HBM."""
+        self.lens_host += 1
+        self.lens_dev += 1
+        self.bm.allocate_blocks_for_seqs(self.seq_ids, self.lens_dev)
+        st = self.infer_state(self.seq_ids, self.lens_dev)
+        self.layers(st, self.q, self.kn, self.vn, self.o)
+
+    def make_host_buffers(self):
+        self.hq = self.q.cpu().pin_memory()
+        self.hk = self.kn.cpu().pin_memory()
+        self.hv = self.vn.cpu().pin_memory()
+        self.ho = torch.empty(self.o.shape, dtype=torch.float16).pin_memory()
+        self.dq, self.dk, self.dv = torch.empty_like(self.q), torch.empty_like(self.kn), torch.empty_like(self.vn)
+        return self.hq.nbytes + self.hk.nbytes + self.hv.nbytes + 8 * self.w["B"], self.ho.nbytes
+
+    def step_host(self):
+        """The same step as a caller with host data makes it: metadata from Python
+        lists (as the reference's LlamaModel.forward builds it), q/k/v from pinned
+        memory, the attention output read back."""
+        self.lens_host += 1
+        seq_ids = torch.tensor(self.seq_ids_list, dtype=torch.int32, device=self.dev)
+        lens = torch.tensor(self.lens_host.tolist(), dtype=torch.int32, device=self.dev)
+        self.lens_dev = lens
+        self.dq.copy_(self.hq, non_blocking=True)
+        self.dk.copy_(self.hk, non_blocking=True)
+        self.dv.copy_(self.hv, non_blocking=True)
+        self.bm.allocate_blocks_for_seqs(seq_ids, lens)
+        st = self.infer_state(seq_ids, lens)
+        self.layers(st, self.dq, self.dk, self.dv, self.o)
+        self.ho.copy_(self.o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def kv_bytes_per_layer(self):
+        return 2 * 2 * self.w["Hkv"] * D * int(self.lens_host.sum())
+
+
+# ----------------------------------------------------------------------------
+# clocks
+# ----------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons of the GPUs in use while the timed
+    region runs (read-only NVML queries)."""
+
+    def __init__(self, indices):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml as N
+            N.nvmlInit()
+            self.N = N
+            self.handles = [N.nvmlDeviceGetHandleByIndex(i) for i in indices]
+            self.max_mhz = max(N.nvmlDeviceGetMaxClockInfo(h, N.NVML_CLOCK_SM) for h in self.handles)
+        except Exception:
+            self.N = None
+
+    def _run(self):
+        N = self.N
+        names = {}
+        for nm in ("HwSlowdown", "HwThermalSlowdown", "SwThermalSlowdown", "SwPowerCap", "HwPowerBrakeSlowdown"):
+            v = getattr(N, "nvmlClocksThrottleReason" + nm, None)
+            if v is not None:
+                names[v] = {"HwSlowdown": "hw_slowdown", "HwThermalSlowdown": "hw_thermal_slowdown",
+                            "SwThermalSlowdown": "sw_thermal_slowdown", "SwPowerCap": "sw_power_cap",
+                            "HwPowerBrakeSlowdown": "hw_power_brake_slowdown"}[nm]
+        while not self._stop.is_set():
+            for h in self.handles:
+                try:
+                    self.samples.append(N.nvmlDeviceGetClockInfo(h, N.NVML_CLOCK_SM))
+                    r = N.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                    for bit, nm in names.items():
+                        if r & bit:
+                            self.reasons.add(nm)
+                except Exception:
+                    pass
+            self._stop.wait(0.02)
+
+    def __enter__(self):
+        if self.N is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable"]}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ----------------------------------------------------------------------------
+# CPU arm: the reference's PyTorch paged-attention path on the host cores
+# ----------------------------------------------------------------------------
+def cpu_reference_sample(w, steps, warmup, layers_sampled=2, seqs_sampled=None):
+    """Times the live restatement of the reference's PyTorch loop (plus the
+    indexed-assignment append) on a bounded sample: `seqs_sampled` sequences of
+    the workload's length distribution x `layers_sampled` layers per step, and
+    scales to the full step (B sequences x L layers).  Returns tokens/s."""
+    from oracle import kv_oracle as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    B = seqs_sampled or min(w["B"], 64)
+    Ls = min(layers_sampled, w["L"])
+    g = torch.Generator().manual_seed(1000 * w["cfg"])
+    lens = torch.randint(1, w["max_len"] + 1, (w["B"],), generator=g)[:B]
+    need = (lens + BS - 1) // BS
+    nb = int(need.sum()) + B
+    perm = torch.randperm(nb, generator=g)
+    mbps = int(need.max()) + 2
+    table = torch.full((B, mbps), -1, dtype=torch.int32)
+    pos = 0
+    for b in range(B):
+        table[b, :int(need[b])] = perm[pos:pos + int(need[b])].to(torch.int32)
+        pos += int(need[b])
+    k_pool = torch.randn((nb, Ls, w["Hkv"], BS, D), generator=g).to(torch.float16)
+    v_pool = torch.randn((nb, Ls, w["Hkv"], BS, D), generator=g).to(torch.float16)
+    q = torch.randn((Ls, B, w["Hq"], D), generator=g).to(torch.float16)
+    kn = torch.randn((Ls, B, w["Hkv"], D), generator=g).to(torch.float16)
+    vn = torch.randn((Ls, B, w["Hkv"], D), generator=g).to(torch.float16)
+    o = torch.empty((B, w["Hq"] * D), dtype=torch.float16)
+    seq_ids = list(range(B))
+    lens_l = [int(x) for x in lens]
+    kp, vp = [k_pool.numpy()], [v_pool.numpy()]
+
+    def one_step():
+        for layer in range(Ls):
+            O.store_kvcache_decode(kn[layer].numpy(), vn[layer].numpy(), kp, vp, table.numpy(), seq_ids, lens_l,
+                                   layer, nb, 1)
+            O.paged_attention_torch_loop(q[layer], [k_pool], [v_pool], table, seq_ids, lens_l, layer, D ** -0.5,
+                                         nb, 1, o=o)
+
+    for _ in range(warmup):
+        one_step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one_step()
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    full_step = dt * (w["B"] / B) * (w["L"] / Ls)
+    return w["B"] / full_step, dict(
+        cores=os.cpu_count() or 1, kind="port",
+        sample=f"{B} of {w['B']} sequences x {Ls} of {w['L']} layers per step, {steps} steps, scaled to the full step")
+
+
+# ----------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="llama3-8b-gqa-decode", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    K, W = args.steps, max(args.warmup, 0)
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    config = {"workload": args.workload, "baseline_config": w["cfg"], "batch_per_gpu": w["B"],
+              "num_q_heads": w["Hq"], "num_kv_heads": w["Hkv"], "head_dim": D, "block_size": BS,
+              "num_layers": w["L"], "context_len": f"uniform[1,{w['max_len']}] + 1 per step",
+              "sharding": f"sequence x{world}", "l2": "inputs_exceed_l2"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        val, info = cpu_reference_sample(w, steps=K, warmup=min(W, 2))
+        line = {"impl": "reference", "metric": "decode_tokens_per_s", "value": val, "unit": "tokens/s",
+                "n_gpus": args.gpus, "steps": K, "warmup": W, "ms_per_step": 1e3 * w["B"] / val,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+                "data": "synthetic", "config": config,
+                "cpu_baseline": dict(value=val, unit="tokens/s", **info),
+                "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    from morphserve_b200 import _lib
+    job = DecodeJob(w, rank, growth_tokens=2 * (K + W) + 16, device=device)
+
+    # ---- leg 1: inputs resident in HBM ----------------------------------------
+    for _ in range(max(W, 3)):
+        job.step_resident()
+    barrier()
+    calls0 = dict(_lib.CALLS)
+    kv_bytes = 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(list(range(world)) if rank == 0 else []) as clocks:
+        e0.record()
+        for _ in range(K):
+            job.step_resident()
+            kv_bytes += job.kv_bytes_per_layer() * w["L"]
+        e1.record()
+        barrier()
+    ms = e0.elapsed_time(e1)
+    launches = sum(v - calls0.get(k, 0) for k, v in _lib.CALLS.items())
+    t = torch.tensor([ms], dtype=torch.float64, device=device)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    value = world * w["B"] * K / (ms_max * 1e-3)
+
+    # ---- per-kernel timing for the roofline (attention only, append only) -----
+    st = job.infer_state(job.seq_ids, job.lens_dev)
+    mk, mc, ec, bt = job.mk, job.model_config, job.engine_config, job.bm.block_table
+    reps = max(3, min(10, K))
+    for layer in range(w["L"]):
+        mk.paged_attention(job.q[layer], job.k_cache, job.v_cache, [], [], bt, mc, ec, st, layer, job.o[layer])
+    torch.cuda.synchronize()
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a0.record()
+    for _ in range(reps):
+        for layer in range(w["L"]):
+            mk.paged_attention(job.q[layer], job.k_cache, job.v_cache, [], [], bt, mc, ec, st, layer, job.o[layer])
+    a1.record()
+    torch.cuda.synchronize()
+    attn_ms = a0.elapsed_time(a1) / (reps * w["L"])
+    a0.record()
+    for _ in range(reps):
+        for layer in range(w["L"]):
+            mk.store_kvcache(job.kn[layer], job.vn[layer], job.k_cache, job.v_cache, [], [], bt, mc, ec, st, layer)
+    a1.record()
+    torch.cuda.synchronize()
+    append_ms = a0.elapsed_time(a1) / (reps * w["L"])
+    peak, peak_kind = measured_peak()
+    attn_bytes = job.kv_bytes_per_layer()
+    achieved = attn_bytes / (attn_ms * 1e-3) / 1e9
+
+    # ---- leg 2: host buffers through the public API ---------------------------
+    e2e = None
+    if not args.no_e2e:
+        h2d, d2h = job.make_host_buffers()
+        for _ in range(3):
+            job.step_host()
+        barrier()
+        Ke = max(3, min(K, 20))
+        e0.record()
+        for _ in range(Ke):
+            job.step_host()
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e = {"value": world * w["B"] * Ke / (float(t.item()) * 1e-3), "unit": "tokens/s",
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": Ke}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        v, info = cpu_reference_sample(w, steps=3, warmup=1)
+        cpu = dict(value=v, unit="tokens/s", **info)
+
+    if rank == 0:
+        line = {
+            "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K,
+            "warmup": max(W, 3), "ms_per_step": ms_max / K, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": config,
+            "kv_gbs_whole_step": world * kv_bytes / (ms_max * 1e-3) / 1e9,
+            "roofline": {"kernel": "attn_decode_f16_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
+                         "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "algorithmic_bytes_per_launch": attn_bytes, "ms_per_launch": attn_ms,
+                         "append_ms_per_launch": append_ms},
+            "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks.summary(),
+        }
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,246 @@
+/*
+ * morphkv.h - C ABI of the B200 (sm_100a) KV-cache hot path for MorphServe / SwiftLLM.
+ *
+ * The library replaces, behind the reference's Python worker API, the Triton
+ * kernels of worker/kernels/{paged_attn,kvcache_mgmt,block_mgmt}.py and the
+ * block-copy / pool-carving routines of csrc/src/{block_swapping,memory_manager}.cpp
+ * (paths relative to the reference project root).  Every entry point cites the
+ * reference interface it stands in for.
+ *
+ * Conventions
+ *  - plain C linkage, plain pointers and sizes; no torch / pybind types.
+ *  - every function returns an int status: MKV_OK (0) or a negative mkv_status.
+ *    Nothing throws, exits, traps or prints.  Arguments are validated on the
+ *    host before any launch.
+ *  - the caller owns every buffer and the stream.  Unless stated otherwise a call
+ *    allocates nothing, never synchronises and never reads device memory from
+ *    the host; it enqueues work on `stream` and returns.
+ *  - `device` is the CUDA ordinal the pointers live on; the calling thread's
+ *    current device is saved and restored around the call, so calls may come
+ *    from any host thread.
+ *  - pointers marked "device" must be device-accessible; "host" pointers are
+ *    ordinary host memory.
+ */
+#ifndef MORPHKV_H
+#define MORPHKV_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MKV_MAX_SEGMENTS 65 /* original pool + up to 64 elastic chunks */
+
+typedef enum mkv_status {
+    MKV_OK = 0,
+    MKV_ERR_NULL = -1,      /* a required pointer is NULL */
+    MKV_ERR_SHAPE = -2,     /* a size / stride / count is out of range or unsupported */
+    MKV_ERR_DTYPE = -3,     /* element size not 2 (fp16) or 4 (fp32) */
+    MKV_ERR_WORKSPACE = -4, /* workspace missing, misaligned or too small */
+    MKV_ERR_RANGE = -5,     /* an id (layer, block, segment) is out of range */
+    MKV_ERR_CUDA = -6,      /* a CUDA runtime call failed; see mkv_last_cuda_error */
+    MKV_ERR_NOSPACE = -7,   /* no room: chunk does not fit / too few free blocks */
+    MKV_ERR_ALIGN = -8      /* a pointer or row size is not aligned as required */
+} mkv_status;
+
+/*
+ * The paged pool, K and V separately, each segment laid out as
+ *   [blocks, num_layers, num_kv_heads, block_size, head_dim]   (contiguous)
+ * (reference: worker/model.py:180-190).  Segment 0 is the original pool with
+ * `num_blocks_org` blocks; segment 1+j is elastic chunk j with `chunk_blocks`
+ * blocks, holding block ids num_blocks_org + j*chunk_blocks + i.  This is the
+ * id -> address rule of worker/kernels/paged_attn.py:354-360 with the chunk
+ * bases stated explicitly instead of derived by negative offsets from chunk 0.
+ */
+typedef struct mkv_pool {
+    int32_t num_segments; /* 1 + number of elastic chunks, <= MKV_MAX_SEGMENTS */
+    int32_t elem_bytes;   /* 2 = fp16, 4 = fp32 */
+    int32_t num_layers;
+    int32_t num_kv_heads;
+    int32_t block_size;   /* tokens per block */
+    int32_t head_dim;
+    int64_t num_blocks_org;
+    int64_t chunk_blocks; /* ignored when num_segments == 1 */
+    void *k_base[MKV_MAX_SEGMENTS]; /* device */
+    void *v_base[MKV_MAX_SEGMENTS]; /* device */
+} mkv_pool;
+
+/* ---- library --------------------------------------------------------- */
+int mkv_version(void);
+const char *mkv_status_string(int status);
+/* Text of the last CUDA error seen by this thread inside the library. */
+const char *mkv_last_cuda_error(void);
+/* Number of SMs of `device` (cached after the first call). */
+int mkv_sm_count(int device, int *sm_count);
+
+/* ---- decode attention ------------------------------------------------ */
+/*
+ * Replaces paged_attention() and its Triton phases
+ * (worker/kernels/paged_attn.py:59-240 phase 1, :243-437 elastic phase 1,
+ * :658-696 phase 2, :700-1015 wrapper).
+ *
+ * The work is split in two calls.  mkv_attn_plan runs once per decode step (the
+ * schedule depends only on the sequence lengths, which all layers of a step
+ * share); mkv_paged_attention_decode runs once per layer and uses the plan.
+ * Both need the same `workspace` (device memory, 256-byte aligned, at least
+ * mkv_attn_workspace_bytes(...) bytes, contents private to the library between
+ * the plan and the last attention call that uses it).  Calls that share a
+ * workspace must be ordered on the GPU (same stream or event-ordered).
+ *
+ * fast path: fp16, head_dim 128, block_size 16, num_q_heads/num_kv_heads <= 16.
+ * Everything else (fp32 pools, other head_dim <= 256 / block sizes) takes a
+ * plain kernel that ignores the plan.
+ */
+size_t mkv_attn_workspace_bytes(int device, int batch, int num_q_heads, int num_kv_heads,
+                                int head_dim, int max_blocks_per_seq_in_batch);
+
+int mkv_attn_plan(int device, void *stream, void *workspace, size_t workspace_bytes,
+                  const int32_t *seq_lens /* device [batch] */, int batch, int num_q_heads,
+                  int num_kv_heads, int head_dim, int block_size,
+                  int max_blocks_per_seq_in_batch /* host upper bound of ceil(len/block_size) */);
+
+int mkv_paged_attention_decode(
+    int device, void *stream,
+    const void *q,               /* device [batch, num_q_heads, head_dim], pool dtype, contiguous */
+    void *o,                     /* device [batch, num_q_heads, head_dim], pool dtype, contiguous */
+    const mkv_pool *pool,        /* host */
+    const int32_t *block_table,  /* device [*, table_stride] */
+    int64_t table_stride,        /* = max_blocks_per_seq */
+    const int32_t *seq_ids,      /* device [batch]: row of the block table */
+    const int32_t *seq_lens,     /* device [batch]: tokens to attend to (includes the newest) */
+    int batch, int num_q_heads, int cur_layer, float softmax_scale,
+    int max_blocks_per_seq_in_batch, /* the value given to mkv_attn_plan */
+    void *workspace, size_t workspace_bytes);
+
+/*
+ * Copies the device-side error word of a workspace to `*flags` (synchronises the
+ * stream).  Bit 0: a block-table entry was outside the pool and was skipped.
+ */
+int mkv_attn_read_error_flags(int device, void *stream, const void *workspace, int *flags /* host */);
+
+/* ---- KV append / scatter --------------------------------------------- */
+/*
+ * Decode append: token len-1 of every sequence goes to
+ * pool[block_table[seq, (len-1)/bs], layer, :, (len-1)%bs, :], K and V.
+ * Replaces _fwd_kvcache_mgmt_decoding_kernel{,_new_kv_combined}
+ * (worker/kernels/kvcache_mgmt.py:52-81, :189-251).  Pure byte copy.
+ */
+int mkv_store_kv_decode(int device, void *stream, const void *k, const void *v, /* device [batch, Hkv, D] */
+                        const mkv_pool *pool, const int32_t *block_table, int64_t table_stride,
+                        const int32_t *seq_ids, const int32_t *seq_lens, int batch, int cur_layer);
+
+/*
+ * Prefill scatter: token t of prompt i (rows start_locs[i]+t of k/v) goes to
+ * pool[block_table[seq_ids[i], t/bs], layer, :, t%bs, :].  Replaces
+ * _fwd_kvcache_mgmt_prefill_kernel{,_new_kv_combined}
+ * (worker/kernels/kvcache_mgmt.py:12-50, :84-187).
+ */
+int mkv_store_kv_prefill(int device, void *stream, const void *k, const void *v, /* device [tokens, Hkv, D] */
+                         const mkv_pool *pool, const int32_t *block_table, int64_t table_stride,
+                         const int32_t *seq_ids, const int32_t *start_locs, const int32_t *seq_lens,
+                         int num_seqs, int max_seq_len, int cur_layer);
+
+/* ---- block table ------------------------------------------------------ */
+/*
+ * need[i] = ceil(target_lens[i]/block_size) - num_allocated[seq_ids[i]];
+ * totals[0] = sum(need), totals[1] = number of negative entries (the reference
+ * asserts there are none, worker/block_manager.py:94-99).
+ */
+int mkv_block_need(int device, void *stream, const int32_t *num_allocated, const int32_t *seq_ids,
+                   const int32_t *target_lens, int batch, int block_size,
+                   int32_t *need /* device [batch] */, int64_t *totals /* device [2] */);
+
+/*
+ * Ascending ids i in [lo, hi) with bitmap[i] == want, at most max_out of them,
+ * written to out_ids; *out_count = min(matches, max_out) and *out_total = all
+ * matches in the range.  If flip != 0 the selected entries are set to !want.
+ * With lo=0, hi=num_blocks, want=1, flip=1 this is the first-fit allocation of
+ * worker/block_manager.py:75-77 (torch.nonzero(...)[:n]) without a host sync.
+ * One thread block; needs no scratch.
+ */
+int mkv_bitmap_select(int device, void *stream, uint8_t *bitmap, int64_t lo, int64_t hi, int want,
+                      int64_t max_out, int flip, int64_t *out_ids /* device [max_out] */,
+                      int64_t *out_count /* device */, int64_t *out_total /* device */);
+
+/* bitmap[ids[i]] = value for i < n. */
+int mkv_bitmap_scatter(int device, void *stream, uint8_t *bitmap, int64_t bitmap_len,
+                       const int64_t *ids, int64_t n, int value);
+
+/*
+ * Appends candidate ids to the rows of the batch and bumps the counts:
+ * replaces set_block_table_and_num_seq_alloc_blocks
+ * (worker/kernels/block_mgmt.py:5-46).  Sequence i takes
+ * candidates[cumsum(need)[i]-need[i] : cumsum(need)[i]] (batch order).
+ */
+int mkv_block_table_set(int device, void *stream, int32_t *num_allocated, int32_t *block_table,
+                        int64_t table_stride, const int64_t *candidates, const int32_t *seq_ids,
+                        const int32_t *need, int batch);
+
+/*
+ * Marks the blocks of the given sequences free and zeroes their counts; rows
+ * keep their entries.  Replaces unset_block_table_and_num_seq_alloc_blocks
+ * (worker/kernels/block_mgmt.py:49-80).  If gathered != NULL the ids are also
+ * written there in batch order (int32), which replaces
+ * gather_allocated_blocks_and_unset (:83-125); gathered_capacity guards it.
+ * total_out (device, may be NULL) receives the number of blocks freed.
+ */
+int mkv_block_table_unset(int device, void *stream, int32_t *num_allocated, const int32_t *block_table,
+                          int64_t table_stride, const int32_t *seq_ids, int batch, uint8_t *is_block_free,
+                          int64_t num_blocks, int32_t *gathered, int64_t gathered_capacity,
+                          int64_t *total_out);
+
+/* sum over the batch of num_allocated[seq_ids[i]] -> *total_out (device). */
+int mkv_block_table_count(int device, void *stream, const int32_t *num_allocated, const int32_t *seq_ids,
+                          int batch, int64_t *total_out);
+
+/* ---- elastic resize --------------------------------------------------- */
+/*
+ * Where an elastic chunk sits in a freed weight slab and how many blocks it
+ * holds: the sizing rule of MemoryManager::acquire_new_kvcache
+ * (csrc/src/memory_manager.cpp:84-97,129-147; fp16 is fixed there, elem_bytes
+ * generalises it).  Host arithmetic only.  MKV_ERR_NOSPACE when no block fits.
+ */
+int mkv_chunk_layout(uint64_t org_start, uint64_t org_size, uint64_t quant_size, int num_layers,
+                     int num_kv_heads, int block_size, int head_dim, int elem_bytes,
+                     uint64_t *k_addr, uint64_t *v_addr, int64_t *num_blocks);
+
+/*
+ * Whole-block copies inside the pool: block src_ids[i] -> dst_ids[i], K and V,
+ * all layers (one block is contiguous).  Used by compaction; the reference has
+ * no counterpart (its release needs an already-empty tail,
+ * server/memory_utils.py:529-544).  src and dst sets must be disjoint.
+ */
+int mkv_copy_blocks(int device, void *stream, const mkv_pool *pool, const int64_t *src_ids /* device */,
+                    const int64_t *dst_ids /* device */, int64_t n);
+
+/*
+ * Rewrites live block-table entries: for every row r < num_rows and column
+ * j < num_allocated[r], an entry equal to src_ids[i] becomes dst_ids[i].
+ * src_ids must be ascending.  Columns >= num_allocated[r] are left alone.
+ */
+int mkv_remap_block_table(int device, void *stream, int32_t *block_table, int64_t table_stride,
+                          int64_t num_rows, const int32_t *num_allocated, const int64_t *src_ids,
+                          const int64_t *dst_ids, int64_t n);
+
+/* ---- swap -------------------------------------------------------------- */
+/*
+ * Block copies between the device pool and the host swap space
+ * [num_cpu_blocks, L, Hkv, bs, D].  Replaces swap_blocks and
+ * swap_blocks_new_kv_combined (csrc/src/block_swapping.cpp:22-85, :88-202):
+ * runs in which both id lists advance by one, and stay inside one pool
+ * segment, become one cudaMemcpyAsync for K and one for V on `stream`.
+ * Swap-in: host block src -> device block dst.  Swap-out: device src -> host dst.
+ * (The reference's elastic variant derives the device address of a swap-in
+ * from the source id, :156-161; here it always comes from the device-side id.)
+ * ids are HOST arrays.  *num_copies (may be NULL) receives the copies issued.
+ */
+int mkv_swap_blocks(int device, void *stream, const mkv_pool *pool, void *k_swap /* host */,
+                    void *v_swap /* host */, int64_t num_swap_blocks, const int64_t *src_ids /* host */,
+                    const int64_t *dst_ids /* host */, int64_t n, int is_swap_in, int64_t *num_copies);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MORPHKV_H */

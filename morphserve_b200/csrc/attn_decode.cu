@@ -1,0 +1,805 @@
+// Paged-attention decode for sm_100a.
+//
+// HBM-bound: per layer every K and V tile ([16 tokens x 128] fp16 = 4 KiB,
+// contiguous in the pool) is read exactly once per KV head; the G = Hq/Hkv query
+// heads that share it are packed as the M rows of a 16 x 16 x 16 tensor-core tile.
+//
+// Structure
+//   plan kernel (once per decode step): cuts every sequence into chunks of
+//     `chunk` blocks so that there are a few work items per resident warp, and
+//     sorts the (sequence, chunk) items longest first.
+//   decode kernel (once per layer): one persistent thread block per SM; every
+//     WARP is an independent worker that pulls (item, kv head) pairs from a
+//     global counter, streams the item's K/V tiles through a private
+//     cp.async ring in shared memory (XOR-swizzled for ldmatrix), and keeps an
+//     fp32 online softmax in base 2.  A sequence cut into several chunks goes
+//     through fp32 partials in the workspace; the warp that finishes a
+//     (sequence, kv head) last merges them (no second launch, no waiting).
+//   plain kernel: any dtype / head_dim / block size, one warp per (seq, q head).
+//
+// No kernel here waits on another thread block, so nothing can spin forever.
+#include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
+
+#include "common.cuh"
+
+namespace mkv {
+
+constexpr int kD = 128;                 // head_dim of the fast path
+constexpr int kBS = 16;                 // block_size of the fast path
+constexpr int kTileBytes = kBS * kD * 2;  // 4 KiB
+constexpr int kStageBytes = 2 * kTileBytes;
+constexpr int kNumCand = 40;
+constexpr int kMinChunk = 4;            // blocks
+constexpr int kSortBins = 1024;
+constexpr unsigned kMagic = 0x4d4b5631u;  // "MKV1"
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kNegBig = -1e20f;       // the reference's mask / initial max
+
+struct alignas(256) WsHeader {
+    unsigned magic;
+    int batch;
+    int n_items;        // (sequence, chunk) items; work units = n_items * Hkv
+    int chunk_blocks;
+    unsigned work_counter;
+    unsigned done_counter;
+    int error_flags;
+    int n_partial_rows;
+    int cap_items;
+};
+
+struct WsLayout {
+    size_t items, items_tmp, split_info, arrive, lse, part_o, total;
+    int cap_items;
+};
+
+static inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+static double item_factor() {
+    static double f = 0.0;
+    if (f == 0.0) {
+        const char *e = getenv("MKV_ATTN_ITEM_FACTOR");  // tuning knob: work units per worker warp
+        double v = e ? atof(e) : 0.0;
+        f = (v > 0.0) ? v : 4.0;
+    }
+    return f;
+}
+
+static WsLayout make_layout(int sm_count, int batch, int num_q_heads, int num_kv_heads, int head_dim,
+                            int max_blocks) {
+    WsLayout L;
+    const int64_t workers = (int64_t)sm_count * 8;
+    int64_t target = (int64_t)ceil(item_factor() * (double)workers / (double)num_kv_heads);
+    int64_t cap = (int64_t)batch + target;
+    int64_t most = (int64_t)batch * ceil_div64(max_blocks > 0 ? max_blocks : 1, kMinChunk);
+    if (cap > most) cap = most;
+    if (cap < batch) cap = batch;
+    if (cap < 1) cap = 1;
+    L.cap_items = (int)cap;
+    size_t off = sizeof(WsHeader);
+    L.items = off;       off = align256(off + (size_t)cap * sizeof(int4));
+    L.items_tmp = off;   off = align256(off + (size_t)cap * sizeof(int4));
+    L.split_info = off;  off = align256(off + (size_t)batch * sizeof(int2));
+    L.arrive = off;      off = align256(off + (size_t)batch * num_kv_heads * sizeof(int));
+    L.lse = off;         off = align256(off + (size_t)cap * num_q_heads * sizeof(float));
+    L.part_o = off;      off = align256(off + (size_t)cap * num_q_heads * head_dim * sizeof(float));
+    L.total = off;
+    return L;
+}
+
+__host__ __device__ __forceinline__ int chunk_candidate(int k) {
+    return (k & 1) ? (6 << (k >> 1)) : (4 << (k >> 1));  // 4,6,8,12,16,24,...
+}
+
+// ------------------------------------------------------------------ plan
+__device__ __forceinline__ int plan_scan(int v, int &total, int *warp_sums) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    int incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        int n = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += n;
+    }
+    __syncthreads();
+    if (lane == 31) warp_sums[wid] = incl;
+    __syncthreads();
+    if (wid == 0) {
+        int w = warp_sums[lane];
+        int wi = w;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            int n = __shfl_up_sync(0xffffffffu, wi, d);
+            if (lane >= d) wi += n;
+        }
+        warp_sums[lane] = wi - w;
+        if (lane == 31) warp_sums[32] = wi;
+    }
+    __syncthreads();
+    total = warp_sums[32];
+    return warp_sums[wid] + incl - v;
+}
+
+__global__ void __launch_bounds__(1024) attn_plan_kernel(WsHeader *hdr, int4 *items, int4 *items_tmp, int2 *split_info,
+                                                       int *arrive, const int32_t *__restrict__ seq_lens, int batch,
+                                                       int num_kv_heads, int block_size, int cap_items) {
+    __shared__ int cnt[kNumCand];
+    __shared__ int hist[kSortBins + 1];
+    __shared__ int start[kSortBins + 1];
+    __shared__ int warp_sums[33];
+    __shared__ int s_chunk;
+    const int tid = threadIdx.x;
+
+    for (int k = tid; k < kNumCand; k += blockDim.x) cnt[k] = 0;
+    for (int k = tid; k <= kSortBins; k += blockDim.x) hist[k] = 0;
+    __syncthreads();
+    for (int b = tid; b < batch; b += blockDim.x) {
+        int len = seq_lens[b];
+        int nblk = len > 0 ? (len + block_size - 1) / block_size : 0;
+        if (nblk > 0) {
+            for (int k = 0; k < kNumCand; ++k) {
+                int c = chunk_candidate(k);
+                atomicAdd(&cnt[k], (nblk + c - 1) / c);
+            }
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int k = 0;
+        while (k < kNumCand - 1 && cnt[k] > cap_items) ++k;
+        s_chunk = chunk_candidate(k);
+    }
+    __syncthreads();
+    const int chunk = s_chunk;
+
+    int carry_items = 0, carry_rows = 0;
+    for (int base = 0; base < batch; base += blockDim.x) {
+        const int b = base + tid;
+        int nblk = 0;
+        if (b < batch) {
+            int len = seq_lens[b];
+            nblk = len > 0 ? (len + block_size - 1) / block_size : 0;
+        }
+        const int ns = (nblk + chunk - 1) / chunk;
+        const int pr = ns > 1 ? ns : 0;
+        int tot_i, tot_r;
+        const int off_i = plan_scan(ns, tot_i, warp_sums);
+        const int off_r = plan_scan(pr, tot_r, warp_sums);
+        if (b < batch) {
+            split_info[b] = make_int2(ns, carry_rows + off_r);
+            for (int s = 0; s < ns; ++s) {
+                int pos = carry_items + off_i + s;
+                int n = min(chunk, nblk - s * chunk);
+                if (pos < cap_items) {
+                    items_tmp[pos] = make_int4(b, s * chunk, n, s);
+                    atomicAdd(&hist[min(n, kSortBins)], 1);
+                }
+            }
+        }
+        carry_items += tot_i;
+        carry_rows += tot_r;
+    }
+    const int n_items = min(carry_items, cap_items);
+    __syncthreads();
+    // longest first: thread t owns bin kSortBins - t
+    {
+        int total;
+        int bin = kSortBins - tid;
+        int v = (bin >= 0) ? hist[bin] : 0;
+        int off = plan_scan(v, total, warp_sums);
+        if (bin >= 0) start[bin] = off;
+        if (tid == 0) start[0] = 0;  // bin 0 is never used (n >= 1); 1025 bins, 1024 threads
+    }
+    __syncthreads();
+    for (int i = tid; i < n_items; i += blockDim.x) {
+        int4 it = items_tmp[i];
+        int pos = atomicAdd(&start[min(it.z, kSortBins)], 1);
+        items[pos] = it;
+    }
+    for (int i = tid; i < batch * num_kv_heads; i += blockDim.x) arrive[i] = 0;
+    if (tid == 0) {
+        hdr->magic = kMagic;
+        hdr->batch = batch;
+        hdr->n_items = n_items;
+        hdr->chunk_blocks = chunk;
+        hdr->work_counter = 0;
+        hdr->done_counter = 0;
+        hdr->error_flags = (carry_items > cap_items) ? 4 : 0;
+        hdr->n_partial_rows = carry_rows;
+        hdr->cap_items = cap_items;
+    }
+}
+
+// ------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3, uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr)
+                 : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3,
+                                                  uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr)
+                 : "memory");
+}
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
+// ------------------------------------------------------------------ decode kernel
+struct AttnParams {
+    PoolView pool;
+    const __half *q;
+    __half *o;
+    const int32_t *block_table;
+    int64_t table_stride;
+    const int32_t *seq_ids;
+    const int32_t *seq_lens;
+    int batch;
+    int num_q_heads;
+    int group;          // Hq / Hkv, <= 16
+    int cur_layer;
+    float scale_log2;   // softmax_scale * log2(e)
+    WsHeader *hdr;
+    const int4 *items;
+    const int2 *split_info;
+    int *arrive;
+    float *lse;
+    float *part_o;
+};
+
+struct WorkMeta {
+    bool valid;
+    int b, h, start, nblk, split, nsplit, prow, len;
+    const int32_t *table;  // first entry of the item in the block table
+    int ids;               // lane l: block id of tile l of the item
+};
+
+template <int WARPS, int STAGES>
+__global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __grid_constant__ AttnParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t ring = smem_u32(smem) + warp * (STAGES * kStageBytes);
+
+    WsHeader *hdr = p.hdr;
+    if (hdr->magic != kMagic || hdr->batch != p.batch) {  // no plan for this batch: refuse, touch nothing
+        if (threadIdx.x == 0) atomicOr(&hdr->error_flags, 2);
+        return;
+    }
+    const int Hkv = p.pool.num_kv_heads;
+    const int G = p.group;
+    const unsigned total_units = (unsigned)hdr->n_items * (unsigned)Hkv;
+    const bool row0 = g < G, row1 = (g + 8) < G;
+
+    auto fetch = [&](WorkMeta &m) {
+        unsigned idx = 0;
+        if (lane == 0) idx = atomicAdd(&hdr->work_counter, 1u);
+        idx = __shfl_sync(0xffffffffu, idx, 0);
+        m.valid = idx < total_units;
+        if (!m.valid) return;
+        const unsigned bc = idx / (unsigned)Hkv;
+        m.h = (int)(idx - bc * (unsigned)Hkv);
+        const int4 it = __ldg(p.items + bc);
+        const int2 si = __ldg(p.split_info + it.x);
+        m.b = it.x;
+        m.start = it.y;
+        m.nblk = it.z;
+        m.split = it.w;
+        m.nsplit = si.x;
+        m.prow = si.y + it.w;
+        m.len = __ldg(p.seq_lens + it.x);
+        const int64_t row = __ldg(p.seq_ids + it.x);
+        m.table = p.block_table + row * p.table_stride + it.y;
+        m.ids = (lane < m.nblk) ? __ldg(m.table + lane) : 0;
+    };
+
+    // lane-constant pieces of the shared-memory addressing (bytes inside a 4 KiB tile)
+    // K (S = Q K^T): matrix mi = lane>>3 : token half = mi>>1, k half = mi&1
+    const int k_tok = ((lane >> 4) << 3) + (lane & 7);
+    const int k_half = (lane >> 3) & 1;
+    // V (O += P V): matrix mi: token half = mi&1, dim chunk half = mi>>1
+    const int v_tok = (((lane >> 3) & 1) << 3) + (lane & 7);
+    const int v_half = lane >> 4;
+
+    WorkMeta nxt;
+    fetch(nxt);
+    while (nxt.valid) {
+        const WorkMeta cur = nxt;
+        __syncwarp();  // the previous item's ldmatrix reads are done before the ring is refilled
+
+        // ---- tile loader ------------------------------------------------------
+        int ids_cur = cur.ids;
+        int ids_nxt = (32 + lane < cur.nblk) ? __ldg(cur.table + 32 + lane) : 0;
+        int win = 0;  // window of 32 tiles that ids_cur covers
+        const int64_t head_off = ((int64_t)p.cur_layer * Hkv + cur.h) * kTileBytes;
+        auto issue_tile = [&](int j) {
+            if ((j >> 5) != win) {
+                ids_cur = ids_nxt;
+                ++win;
+                const int nj = (win + 1) * 32 + lane;
+                ids_nxt = (nj < cur.nblk) ? __ldg(cur.table + nj) : 0;
+            }
+            int64_t blk = __shfl_sync(0xffffffffu, ids_cur, j & 31);
+            if (!block_in_pool(p.pool, blk)) {
+                if (lane == 0) atomicOr(&hdr->error_flags, 1);
+                blk = 0;
+            }
+            int seg;
+            int64_t brow;
+            locate_block(p.pool, blk, seg, brow);
+            const char *kt = p.pool.k_base[seg] + brow * p.pool.block_bytes + head_off;
+            const char *vt = p.pool.v_base[seg] + brow * p.pool.block_bytes + head_off;
+            const uint32_t st = ring + (j % STAGES) * kStageBytes;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int id = i * 32 + lane;           // 16-byte piece of the tile
+                const int r = id >> 4, c = id & 15;     // token row, piece in the row
+                const uint32_t off = r * 256 + ((c ^ (r & 7)) << 4);
+                cp_async16(st + off, kt + id * 16);
+                cp_async16(st + kTileBytes + off, vt + id * 16);
+            }
+        };
+
+#pragma unroll
+        for (int s = 0; s < STAGES - 1; ++s) {
+            if (s < cur.nblk) issue_tile(s);
+            cp_async_commit();
+        }
+
+        // ---- Q fragments (A operand, rows = query heads of the group) -----------
+        uint32_t qf[8][4];
+        {
+            const __half *qb = p.q + ((int64_t)cur.b * p.num_q_heads + (int64_t)cur.h * G) * kD;
+            const uint32_t *q0 = reinterpret_cast<const uint32_t *>(qb + (int64_t)g * kD) + t;
+            const uint32_t *q1 = reinterpret_cast<const uint32_t *>(qb + (int64_t)(g + 8) * kD) + t;
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+                qf[kk][0] = row0 ? __ldg(q0 + kk * 8) : 0u;
+                qf[kk][1] = row1 ? __ldg(q1 + kk * 8) : 0u;
+                qf[kk][2] = row0 ? __ldg(q0 + kk * 8 + 4) : 0u;
+                qf[kk][3] = row1 ? __ldg(q1 + kk * 8 + 4) : 0u;
+            }
+        }
+
+        fetch(nxt);  // overlaps with the prologue loads in flight
+
+        float oacc[16][4];
+#pragma unroll
+        for (int n = 0; n < 16; ++n) oacc[n][0] = oacc[n][1] = oacc[n][2] = oacc[n][3] = 0.f;
+        float m0 = kNegBig, m1 = kNegBig, l0 = 0.f, l1 = 0.f;
+
+        for (int j = 0; j < cur.nblk; ++j) {
+            cp_async_wait<STAGES - 2>();
+            __syncwarp();
+            if (j + STAGES - 1 < cur.nblk) issue_tile(j + STAGES - 1);
+            cp_async_commit();
+
+            const uint32_t st = ring + (j % STAGES) * kStageBytes;
+            // S = Q K^T   (16 heads x 16 tokens)
+            float sc[2][4];
+#pragma unroll
+            for (int jj = 0; jj < 2; ++jj) sc[jj][0] = sc[jj][1] = sc[jj][2] = sc[jj][3] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+                uint32_t b0, b1, b2, b3;
+                const int c = 2 * kk + k_half;
+                ldmatrix_x4(b0, b1, b2, b3, st + k_tok * 256 + ((c ^ (k_tok & 7)) << 4));
+                mma_16816(sc[0], qf[kk], b0, b1);
+                mma_16816(sc[1], qf[kk], b2, b3);
+            }
+            // scale, mask the tail of the sequence
+            const int valid = cur.len - (cur.start + j) * kBS;  // tokens of this tile inside the sequence
+#pragma unroll
+            for (int jj = 0; jj < 2; ++jj) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int tok = jj * 8 + 2 * t + (e & 1);
+                    const float v = sc[jj][e] * p.scale_log2;
+                    sc[jj][e] = (tok < valid) ? v : kNegBig;
+                }
+            }
+            float mx0 = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
+            float mx1 = fmaxf(fmaxf(sc[0][2], sc[0][3]), fmaxf(sc[1][2], sc[1][3]));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+            const float a0 = fast_exp2(m0 - mn0), a1 = fast_exp2(m1 - mn1);
+            m0 = mn0;
+            m1 = mn1;
+            float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+            for (int jj = 0; jj < 2; ++jj) {
+                sc[jj][0] = fast_exp2(sc[jj][0] - mn0);
+                sc[jj][1] = fast_exp2(sc[jj][1] - mn0);
+                sc[jj][2] = fast_exp2(sc[jj][2] - mn1);
+                sc[jj][3] = fast_exp2(sc[jj][3] - mn1);
+                ps0 += sc[jj][0] + sc[jj][1];
+                ps1 += sc[jj][2] + sc[jj][3];
+            }
+            l0 = l0 * a0 + ps0;  // per-thread share of the row sum; reduced over the quad at the end
+            l1 = l1 * a1 + ps1;
+#pragma unroll
+            for (int n = 0; n < 16; ++n) {
+                oacc[n][0] *= a0;
+                oacc[n][1] *= a0;
+                oacc[n][2] *= a1;
+                oacc[n][3] *= a1;
+            }
+            // P (16 heads x 16 tokens) as the A operand of O += P V
+            uint32_t pa[4];
+            pa[0] = pack_half2(sc[0][0], sc[0][1]);
+            pa[1] = pack_half2(sc[0][2], sc[0][3]);
+            pa[2] = pack_half2(sc[1][0], sc[1][1]);
+            pa[3] = pack_half2(sc[1][2], sc[1][3]);
+#pragma unroll
+            for (int np = 0; np < 8; ++np) {
+                uint32_t b0, b1, b2, b3;
+                const int c = 2 * np + v_half;
+                ldmatrix_x4_trans(b0, b1, b2, b3, st + kTileBytes + v_tok * 256 + ((c ^ (v_tok & 7)) << 4));
+                mma_16816(oacc[2 * np], pa, b0, b1);
+                mma_16816(oacc[2 * np + 1], pa, b2, b3);
+            }
+        }
+        cp_async_wait<0>();
+
+        // ---- epilogue ---------------------------------------------------------
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+        const float inv0 = 1.f / l0, inv1 = 1.f / l1;
+        const int hq0 = cur.h * G;  // first query head of the group
+        if (cur.nsplit == 1) {
+            __half *ob = p.o + ((int64_t)cur.b * p.num_q_heads + hq0) * kD;
+#pragma unroll
+            for (int n = 0; n < 16; ++n) {
+                if (row0)
+                    *reinterpret_cast<__half2 *>(ob + (int64_t)g * kD + n * 8 + 2 * t) =
+                        __floats2half2_rn(oacc[n][0] * inv0, oacc[n][1] * inv0);
+                if (row1)
+                    *reinterpret_cast<__half2 *>(ob + (int64_t)(g + 8) * kD + n * 8 + 2 * t) =
+                        __floats2half2_rn(oacc[n][2] * inv1, oacc[n][3] * inv1);
+            }
+        } else {
+            float *po = p.part_o + ((int64_t)cur.prow * p.num_q_heads + hq0) * kD;
+            float *pl = p.lse + (int64_t)cur.prow * p.num_q_heads + hq0;
+#pragma unroll
+            for (int n = 0; n < 16; ++n) {
+                if (row0)
+                    __stcg(reinterpret_cast<float2 *>(po + (int64_t)g * kD + n * 8 + 2 * t),
+                           make_float2(oacc[n][0] * inv0, oacc[n][1] * inv0));
+                if (row1)
+                    __stcg(reinterpret_cast<float2 *>(po + (int64_t)(g + 8) * kD + n * 8 + 2 * t),
+                           make_float2(oacc[n][2] * inv1, oacc[n][3] * inv1));
+            }
+            if (t == 0) {
+                if (row0) __stcg(pl + g, log2f(l0) + m0);
+                if (row1) __stcg(pl + g + 8, log2f(l1) + m1);
+            }
+            __threadfence();
+            __syncwarp();
+            int *cnt = p.arrive + (int64_t)cur.b * Hkv + cur.h;
+            int old = 0;
+            if (lane == 0) old = atomicAdd(cnt, 1);
+            old = __shfl_sync(0xffffffffu, old, 0);
+            if (old == cur.nsplit - 1) {  // every chunk of this (sequence, kv head) is in the workspace
+                __threadfence();
+                if (lane == 0) *cnt = 0;
+                const int64_t base = cur.prow - cur.split;
+                for (int r = 0; r < G; ++r) {
+                    const int hq = hq0 + r;
+                    float mx = -INFINITY;
+                    for (int s = 0; s < cur.nsplit; ++s)
+                        mx = fmaxf(mx, __ldcg(p.lse + (base + s) * p.num_q_heads + hq));
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                    float wsum = 0.f;
+                    for (int s = 0; s < cur.nsplit; ++s) {
+                        const float w = exp2f(__ldcg(p.lse + (base + s) * p.num_q_heads + hq) - mx);
+                        const float4 v = __ldcg(reinterpret_cast<const float4 *>(
+                            p.part_o + ((base + s) * p.num_q_heads + hq) * kD + lane * 4));
+                        acc.x += w * v.x;
+                        acc.y += w * v.y;
+                        acc.z += w * v.z;
+                        acc.w += w * v.w;
+                        wsum += w;
+                    }
+                    const float inv = 1.f / wsum;
+                    __half2 h01 = __floats2half2_rn(acc.x * inv, acc.y * inv);
+                    __half2 h23 = __floats2half2_rn(acc.z * inv, acc.w * inv);
+                    uint2 pk;
+                    pk.x = *reinterpret_cast<uint32_t *>(&h01);
+                    pk.y = *reinterpret_cast<uint32_t *>(&h23);
+                    *reinterpret_cast<uint2 *>(p.o + ((int64_t)cur.b * p.num_q_heads + hq) * kD + lane * 4) = pk;
+                }
+            }
+        }
+    }
+    // the last worker to run dry re-arms the counters for the next launch
+    if (lane == 0) {
+        const unsigned workers = gridDim.x * WARPS;
+        const unsigned d = atomicAdd(&hdr->done_counter, 1u);
+        if (d == workers - 1) {
+            hdr->work_counter = 0;
+            hdr->done_counter = 0;
+        }
+    }
+}
+
+// ------------------------------------------------------------------ plain kernel
+template <typename T>
+__device__ __forceinline__ float to_f32(T x);
+template <>
+__device__ __forceinline__ float to_f32<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half x) { return __half2float(x); }
+template <typename T>
+__device__ __forceinline__ T from_f32_via_half(float x);  // the reference stores fp16-rounded values
+template <>
+__device__ __forceinline__ float from_f32_via_half<float>(float x) { return __half2float(__float2half_rn(x)); }
+template <>
+__device__ __forceinline__ __half from_f32_via_half<__half>(float x) { return __float2half_rn(x); }
+
+constexpr int kMaxDimsPerLane = 8;  // head_dim <= 256
+
+template <typename T>
+__global__ void attn_decode_plain_kernel(const __grid_constant__ PoolView pool, const T *__restrict__ q, T *__restrict__ o,
+                                         const int32_t *__restrict__ block_table, int64_t table_stride,
+                                         const int32_t *__restrict__ seq_ids, const int32_t *__restrict__ seq_lens,
+                                         int batch, int num_q_heads, int cur_layer, float scale_log2, int *error_flags) {
+    const int lane = threadIdx.x & 31;
+    const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (wid >= (int64_t)batch * num_q_heads) return;
+    const int b = (int)(wid / num_q_heads);
+    const int hq = (int)(wid - (int64_t)b * num_q_heads);
+    const int G = num_q_heads / pool.num_kv_heads;
+    const int h = hq / G;
+    const int D = pool.head_dim, bs = pool.block_size;
+    const int len = seq_lens[b];
+    if (len <= 0) return;
+    const int64_t row = seq_ids[b];
+    float qr[kMaxDimsPerLane], acc[kMaxDimsPerLane];
+#pragma unroll
+    for (int i = 0; i < kMaxDimsPerLane; ++i) {
+        const int d = lane + 32 * i;
+        qr[i] = d < D ? to_f32<T>(q[((int64_t)b * num_q_heads + hq) * D + d]) : 0.f;
+        acc[i] = 0.f;
+    }
+    float m = kNegBig, l = 0.f;
+    const int nblk = (len + bs - 1) / bs;
+    const int64_t tile_elems = (int64_t)bs * D;
+    for (int jb = 0; jb < nblk; ++jb) {
+        const int64_t blk = block_table[row * table_stride + jb];
+        if (!block_in_pool(pool, blk)) {
+            if (lane == 0 && error_flags) atomicOr(error_flags, 1);
+            continue;
+        }
+        int seg;
+        int64_t brow;
+        locate_block(pool, blk, seg, brow);
+        const int64_t off = brow * pool.block_bytes +
+                            ((int64_t)cur_layer * pool.num_kv_heads + h) * tile_elems * (int64_t)sizeof(T);
+        const T *kt = reinterpret_cast<const T *>(pool.k_base[seg] + off);
+        const T *vt = reinterpret_cast<const T *>(pool.v_base[seg] + off);
+        const int ntok = min(bs, len - jb * bs);
+        for (int tk = 0; tk < ntok; ++tk) {
+            float dot = 0.f;
+#pragma unroll
+            for (int i = 0; i < kMaxDimsPerLane; ++i) {
+                const int d = lane + 32 * i;
+                if (d < D) dot += qr[i] * to_f32<T>(kt[(int64_t)tk * D + d]);
+            }
+#pragma unroll
+            for (int s = 16; s > 0; s >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, s);
+            const float sc = dot * scale_log2;
+            const float mn = fmaxf(m, sc);
+            const float a = exp2f(m - mn), pr = exp2f(sc - mn);
+            l = l * a + pr;
+#pragma unroll
+            for (int i = 0; i < kMaxDimsPerLane; ++i) {
+                const int d = lane + 32 * i;
+                if (d < D) acc[i] = acc[i] * a + pr * to_f32<T>(vt[(int64_t)tk * D + d]);
+            }
+            m = mn;
+        }
+    }
+    const float inv = 1.f / l;
+#pragma unroll
+    for (int i = 0; i < kMaxDimsPerLane; ++i) {
+        const int d = lane + 32 * i;
+        if (d < D) o[((int64_t)b * num_q_heads + hq) * D + d] = from_f32_via_half<T>(acc[i] * inv);
+    }
+}
+
+// ------------------------------------------------------------------ host side
+static void attn_variant(int &warps, int &stages) {
+    static int w = 0, s = 0;
+    if (w == 0) {
+        int ww = 8, ss = 3;
+        const char *e = getenv("MKV_ATTN_VARIANT");  // tuning knob: "<warps>x<stages>"
+        if (e) sscanf(e, "%dx%d", &ww, &ss);
+        w = ww;
+        s = ss;
+    }
+    warps = w;
+    stages = s;
+}
+
+template <int WARPS, int STAGES>
+static cudaError_t launch_decode(const AttnParams &p, int sm_count, cudaStream_t s) {
+    const int smem = WARPS * STAGES * kStageBytes;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_f16_kernel<WARPS, STAGES>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    attn_decode_f16_kernel<WARPS, STAGES><<<sm_count, WARPS * 32, smem, s>>>(p);
+    return cudaGetLastError();
+}
+
+static bool fast_path_ok(const PoolView &pv, int num_q_heads, const void *q, const void *o) {
+    if (pv.elem_bytes != 2 || pv.head_dim != kD || pv.block_size != kBS) return false;
+    if (num_q_heads % pv.num_kv_heads != 0 || num_q_heads / pv.num_kv_heads > 16) return false;
+    if ((((uintptr_t)q) | ((uintptr_t)o)) % 16 != 0) return false;
+    for (int i = 0; i < pv.num_segments; ++i)
+        if ((((uintptr_t)pv.k_base[i]) | ((uintptr_t)pv.v_base[i])) % 16 != 0) return false;
+    return true;
+}
+
+}  // namespace mkv
+
+using namespace mkv;
+
+extern "C" {
+
+size_t mkv_attn_workspace_bytes(int device, int batch, int num_q_heads, int num_kv_heads, int head_dim,
+                                int max_blocks_per_seq_in_batch) {
+    int sms = 0;
+    if (mkv_sm_count(device, &sms) != MKV_OK) return 0;
+    if (batch < 0 || num_q_heads < 1 || num_kv_heads < 1 || head_dim < 1) return 0;
+    return make_layout(sms, batch, num_q_heads, num_kv_heads, head_dim, max_blocks_per_seq_in_batch).total;
+}
+
+int mkv_attn_plan(int device, void *stream, void *workspace, size_t workspace_bytes, const int32_t *seq_lens,
+                  int batch, int num_q_heads, int num_kv_heads, int head_dim, int block_size,
+                  int max_blocks_per_seq_in_batch) {
+    if (batch < 0 || num_q_heads < 1 || num_kv_heads < 1 || head_dim < 1 || block_size < 1) return MKV_ERR_SHAPE;
+    if (!workspace || ((uintptr_t)workspace % 256) != 0) return MKV_ERR_WORKSPACE;
+    if (batch > 0 && !seq_lens) return MKV_ERR_NULL;
+    int sms = 0;
+    int st = mkv_sm_count(device, &sms);
+    if (st) return st;
+    WsLayout L = make_layout(sms, batch, num_q_heads, num_kv_heads, head_dim, max_blocks_per_seq_in_batch);
+    if (workspace_bytes < L.total) return MKV_ERR_WORKSPACE;
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
+    char *ws = (char *)workspace;
+    attn_plan_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(
+        (WsHeader *)ws, (int4 *)(ws + L.items), (int4 *)(ws + L.items_tmp), (int2 *)(ws + L.split_info),
+        (int *)(ws + L.arrive), seq_lens, batch, num_kv_heads, block_size, L.cap_items);
+    MKV_LAUNCH_CHECK();
+    return MKV_OK;
+}
+
+int mkv_paged_attention_decode(int device, void *stream, const void *q, void *o, const mkv_pool *pool,
+                               const int32_t *block_table, int64_t table_stride, const int32_t *seq_ids,
+                               const int32_t *seq_lens, int batch, int num_q_heads, int cur_layer,
+                               float softmax_scale, int max_blocks_per_seq_in_batch, void *workspace,
+                               size_t workspace_bytes) {
+    PoolView pv;
+    int st = validate_pool(pool, &pv);
+    if (st) return st;
+    if (batch < 0 || num_q_heads < 1 || table_stride < 1) return MKV_ERR_SHAPE;
+    if (num_q_heads % pv.num_kv_heads != 0) return MKV_ERR_SHAPE;
+    if (pv.head_dim > 32 * kMaxDimsPerLane) return MKV_ERR_SHAPE;
+    if (cur_layer < 0 || cur_layer >= pv.num_layers) return MKV_ERR_RANGE;
+    if (batch == 0) return MKV_OK;
+    if (!q || !o || !block_table || !seq_ids || !seq_lens) return MKV_ERR_NULL;
+    if (pv.total_blocks < 1) return MKV_ERR_SHAPE;
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
+    cudaStream_t s = (cudaStream_t)stream;
+    const float scale_log2 = softmax_scale * kLog2e;
+
+    if (!fast_path_ok(pv, num_q_heads, q, o)) {
+        int *flags = nullptr;
+        if (workspace && workspace_bytes >= sizeof(WsHeader) && ((uintptr_t)workspace % 256) == 0)
+            flags = &((WsHeader *)workspace)->error_flags;
+        const int threads = 128;
+        const int64_t warps = (int64_t)batch * num_q_heads;
+        const unsigned grid = (unsigned)ceil_div64(warps, threads / 32);
+        if (pv.elem_bytes == 2)
+            attn_decode_plain_kernel<__half><<<grid, threads, 0, s>>>(pv, (const __half *)q, (__half *)o, block_table,
+                                                                     table_stride, seq_ids, seq_lens, batch,
+                                                                     num_q_heads, cur_layer, scale_log2, flags);
+        else
+            attn_decode_plain_kernel<float><<<grid, threads, 0, s>>>(pv, (const float *)q, (float *)o, block_table,
+                                                                    table_stride, seq_ids, seq_lens, batch,
+                                                                    num_q_heads, cur_layer, scale_log2, flags);
+        MKV_LAUNCH_CHECK();
+        return MKV_OK;
+    }
+
+    if (!workspace || ((uintptr_t)workspace % 256) != 0) return MKV_ERR_WORKSPACE;
+    int sms = 0;
+    st = mkv_sm_count(device, &sms);
+    if (st) return st;
+    WsLayout L = make_layout(sms, batch, num_q_heads, pv.num_kv_heads, pv.head_dim, max_blocks_per_seq_in_batch);
+    if (workspace_bytes < L.total) return MKV_ERR_WORKSPACE;
+    char *ws = (char *)workspace;
+    AttnParams p;
+    p.pool = pv;
+    p.q = (const __half *)q;
+    p.o = (__half *)o;
+    p.block_table = block_table;
+    p.table_stride = table_stride;
+    p.seq_ids = seq_ids;
+    p.seq_lens = seq_lens;
+    p.batch = batch;
+    p.num_q_heads = num_q_heads;
+    p.group = num_q_heads / pv.num_kv_heads;
+    p.cur_layer = cur_layer;
+    p.scale_log2 = scale_log2;
+    p.hdr = (WsHeader *)ws;
+    p.items = (const int4 *)(ws + L.items);
+    p.split_info = (const int2 *)(ws + L.split_info);
+    p.arrive = (int *)(ws + L.arrive);
+    p.lse = (float *)(ws + L.lse);
+    p.part_o = (float *)(ws + L.part_o);
+
+    int warps, stages;
+    attn_variant(warps, stages);
+    cudaError_t e;
+    if (warps == 6 && stages == 4) e = launch_decode<6, 4>(p, sms, s);
+    else if (warps == 12 && stages == 2) e = launch_decode<12, 2>(p, sms, s);
+    else if (warps == 9 && stages == 3) e = launch_decode<9, 3>(p, sms, s);
+    else if (warps == 7 && stages == 4) e = launch_decode<7, 4>(p, sms, s);
+    else if (warps == 4 && stages == 6) e = launch_decode<4, 6>(p, sms, s);
+    else if (warps == 5 && stages == 5) e = launch_decode<5, 5>(p, sms, s);
+    else e = launch_decode<8, 3>(p, sms, s);
+    if (e != cudaSuccess) return set_cuda_error(e);
+    return MKV_OK;
+}
+
+int mkv_attn_read_error_flags(int device, void *stream, const void *workspace, int *flags) {
+    if (!workspace || !flags) return MKV_ERR_NULL;
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
+    const WsHeader *hdr = (const WsHeader *)workspace;
+    MKV_CUDA_TRY(cudaMemcpyAsync(flags, &hdr->error_flags, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    MKV_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+    return MKV_OK;
+}
+
+}  // extern "C"

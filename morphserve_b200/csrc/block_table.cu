@@ -1,0 +1,285 @@
+// Block-table maintenance: integer kernels, exact.  Each runs as ONE thread
+// block (the tables are small: batch <= a few thousand rows, bitmap <= a few
+// million bytes) so that prefix sums need no scratch memory and no second
+// launch.  None of them synchronises with the host.
+#include "common.cuh"
+
+namespace mkv {
+
+constexpr int kThreads = 1024;
+
+// Exclusive prefix sum of one int per thread across the block; returns the
+// exclusive offset of this thread and the block total in `total`.
+__device__ __forceinline__ int block_exclusive_scan(int v, int &total, int *warp_sums /* [32] shared */) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    int incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        int n = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += n;
+    }
+    __syncthreads();  // protect warp_sums from the previous use
+    if (lane == 31) warp_sums[wid] = incl;
+    __syncthreads();
+    if (wid == 0) {
+        int w = (lane < (int)(blockDim.x >> 5)) ? warp_sums[lane] : 0;
+        int wi = w;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            int n = __shfl_up_sync(0xffffffffu, wi, d);
+            if (lane >= d) wi += n;
+        }
+        warp_sums[lane] = wi - w;  // exclusive offsets of the warps
+        if (lane == 31) warp_sums[32] = wi;
+    }
+    __syncthreads();
+    total = warp_sums[32];
+    return warp_sums[wid] + incl - v;
+}
+
+__global__ void __launch_bounds__(kThreads) block_need_kernel(const int32_t *__restrict__ num_allocated,
+                                                            const int32_t *__restrict__ seq_ids,
+                                                            const int32_t *__restrict__ target_lens, int batch,
+                                                            int block_size, int32_t *__restrict__ need,
+                                                            int64_t *__restrict__ totals) {
+    __shared__ long long s_sum;
+    __shared__ int s_neg;
+    if (threadIdx.x == 0) {
+        s_sum = 0;
+        s_neg = 0;
+    }
+    __syncthreads();
+    long long sum = 0;
+    int neg = 0;
+    for (int i = threadIdx.x; i < batch; i += blockDim.x) {
+        int target = (target_lens[i] + (block_size - 1)) / block_size;
+        int n = target - num_allocated[seq_ids[i]];
+        need[i] = n;
+        sum += n;
+        neg += (n < 0);
+    }
+    for (int d = 16; d > 0; d >>= 1) {
+        sum += __shfl_down_sync(0xffffffffu, sum, d);
+        neg += __shfl_down_sync(0xffffffffu, neg, d);
+    }
+    if ((threadIdx.x & 31) == 0) {
+        atomicAdd((unsigned long long *)&s_sum, (unsigned long long)sum);
+        atomicAdd(&s_neg, neg);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        totals[0] = s_sum;
+        totals[1] = s_neg;
+    }
+}
+
+constexpr int kPerThread = 16;
+
+__global__ void __launch_bounds__(kThreads) bitmap_select_kernel(uint8_t *__restrict__ bitmap, int64_t lo, int64_t hi,
+                                                               int want, int64_t max_out, int flip,
+                                                               int64_t *__restrict__ out_ids,
+                                                               int64_t *__restrict__ out_count,
+                                                               int64_t *__restrict__ out_total) {
+    __shared__ int warp_sums[33];
+    int64_t carry = 0;
+    const bool need_total = out_total != nullptr;
+    for (int64_t base = lo; base < hi; base += (int64_t)kThreads * kPerThread) {
+        if (!need_total && carry >= max_out) break;  // uniform across the block
+        const int64_t i0 = base + (int64_t)threadIdx.x * kPerThread;
+        unsigned mask = 0;
+#pragma unroll
+        for (int j = 0; j < kPerThread; ++j) {
+            int64_t i = i0 + j;
+            if (i < hi) {
+                bool set = bitmap[i] != 0;
+                if (set == (want != 0)) mask |= 1u << j;
+            }
+        }
+        int total;
+        int off = block_exclusive_scan(__popc(mask), total, warp_sums);
+        int64_t pos = carry + off;
+        while (mask) {
+            int j = __ffs(mask) - 1;
+            mask &= mask - 1;
+            if (pos < max_out) {
+                out_ids[pos] = i0 + j;
+                if (flip) bitmap[i0 + j] = want ? 0 : 1;
+            }
+            ++pos;
+        }
+        carry += total;
+    }
+    if (threadIdx.x == 0) {
+        if (out_count) *out_count = carry < max_out ? carry : max_out;
+        if (out_total) *out_total = carry;
+    }
+}
+
+__global__ void bitmap_scatter_kernel(uint8_t *__restrict__ bitmap, int64_t bitmap_len,
+                                      const int64_t *__restrict__ ids, int64_t n, int value) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t id = ids[i];
+        if (id >= 0 && id < bitmap_len) bitmap[id] = (uint8_t)(value != 0);
+    }
+}
+
+__global__ void __launch_bounds__(kThreads) block_table_set_kernel(int32_t *__restrict__ num_allocated,
+                                                                 int32_t *__restrict__ block_table,
+                                                                 int64_t table_stride,
+                                                                 const int64_t *__restrict__ candidates,
+                                                                 const int32_t *__restrict__ seq_ids,
+                                                                 const int32_t *__restrict__ need, int batch) {
+    __shared__ int warp_sums[33];
+    int64_t carry = 0;
+    for (int base = 0; base < batch; base += kThreads) {
+        const int i = base + threadIdx.x;
+        int n = (i < batch) ? max(need[i], 0) : 0;
+        int total;
+        int off = block_exclusive_scan(n, total, warp_sums);
+        if (i < batch && n > 0) {
+            const int64_t s = seq_ids[i];
+            const int have = num_allocated[s];
+            int room = (int)min((int64_t)n, table_stride - have);  // never write past the row
+            for (int j = 0; j < room; ++j)
+                block_table[s * table_stride + have + j] = (int32_t)candidates[carry + off + j];
+            num_allocated[s] = have + n;
+        }
+        carry += total;
+    }
+}
+
+__global__ void __launch_bounds__(kThreads) block_table_unset_kernel(int32_t *__restrict__ num_allocated,
+                                                                   const int32_t *__restrict__ block_table,
+                                                                   int64_t table_stride,
+                                                                   const int32_t *__restrict__ seq_ids, int batch,
+                                                                   uint8_t *__restrict__ is_block_free,
+                                                                   int64_t num_blocks, int32_t *__restrict__ gathered,
+                                                                   int64_t gathered_capacity,
+                                                                   int64_t *__restrict__ total_out) {
+    __shared__ int warp_sums[33];
+    int64_t carry = 0;
+    for (int base = 0; base < batch; base += kThreads) {
+        const int i = base + threadIdx.x;
+        int64_t s = 0;
+        int n = 0;
+        if (i < batch) {
+            s = seq_ids[i];
+            n = num_allocated[s];
+        }
+        int total;
+        int off = block_exclusive_scan(n, total, warp_sums);
+        if (i < batch) {
+            for (int j = 0; j < n; ++j) {
+                int32_t id = block_table[s * table_stride + j];
+                if (gathered && carry + off + j < gathered_capacity) gathered[carry + off + j] = id;
+                if (id >= 0 && id < num_blocks) is_block_free[id] = 1;
+            }
+        }
+        carry += total;
+    }
+    __syncthreads();  // every count was read before any is cleared (duplicate ids in a batch)
+    for (int i = threadIdx.x; i < batch; i += blockDim.x) num_allocated[seq_ids[i]] = 0;
+    if (threadIdx.x == 0 && total_out) *total_out = carry;
+}
+
+__global__ void __launch_bounds__(kThreads) block_table_count_kernel(const int32_t *__restrict__ num_allocated,
+                                                                   const int32_t *__restrict__ seq_ids, int batch,
+                                                                   int64_t *__restrict__ total_out) {
+    __shared__ long long s_sum;
+    if (threadIdx.x == 0) s_sum = 0;
+    __syncthreads();
+    long long sum = 0;
+    for (int i = threadIdx.x; i < batch; i += blockDim.x) sum += num_allocated[seq_ids[i]];
+    for (int d = 16; d > 0; d >>= 1) sum += __shfl_down_sync(0xffffffffu, sum, d);
+    if ((threadIdx.x & 31) == 0) atomicAdd((unsigned long long *)&s_sum, (unsigned long long)sum);
+    __syncthreads();
+    if (threadIdx.x == 0) *total_out = s_sum;
+}
+
+}  // namespace mkv
+
+using namespace mkv;
+
+extern "C" {
+
+int mkv_block_need(int device, void *stream, const int32_t *num_allocated, const int32_t *seq_ids,
+                   const int32_t *target_lens, int batch, int block_size, int32_t *need, int64_t *totals) {
+    if (batch < 0 || block_size < 1) return MKV_ERR_SHAPE;
+    if (!totals) return MKV_ERR_NULL;
+    if (batch > 0 && (!num_allocated || !seq_ids || !target_lens || !need)) return MKV_ERR_NULL;
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
+    block_need_kernel<<<1, kThreads, 0, (cudaStream_t)stream>>>(num_allocated, seq_ids, target_lens, batch,
+                                                               block_size, need, totals);
+    MKV_LAUNCH_CHECK();
+    return MKV_OK;
+}
+
+int mkv_bitmap_select(int device, void *stream, uint8_t *bitmap, int64_t lo, int64_t hi, int want,
+                      int64_t max_out, int flip, int64_t *out_ids, int64_t *out_count, int64_t *out_total) {
+    if (lo < 0 || hi < lo || max_out < 0) return MKV_ERR_SHAPE;
+    if (!bitmap && hi > lo) return MKV_ERR_NULL;
+    if (max_out > 0 && !out_ids) return MKV_ERR_NULL;
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
+    bitmap_select_kernel<<<1, kThreads, 0, (cudaStream_t)stream>>>(bitmap, lo, hi, want, max_out, flip, out_ids,
+                                                                  out_count, out_total);
+    MKV_LAUNCH_CHECK();
+    return MKV_OK;
+}
+
+int mkv_bitmap_scatter(int device, void *stream, uint8_t *bitmap, int64_t bitmap_len, const int64_t *ids,
+                       int64_t n, int value) {
+    if (n < 0 || bitmap_len < 0) return MKV_ERR_SHAPE;
+    if (n == 0) return MKV_OK;
+    if (!bitmap || !ids) return MKV_ERR_NULL;
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
+    int blocks = (int)(ceil_div64(n, 256) > 1024 ? 1024 : ceil_div64(n, 256));
+    bitmap_scatter_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(bitmap, bitmap_len, ids, n, value);
+    MKV_LAUNCH_CHECK();
+    return MKV_OK;
+}
+
+int mkv_block_table_set(int device, void *stream, int32_t *num_allocated, int32_t *block_table,
+                        int64_t table_stride, const int64_t *candidates, const int32_t *seq_ids,
+                        const int32_t *need, int batch) {
+    if (batch < 0 || table_stride < 1) return MKV_ERR_SHAPE;
+    if (batch == 0) return MKV_OK;
+    if (!num_allocated || !block_table || !candidates || !seq_ids || !need) return MKV_ERR_NULL;
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
+    block_table_set_kernel<<<1, kThreads, 0, (cudaStream_t)stream>>>(num_allocated, block_table, table_stride,
+                                                                    candidates, seq_ids, need, batch);
+    MKV_LAUNCH_CHECK();
+    return MKV_OK;
+}
+
+int mkv_block_table_unset(int device, void *stream, int32_t *num_allocated, const int32_t *block_table,
+                          int64_t table_stride, const int32_t *seq_ids, int batch, uint8_t *is_block_free,
+                          int64_t num_blocks, int32_t *gathered, int64_t gathered_capacity, int64_t *total_out) {
+    if (batch < 0 || table_stride < 1 || num_blocks < 0 || gathered_capacity < 0) return MKV_ERR_SHAPE;
+    if (batch == 0) return MKV_OK;
+    if (!num_allocated || !block_table || !seq_ids || !is_block_free) return MKV_ERR_NULL;
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
+    block_table_unset_kernel<<<1, kThreads, 0, (cudaStream_t)stream>>>(num_allocated, block_table, table_stride,
+                                                                      seq_ids, batch, is_block_free, num_blocks,
+                                                                      gathered, gathered_capacity, total_out);
+    MKV_LAUNCH_CHECK();
+    return MKV_OK;
+}
+
+int mkv_block_table_count(int device, void *stream, const int32_t *num_allocated, const int32_t *seq_ids,
+                          int batch, int64_t *total_out) {
+    if (batch < 0) return MKV_ERR_SHAPE;
+    if (!total_out) return MKV_ERR_NULL;
+    if (batch > 0 && (!num_allocated || !seq_ids)) return MKV_ERR_NULL;
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
+    block_table_count_kernel<<<1, kThreads, 0, (cudaStream_t)stream>>>(num_allocated, seq_ids, batch, total_out);
+    MKV_LAUNCH_CHECK();
+    return MKV_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,121 @@
+// Elastic pool resize, device side: whole-block copies for compaction and the
+// block-table remap that follows.  HBM-bound streaming copy; no arithmetic.
+#include "common.cuh"
+
+namespace mkv {
+
+constexpr int kCopyThreads = 256;
+constexpr int kVecPerThread = 8;                                   // 8 x 16 B in flight per thread
+constexpr int kSliceBytes = kCopyThreads * kVecPerThread * 16;     // 32 KiB per thread block
+
+// Work item = (pair, K|V, slice).  grid-stride over items; each thread issues
+// all its loads before its stores so that 128 B per thread are in flight.
+__global__ void __launch_bounds__(kCopyThreads) copy_blocks_kernel(const __grid_constant__ PoolView pool, const int64_t *__restrict__ src_ids,
+                                                                  const int64_t *__restrict__ dst_ids, int64_t n,
+                                                                  int slices_per_block) {
+    const int64_t items = n * 2 * slices_per_block;
+    const int64_t vec_per_block = pool.block_bytes / 16;
+    for (int64_t item = blockIdx.x; item < items; item += gridDim.x) {
+        const int64_t pair = item / (2 * slices_per_block);
+        const int rem = (int)(item - pair * 2 * slices_per_block);
+        const int which = rem / slices_per_block;
+        const int slice = rem - which * slices_per_block;
+        const int64_t s = src_ids[pair], d = dst_ids[pair];
+        if (!block_in_pool(pool, s) || !block_in_pool(pool, d)) continue;
+        int sseg, dseg;
+        int64_t srow, drow;
+        locate_block(pool, s, sseg, srow);
+        locate_block(pool, d, dseg, drow);
+        const uint4 *sp = reinterpret_cast<const uint4 *>((which ? pool.v_base[sseg] : pool.k_base[sseg]) +
+                                                          srow * pool.block_bytes);
+        uint4 *dp = reinterpret_cast<uint4 *>((which ? pool.v_base[dseg] : pool.k_base[dseg]) + drow * pool.block_bytes);
+        const int64_t v0 = (int64_t)slice * (kSliceBytes / 16) + threadIdx.x;
+        uint4 r[kVecPerThread];
+#pragma unroll
+        for (int j = 0; j < kVecPerThread; ++j) {
+            int64_t vi = v0 + (int64_t)j * kCopyThreads;
+            if (vi < vec_per_block) r[j] = __ldcs(sp + vi);
+        }
+#pragma unroll
+        for (int j = 0; j < kVecPerThread; ++j) {
+            int64_t vi = v0 + (int64_t)j * kCopyThreads;
+            if (vi < vec_per_block) __stcs(dp + vi, r[j]);
+        }
+    }
+}
+
+// One warp per table row; lanes stride over the live columns.  An entry is
+// looked up in the ascending src list by binary search.
+__global__ void remap_block_table_kernel(int32_t *__restrict__ block_table, int64_t table_stride, int64_t num_rows,
+                                         const int32_t *__restrict__ num_allocated,
+                                         const int64_t *__restrict__ src_ids, const int64_t *__restrict__ dst_ids,
+                                         int64_t n) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int64_t lowest = src_ids[0];
+    for (int64_t r = warp; r < num_rows; r += nwarps) {
+        int64_t c = num_allocated[r];
+        if (c > table_stride) c = table_stride;
+        for (int64_t j = lane; j < c; j += 32) {
+            const int64_t e = block_table[r * table_stride + j];
+            if (e < lowest) continue;
+            int64_t lo = 0, hi = n;
+            while (lo < hi) {
+                int64_t mid = (lo + hi) >> 1;
+                if (src_ids[mid] < e) lo = mid + 1;
+                else hi = mid;
+            }
+            if (lo < n && src_ids[lo] == e) block_table[r * table_stride + j] = (int32_t)dst_ids[lo];
+        }
+    }
+}
+
+}  // namespace mkv
+
+using namespace mkv;
+
+extern "C" {
+
+int mkv_copy_blocks(int device, void *stream, const mkv_pool *pool, const int64_t *src_ids,
+                    const int64_t *dst_ids, int64_t n) {
+    PoolView pv;
+    int st = validate_pool(pool, &pv);
+    if (st) return st;
+    if (n < 0) return MKV_ERR_SHAPE;
+    if (n == 0) return MKV_OK;
+    if (!src_ids || !dst_ids) return MKV_ERR_NULL;
+    if (pv.block_bytes % 16 != 0) return MKV_ERR_ALIGN;
+    for (int i = 0; i < pv.num_segments; ++i)
+        if ((((uintptr_t)pv.k_base[i]) | ((uintptr_t)pv.v_base[i])) % 16 != 0) return MKV_ERR_ALIGN;
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
+    int sms = 148;
+    mkv_sm_count(device, &sms);
+    const int slices = (int)ceil_div64(pv.block_bytes, kSliceBytes);
+    const int64_t items = n * 2 * slices;
+    int64_t grid = (int64_t)sms * 8;  // 8 x 256 threads resident per SM
+    if (grid > items) grid = items;
+    copy_blocks_kernel<<<(unsigned)grid, kCopyThreads, 0, (cudaStream_t)stream>>>(pv, src_ids, dst_ids, n, slices);
+    MKV_LAUNCH_CHECK();
+    return MKV_OK;
+}
+
+int mkv_remap_block_table(int device, void *stream, int32_t *block_table, int64_t table_stride,
+                          int64_t num_rows, const int32_t *num_allocated, const int64_t *src_ids,
+                          const int64_t *dst_ids, int64_t n) {
+    if (n < 0 || num_rows < 0 || table_stride < 1) return MKV_ERR_SHAPE;
+    if (n == 0 || num_rows == 0) return MKV_OK;
+    if (!block_table || !num_allocated || !src_ids || !dst_ids) return MKV_ERR_NULL;
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
+    const int threads = 256;
+    int64_t grid = ceil_div64(num_rows, threads / 32);
+    if (grid > 148 * 8) grid = 148 * 8;
+    remap_block_table_kernel<<<(unsigned)grid, threads, 0, (cudaStream_t)stream>>>(
+        block_table, table_stride, num_rows, num_allocated, src_ids, dst_ids, n);
+    MKV_LAUNCH_CHECK();
+    return MKV_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,155 @@
+"""Elastic KV-pool resize: the KV half of the reference's
+``server/memory_utils.py`` - expand (:370-420), the release rule (:529-544,
+:602-613, :644-651) - plus compaction, which the reference does not have.
+
+Functions take the reference's ``engine`` object duck-typed: they touch
+``engine.model.{k_cache,v_cache,k_cache_new,v_cache_new,kv_cache_new_block_size,
+gpu_block_manager}`` and ``engine.scheduler.num_gpu_blocks`` only.  Swapping the
+transformer layer's weights (the other half of org2quant / quant2org) is not
+part of the KV path and stays with the caller.
+
+Compaction rule (defined here; the reference can only release a chunk that is
+already empty, :529-544,:622-624).  Given a target size T in blocks:
+  src = ascending ids >= T that are in use,
+  dst = the first len(src) ascending free ids < T (first-fit, like allocation),
+  fail, changing nothing, if there are too few;
+  copy K and V of block src[i] to dst[i] (all layers);
+  in every row r of the block table, entries [0, num_seq_allocated_blocks[r])
+  equal to src[i] become dst[i]; other columns and rows of freed sequences keep
+  whatever they held; is_block_free[dst] = False, is_block_free[src] = True;
+  num_free_blocks is unchanged and the source blocks keep their bytes.
+"""
+from __future__ import annotations
+
+import torch
+
+from .._lib import check, lib
+from ..worker.kernels._common import device_and_stream, make_pool
+
+
+def update_kvcache_after_replacing_layer(engine, layer_id, acquire=None):
+    """Attach the chunk freed by quantising ``layer_id`` to the pool.
+    server/memory_utils.py:370-420.  ``acquire`` defaults to
+    ``swiftllm_c.acquire_new_kvcache``."""
+    if acquire is None:
+        from ..swiftllm_c import acquire_new_kvcache as acquire
+    k_cache_new, v_cache_new = acquire(layer_id)
+    return attach_kvcache_chunk(engine, k_cache_new, v_cache_new)
+
+
+def attach_kvcache_chunk(engine, k_cache_new: torch.Tensor, v_cache_new: torch.Tensor) -> int:
+    """Bookkeeping of an expand (server/memory_utils.py:389-420)."""
+    model = engine.model
+    bm = model.gpu_block_manager
+    n = len(k_cache_new)
+    if model.k_cache_new and n != model.kv_cache_new_block_size:
+        raise RuntimeError("elastic KV chunks must all have the same number of blocks")
+    model.k_cache_new.append(k_cache_new)
+    model.v_cache_new.append(v_cache_new)
+    bm.num_blocks += n
+    bm.num_free_blocks += n
+    model.kv_cache_new_block_size = k_cache_new.shape[0]
+    is_block_free_new = torch.ones((n,), dtype=torch.bool, device=bm.is_block_free.device)
+    bm.is_block_free = torch.cat((bm.is_block_free, is_block_free_new), dim=0)
+    if getattr(engine, "scheduler", None) is not None:
+        engine.scheduler.num_gpu_blocks += n
+    return n
+
+
+def if_kv_cache_unused(engine, layer_id=None) -> bool:
+    """True when the LAST chunk holds no live block (server/memory_utils.py:529-544)."""
+    model = engine.model
+    kv_cache_index = len(model.k_cache_new) - 1
+    assert kv_cache_index >= 0, f"[Engine] Layer {layer_id} is not quantized, no KV cache tensors to free"
+    n = model.kv_cache_new_block_size
+    start = model.gpu_block_manager.num_blocks_org + n * kv_cache_index
+    return bool(model.gpu_block_manager.is_block_free[start:start + n].all())
+
+
+def free_kv_cache_tensors(engine, layer_id=None) -> None:
+    """Drop the last chunk's tensors (server/memory_utils.py:602-613)."""
+    model = engine.model
+    kv_cache_index = len(model.k_cache_new) - 1
+    assert kv_cache_index >= 0, f"[Engine] Layer {layer_id} is not quantized, no KV cache tensors to free"
+    del model.k_cache_new[kv_cache_index]
+    del model.v_cache_new[kv_cache_index]
+
+
+def release_last_kvcache_chunk(engine, layer_id=None) -> bool:
+    """The KV half of quant2org_and_update_kvcache (server/memory_utils.py:617-662):
+    refuse (return False) unless the last chunk is empty, else drop its tensors and
+    shrink the counters and the free bitmap."""
+    if not if_kv_cache_unused(engine, layer_id):
+        return False
+    model = engine.model
+    bm = model.gpu_block_manager
+    n = model.kv_cache_new_block_size
+    free_kv_cache_tensors(engine, layer_id)
+    bm.num_blocks -= n
+    bm.num_free_blocks -= n
+    bm.is_block_free = bm.is_block_free[:-n]
+    if getattr(engine, "scheduler", None) is not None:
+        engine.scheduler.num_gpu_blocks -= n
+    return True
+
+
+def compact_kvcache(engine, target_num_blocks: int) -> int:
+    """Move every live block with id >= ``target_num_blocks`` below it and remap the
+    block table (rule in the module docstring).  Returns the number of blocks
+    moved, or -1 - with nothing changed - when the low region has too few free
+    blocks.  One host synchronisation (the move count sizes the launches)."""
+    model = engine.model
+    bm = model.gpu_block_manager
+    free = bm.is_block_free
+    total = free.shape[0]
+    T = int(target_num_blocks)
+    if not 0 <= T <= total:
+        raise RuntimeError(f"compaction target {T} outside the pool of {total} blocks")
+    dev, stream = device_and_stream(free)
+    device = free.device
+    n_hi = total - T
+    src = torch.empty((max(n_hi, 1),), dtype=torch.int64, device=device)
+    counts = torch.empty((4,), dtype=torch.int64, device=device)
+    # live ids >= T, ascending
+    check(lib.mkv_bitmap_select(dev, stream, free.data_ptr(), T, total, 0, n_hi, 0, src.data_ptr(),
+                                counts[0:].data_ptr(), counts[1:].data_ptr()), "mkv_bitmap_select")
+    # how many free ids < T exist (count only)
+    check(lib.mkv_bitmap_select(dev, stream, free.data_ptr(), 0, T, 1, 0, 0, None,
+                                counts[2:].data_ptr(), counts[3:].data_ptr()), "mkv_bitmap_select")
+    n_src, _, _, n_free_lo = counts.tolist()
+    if n_src == 0:
+        return 0
+    if n_free_lo < n_src:
+        return -1
+    dst = torch.empty((n_src,), dtype=torch.int64, device=device)
+    # first n_src free ids < T, ascending; mark them used
+    check(lib.mkv_bitmap_select(dev, stream, free.data_ptr(), 0, T, 1, n_src, 1, dst.data_ptr(), None, None),
+          "mkv_bitmap_select")
+    pool = make_pool(model.k_cache, model.v_cache, model.k_cache_new, model.v_cache_new,
+                     bm.num_blocks_org, model.kv_cache_new_block_size)
+    check(lib.mkv_copy_blocks(dev, stream, pool, src.data_ptr(), dst.data_ptr(), n_src), "mkv_copy_blocks")
+    check(lib.mkv_remap_block_table(dev, stream, bm.block_table.data_ptr(), bm.block_table.stride(0),
+                                    bm.block_table.shape[0], bm.num_seq_allocated_blocks.data_ptr(),
+                                    src.data_ptr(), dst.data_ptr(), n_src), "mkv_remap_block_table")
+    check(lib.mkv_bitmap_scatter(dev, stream, free.data_ptr(), total, src.data_ptr(), n_src, 1),
+          "mkv_bitmap_scatter")
+    return n_src
+
+
+def shrink_kvcache(engine, num_chunks_to_release: int) -> int:
+    """Compact to the boundary below the last ``num_chunks_to_release`` chunks, then
+    release them one by one with the reference's rule.  Returns chunks released."""
+    model = engine.model
+    bm = model.gpu_block_manager
+    k = min(int(num_chunks_to_release), len(model.k_cache_new))
+    if k <= 0:
+        return 0
+    target = bm.num_blocks_org + (len(model.k_cache_new) - k) * model.kv_cache_new_block_size
+    if compact_kvcache(engine, target) < 0:
+        return 0
+    released = 0
+    for _ in range(k):
+        if not release_last_kvcache_chunk(engine):
+            break
+        released += 1
+    return released

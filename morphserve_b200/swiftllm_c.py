@@ -1,0 +1,123 @@
+"""Stand-in for the reference's native extension module ``swiftllm_c``
+(csrc/src/entrypoints.cpp:6-33) for the KV path: block swap and elastic chunk
+carving.  Same function names and argument order; the work is done by
+``libmorphkv.so`` through its C ABI.
+
+Layer replacement (``replace_layer_*``, ``register_layer_memory_tensor_map_*``)
+is weight swapping, not the KV path, and is not provided here.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from ._lib import MKV_MAX_SEGMENTS, MkvPool, MorphKVError, check, lib
+from .worker.kernels._common import device_and_stream, make_pool
+
+_state = {"kv_info": None, "org_gpu": {}, "quant": {}}
+
+
+def _ids(xs):
+    n = len(xs)
+    return (C.c_int64 * n)(*[int(x) for x in xs]), n
+
+
+def _swap(src, dst, is_swap_in, pool, k_cache, k_swap, v_swap):
+    if len(src) != len(dst):
+        raise RuntimeError("source_block_ids and target_block_ids differ in length")
+    if k_swap.is_cuda or v_swap.is_cuda:
+        raise RuntimeError("k_swap / v_swap must be host tensors")
+    dev, stream = device_and_stream(k_cache)
+    s, n = _ids(src)
+    d, _ = _ids(dst)
+    check(lib.mkv_swap_blocks(dev, stream, pool, k_swap.data_ptr(), v_swap.data_ptr(), k_swap.shape[0],
+                              s, d, n, 1 if is_swap_in else 0, None), "mkv_swap_blocks")
+
+
+def swap_blocks(source_block_ids, target_block_ids, is_swap_in, k_cache, v_cache, k_swap, v_swap):
+    """csrc/src/block_swapping.cpp:22-85.  Asynchronous on the current stream."""
+    pool = make_pool(k_cache, v_cache, [], [], k_cache.shape[0], 0)
+    _swap(source_block_ids, target_block_ids, is_swap_in, pool, k_cache, k_swap, v_swap)
+
+
+def swap_blocks_new_kv_combined(source_block_ids, target_block_ids, is_swap_in, num_blocks_org,
+                                org_layer_param_size, kv_cache_new_block_size, k_cache_element_size,
+                                k_cache, v_cache, k_swap, v_swap, k_cache_new, v_cache_new):
+    """csrc/src/block_swapping.cpp:88-202.  Only chunk 0 is passed in; chunk j is
+    taken to sit ``j * org_layer_param_size`` elements below it, the layout the
+    reference's allocator produces (:159-160).  The device address always comes
+    from the device-side id (the reference uses the source id on swap-in, :156-161)."""
+    dev_ids = target_block_ids if is_swap_in else source_block_ids
+    top = max([int(x) for x in dev_ids], default=0)
+    n_chunks = 1 + max(0, (top - num_blocks_org) // kv_cache_new_block_size) if top >= num_blocks_org else 1
+    if n_chunks + 1 > MKV_MAX_SEGMENTS:
+        raise RuntimeError("block id beyond the supported number of elastic chunks")
+    pool = MkvPool()
+    pool.num_segments = 1 + n_chunks
+    pool.elem_bytes = int(k_cache_element_size)
+    _, pool.num_layers, pool.num_kv_heads, pool.block_size, pool.head_dim = k_cache.shape
+    pool.num_blocks_org = int(num_blocks_org)
+    pool.chunk_blocks = int(kv_cache_new_block_size)
+    pool.k_base[0] = k_cache.data_ptr()
+    pool.v_base[0] = v_cache.data_ptr()
+    step = int(org_layer_param_size) * int(k_cache_element_size)
+    for j in range(n_chunks):
+        pool.k_base[1 + j] = k_cache_new.data_ptr() - j * step
+        pool.v_base[1 + j] = v_cache_new.data_ptr() - j * step
+    _swap(source_block_ids, target_block_ids, is_swap_in, pool, k_cache, k_swap, v_swap)
+
+
+def register_kv_cache_info(num_layers: int, num_kv_heads: int, block_size: int, head_dim: int) -> None:
+    """csrc/src/memory_manager.cpp:57-66."""
+    _state["kv_info"] = (int(num_layers), int(num_kv_heads), int(block_size), int(head_dim))
+
+
+def register_layer_memory_org_gpu(layer_id: int, start_addr: int, size: int) -> None:
+    """csrc/src/memory_manager.cpp:16-21: the fp16 layer's slab on the GPU."""
+    _state["org_gpu"][int(layer_id)] = (int(start_addr), int(size))
+
+
+def register_layer_memory_quant(layer_id: int, start_addr: int, size: int) -> None:
+    """csrc/src/memory_manager.cpp:30-35: only the size of the quantised layer is used here."""
+    _state["quant"][int(layer_id)] = (int(start_addr), int(size))
+
+
+class _RawCudaMemory:
+    """Non-owning view of device memory for torch.as_tensor."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False),
+                                         "version": 2, "strides": None}
+
+
+def acquire_new_kvcache(layer_id: int):
+    """K and V tensors ``[n, L, Hkv, bs, D]`` fp16 carved out of the part of layer
+    ``layer_id``'s slab that the quantised layer does not cover, zero-filled.
+    csrc/src/memory_manager.cpp:69-176.  The tensors do not own the memory."""
+    layer_id = int(layer_id)
+    if layer_id not in _state["org_gpu"] or layer_id not in _state["quant"]:
+        raise RuntimeError("Layer not found in memory maps")
+    if _state["kv_info"] is None:
+        raise RuntimeError("KV cache info not registered")
+    L, hkv, bs, d = _state["kv_info"]
+    org_start, org_size = _state["org_gpu"][layer_id]
+    _, quant_size = _state["quant"][layer_id]
+    k_addr, v_addr, n = C.c_uint64(0), C.c_uint64(0), C.c_int64(0)
+    st = lib.mkv_chunk_layout(org_start, org_size, quant_size, L, hkv, bs, d, 2,
+                              C.byref(k_addr), C.byref(v_addr), C.byref(n))
+    if st == -7:
+        raise RuntimeError("No space available for new KV cache blocks")
+    check(st, "mkv_chunk_layout")
+    shape = (n.value, L, hkv, bs, d)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    k = torch.as_tensor(_RawCudaMemory(k_addr.value, shape, "<f2"), device=dev)
+    v = torch.as_tensor(_RawCudaMemory(v_addr.value, shape, "<f2"), device=dev)
+    k.zero_()
+    v.zero_()
+    return k, v
+
+
+__all__ = ["swap_blocks", "swap_blocks_new_kv_combined", "register_kv_cache_info",
+           "register_layer_memory_org_gpu", "register_layer_memory_quant", "acquire_new_kvcache",
+           "MorphKVError"]

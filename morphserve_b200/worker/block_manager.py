@@ -1,0 +1,137 @@
+"""GPU-resident block table and free-block bitmap: drop-in for the reference's
+``swiftllm.worker.block_manager.BlockManager`` (worker/block_manager.py:5-137).
+
+Same constructor, methods, exceptions and public mutable attributes
+(``num_blocks``, ``num_free_blocks``, ``num_blocks_org``, ``block_size``,
+``num_seq_allocated_blocks``, ``block_table``, ``is_block_free`` - the elastic
+resize code replaces ``is_block_free`` and bumps the counters from outside).
+Allocation is first-fit in ascending block id like the reference's
+``torch.nonzero(is_block_free)[:n]`` (:75), done by one CUDA kernel without the
+nonzero pass; an allocate costs one host synchronisation (the size of the
+returned tensor is data dependent) instead of the reference's three.
+"""
+from __future__ import annotations
+
+import torch
+
+from .._lib import check, lib
+from .kernels._common import device_and_stream
+from .kernels.block_mgmt import (gather_allocated_blocks_and_unset,
+                                 set_block_table_and_num_seq_alloc_blocks)
+
+
+class BlockCount(int):
+    """An int that also answers ``.item()``: the reference's ``num_free_blocks``
+    turns into a 0-d tensor after the first free (worker/block_manager.py:118)
+    and its callers read it with ``.item()`` (server/engine.py:239,247)."""
+
+    def item(self) -> int:
+        return int(self)
+
+    def __add__(self, other):
+        return BlockCount(int(self) + int(other))
+
+    __radd__ = __add__
+
+    def __sub__(self, other):
+        return BlockCount(int(self) - int(other))
+
+    def __rsub__(self, other):
+        return BlockCount(int(other) - int(self))
+
+
+def _as_i32(t: torch.Tensor) -> torch.Tensor:
+    if t.dtype != torch.int32:
+        t = t.to(torch.int32)
+    return t.contiguous()
+
+
+class BlockManager:
+    def __init__(self, device_name: str, num_blocks: int, max_seqs_in_block_table: int,
+                 max_blocks_per_seq: int, block_size: int):
+        if not torch.cuda.is_available():
+            raise RuntimeError("BlockManager keeps its tables on the GPU; no CUDA device is available")
+        self.device_name = device_name
+        self.num_free_blocks = BlockCount(num_blocks)
+        self.num_blocks = num_blocks
+        self.block_size = block_size
+
+        self.num_free_blocks_org = num_blocks
+        self.num_blocks_org = num_blocks
+
+        # seq_id |-> number of blocks allocated for this sequence
+        self.num_seq_allocated_blocks = torch.zeros((max_seqs_in_block_table,), dtype=torch.int32, device="cuda")
+        # (seq_id, block_index) |-> block_id; -1 where never assigned
+        self.block_table = torch.full((max_seqs_in_block_table, max_blocks_per_seq), -1,
+                                      dtype=torch.int32, device="cuda")
+        # block_id |-> free?
+        self.is_block_free = torch.ones((num_blocks,), dtype=torch.bool, device="cuda")
+
+    def get_num_used_blocks(self) -> int:
+        return self.num_blocks - self.num_free_blocks
+
+    def _allocate_blocks(self, num_blocks: int) -> torch.Tensor:
+        """First ``num_blocks`` free ids in ascending order; marks them used."""
+        num_blocks = int(num_blocks)
+        if num_blocks > self.num_free_blocks:
+            raise RuntimeError(f"No enough free blocks available on {self.device_name} ({self.num_blocks} in total, "
+                               f"{self.num_free_blocks} free, {num_blocks} requested)")
+        free = self.is_block_free
+        dev, stream = device_and_stream(free)
+        selected = torch.empty((num_blocks,), dtype=torch.int64, device=free.device)
+        check(lib.mkv_bitmap_select(dev, stream, free.data_ptr(), 0, free.shape[0], 1, num_blocks, 1,
+                                    selected.data_ptr(), None, None), "mkv_bitmap_select")
+        self.num_free_blocks = BlockCount(self.num_free_blocks - num_blocks)
+        return selected
+
+    def _free_blocks(self, block_ids: torch.Tensor):
+        self.num_free_blocks = BlockCount(self.num_free_blocks + len(block_ids))
+        free = self.is_block_free
+        dev, stream = device_and_stream(free)
+        ids = block_ids.to(torch.int64).contiguous()
+        check(lib.mkv_bitmap_scatter(dev, stream, free.data_ptr(), free.shape[0], ids.data_ptr(), ids.shape[0], 1),
+              "mkv_bitmap_scatter")
+
+    def allocate_blocks_for_seqs(self, seq_ids: torch.Tensor, target_lens: torch.Tensor) -> torch.Tensor:
+        """Make sure sequence i owns ceil(target_lens[i] / block_size) blocks.
+        Returns the newly allocated ids (int64), assigned in batch order."""
+        seq_ids = _as_i32(seq_ids)
+        target_lens = _as_i32(target_lens)
+        batch = seq_ids.shape[0]
+        dev, stream = device_and_stream(self.block_table)
+        need = torch.empty((batch,), dtype=torch.int32, device=self.block_table.device)
+        totals = torch.empty((2,), dtype=torch.int64, device=self.block_table.device)
+        check(lib.mkv_block_need(dev, stream, self.num_seq_allocated_blocks.data_ptr(), seq_ids.data_ptr(),
+                                 target_lens.data_ptr(), batch, self.block_size, need.data_ptr(),
+                                 totals.data_ptr()), "mkv_block_need")
+        n_needed, n_negative = totals.tolist()
+        assert n_negative == 0, \
+            f"""(On {self.device_name}) Logic error: Some sequences have more blocks already allocated than needed.
+                seq_ids: {seq_ids}, target_lens: {target_lens}, block_needed: {need}"""
+        if n_needed == 0:
+            return torch.empty(0, device=self.block_table.device, dtype=torch.int64)
+        new_blocks = self._allocate_blocks(n_needed)
+        set_block_table_and_num_seq_alloc_blocks(self.num_seq_allocated_blocks, self.block_table, new_blocks,
+                                                 seq_ids, need)
+        return new_blocks
+
+    def free_blocks_for_seqs(self, seq_ids: torch.Tensor):
+        seq_ids = _as_i32(seq_ids)
+        dev, stream = device_and_stream(self.block_table)
+        total = torch.empty((1,), dtype=torch.int64, device=self.block_table.device)
+        check(lib.mkv_block_table_unset(dev, stream, self.num_seq_allocated_blocks.data_ptr(),
+                                        self.block_table.data_ptr(), self.block_table.stride(0),
+                                        seq_ids.data_ptr(), seq_ids.shape[0], self.is_block_free.data_ptr(),
+                                        self.is_block_free.shape[0], None, 0, total.data_ptr()),
+              "mkv_block_table_unset")
+        self.num_free_blocks = BlockCount(self.num_free_blocks + int(total.item()))
+
+    def gather_allocated_blocks_and_free(self, seq_ids: torch.Tensor) -> torch.Tensor:
+        """Ids (int32, batch order) of the blocks of the given sequences; frees them.  Used by swapping."""
+        gathered = gather_allocated_blocks_and_unset(self.num_seq_allocated_blocks, self.block_table,
+                                                     _as_i32(seq_ids), self.is_block_free)
+        self.num_free_blocks = BlockCount(self.num_free_blocks + len(gathered))
+        return gathered
+
+    def get_num_allocated_blocks(self, seq_ids: torch.Tensor) -> torch.Tensor:
+        return self.num_seq_allocated_blocks[seq_ids]

@@ -1,0 +1,58 @@
+"""KV append / scatter: drop-in for the reference's
+``swiftllm.worker.kernels.kvcache_mgmt.store_kvcache``
+(worker/kernels/kvcache_mgmt.py:298-478), same signature, in place.
+
+Prefill tokens ``[0, num_prefill_tokens)`` are scattered block by block, decode
+tokens after them are appended at position ``len-1``.  Both are byte copies, so
+results are bit-identical to the reference's.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..._lib import check, lib
+from ._common import device_and_stream, make_pool, require_cuda
+
+
+def store_kvcache(
+    k: torch.Tensor,            # [num_tokens, num_kv_heads, head_dim]
+    v: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    k_cache_new: list,
+    v_cache_new: list,
+    block_table: torch.Tensor,
+    model_config,
+    engine_config,
+    infer_state,
+    cur_layer: int,
+):
+    assert k.is_contiguous()
+    assert v.is_contiguous()
+    assert k_cache.is_contiguous()
+    assert v_cache.is_contiguous()
+    assert block_table.is_contiguous()
+    assert infer_state.seq_ids.is_contiguous()
+    assert infer_state.decoding_seq_lens.is_contiguous()
+    require_cuda(k, "k")
+
+    dev, stream = device_and_stream(k)
+    pool = make_pool(k_cache, v_cache, k_cache_new, v_cache_new,
+                     infer_state.num_blocks_org, infer_state.kv_cache_new_block_size)
+    stride = block_table.stride(0)
+    n_pre = infer_state.num_prefill_seqs
+    if n_pre > 0:
+        check(lib.mkv_store_kv_prefill(
+            dev, stream, k.data_ptr(), v.data_ptr(), pool, block_table.data_ptr(), stride,
+            infer_state.seq_ids.data_ptr(), infer_state.prefill_seq_start_locs.data_ptr(),
+            infer_state.prefill_seq_lens.data_ptr(), n_pre, int(infer_state.max_prefill_len), cur_layer),
+            "mkv_store_kv_prefill")
+    n_dec = infer_state.num_decoding_seqs
+    if n_dec > 0:
+        row = k.stride(0) * k.element_size()
+        off = infer_state.num_prefill_tokens * row
+        seq_ids = infer_state.seq_ids[n_pre:]
+        check(lib.mkv_store_kv_decode(
+            dev, stream, k.data_ptr() + off, v.data_ptr() + off, pool, block_table.data_ptr(), stride,
+            seq_ids.data_ptr(), infer_state.decoding_seq_lens.data_ptr(), n_dec, cur_layer),
+            "mkv_store_kv_decode")

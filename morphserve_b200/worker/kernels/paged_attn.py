@@ -1,0 +1,75 @@
+"""Decode paged attention: drop-in for the reference's
+``swiftllm.worker.kernels.paged_attn.paged_attention``
+(worker/kernels/paged_attn.py:700-1015), same signature, writes ``o`` in place.
+
+What changes underneath: the two Triton phases become one sm_100a kernel that
+packs the query heads of a GQA group on one K/V stream (each tile read once per
+KV head), schedules (sequence, chunk) work items longest-first from a plan made
+once per decode step, and merges split sequences in the same launch.  There is
+no allocation, no host synchronisation and no full-table scan per call (the
+reference does ``(block_table >= num_blocks_org).any()`` per layer when elastic
+chunks exist, :893-895); elastic blocks are resolved in the kernel.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..._lib import check, lib
+from ._common import attn_workspace, device_and_stream, make_pool, require_cuda
+
+
+def _plan_for(infer_state, ws, dev, stream, lens, batch, hq, hkv, d, bs, max_blocks):
+    token = (ws.generation, dev, batch, max_blocks, lens.data_ptr())
+    state = getattr(infer_state, "__dict__", None)
+    if state is not None and state.get("_mkv_plan_token") == token:
+        return
+    ws.generation += 1
+    token = (ws.generation,) + token[1:]
+    check(lib.mkv_attn_plan(dev, stream, ws.tensor.data_ptr(), ws.nbytes, lens.data_ptr(), batch, hq, hkv, d, bs,
+                            max_blocks), "mkv_attn_plan")
+    if state is not None:
+        state["_mkv_plan_token"] = token
+
+
+def paged_attention(
+    q: torch.Tensor,                # [num_decoding_seqs, num_q_heads, head_dim]
+    k_cache: torch.Tensor,          # [num_blocks, num_layers, num_kv_heads, block_size, head_dim]
+    v_cache: torch.Tensor,
+    k_cache_new: list,              # elastic chunks, each [chunk_blocks, num_layers, num_kv_heads, block_size, head_dim]
+    v_cache_new: list,
+    block_table: torch.Tensor,      # [max_seqs_in_block_table, max_blocks_per_seq] int32
+    model_config,
+    engine_config,
+    infer_state,
+    cur_layer: int,
+    o: torch.Tensor,                # [num_decoding_seqs, num_q_heads(*)head_dim]
+):
+    assert q.is_contiguous()
+    assert k_cache.is_contiguous()
+    assert v_cache.is_contiguous()
+    assert block_table.is_contiguous()
+    assert infer_state.seq_block_size % engine_config.block_size == 0
+    assert o.is_contiguous()
+    require_cuda(q, "q")
+
+    batch = infer_state.num_decoding_seqs
+    if batch == 0:
+        return
+    dev, stream = device_and_stream(q)
+    hq, hkv, d = model_config.num_q_heads, model_config.num_kv_heads, model_config.head_dim
+    bs = engine_config.block_size
+    pool = make_pool(k_cache, v_cache, k_cache_new, v_cache_new,
+                     infer_state.num_blocks_org, infer_state.kv_cache_new_block_size)
+    lens = infer_state.decoding_seq_lens
+    seq_ids = infer_state.seq_ids[infer_state.num_prefill_seqs:]
+    max_len = getattr(infer_state, "max_decoding_len", None)
+    if not max_len:
+        max_len = engine_config.max_blocks_per_seq * bs
+    max_blocks = min((max_len + bs - 1) // bs, block_table.shape[1])
+
+    ws = attn_workspace(dev, batch, hq, hkv, d, max_blocks)
+    _plan_for(infer_state, ws, dev, stream, lens, batch, hq, hkv, d, bs, max_blocks)
+    check(lib.mkv_paged_attention_decode(
+        dev, stream, q.data_ptr(), o.data_ptr(), pool, block_table.data_ptr(), block_table.stride(0),
+        seq_ids.data_ptr(), lens.data_ptr(), batch, hq, cur_layer, float(infer_state.softmax_scale),
+        max_blocks, ws.tensor.data_ptr(), ws.nbytes), "mkv_paged_attention_decode")

@@ -1,0 +1,63 @@
+"""Helpers shared by the GPU parity tests: move a seeded case to the device and
+call the package exactly as the reference's worker would."""
+from __future__ import annotations
+
+import types
+
+import numpy as np
+import torch
+
+
+def cfgs(c, max_blocks_per_seq):
+    model_config = types.SimpleNamespace(num_layers=c["L"], num_q_heads=c.get("Hq", c["Hkv"]),
+                                         num_kv_heads=c["Hkv"], head_dim=c["D"])
+    engine_config = types.SimpleNamespace(block_size=c["bs"], max_blocks_per_seq=max_blocks_per_seq)
+    return model_config, engine_config
+
+
+def to_dev(a, dev="cuda"):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+
+
+def decode_state(c, seq_ids, seq_lens, sbs=512):
+    from morphserve_b200.worker.infer_state import LlamaInferState
+    lens_list = [int(x) for x in seq_lens.tolist()]
+    z = torch.zeros(0, dtype=torch.int32, device="cuda")
+    max_len = max(lens_list) if lens_list else 0
+    return LlamaInferState(
+        batch_size=len(lens_list), num_tokens=len(lens_list), seq_ids=seq_ids, softmax_scale=c["scale"],
+        num_prefill_seqs=0, num_prefill_tokens=0, prefill_seq_start_locs=z, prefill_seq_start_locs_with_end=z,
+        prefill_seq_lens=z, max_prefill_len=0, num_decoding_seqs=len(lens_list), decoding_seq_lens=seq_lens,
+        max_decoding_len=max_len, seq_block_size=sbs, num_seq_blocks=(max_len + sbs - 1) // sbs,
+        num_blocks_org=c["num_blocks_org"], kv_cache_new_block_size=c["chunk_blocks"],
+        org_layer_param_size=0, position_cos=z, position_sin=z, ignore_kvcache=False)
+
+
+def device_case(c):
+    """numpy case -> dict of CUDA tensors (pools as [main] + chunks)."""
+    d = dict(c)
+    d["k_pools_t"] = [to_dev(p) for p in c["k_pools"]]
+    d["v_pools_t"] = [to_dev(p) for p in c["v_pools"]]
+    d["q_t"] = to_dev(c["q"])
+    d["k_new_t"] = to_dev(c["k_new"])
+    d["v_new_t"] = to_dev(c["v_new"])
+    d["block_table_t"] = to_dev(c["block_table"])
+    d["seq_ids_t"] = to_dev(c["seq_ids"])
+    d["seq_lens_t"] = to_dev(c["seq_lens"])
+    return d
+
+
+def run_decode_step(d):
+    """store_kvcache + paged_attention through the public API; returns o [B,Hq,D] (numpy)
+    and the pools after the append (numpy lists)."""
+    from morphserve_b200 import paged_attention, store_kvcache
+    mc, ec = cfgs(d, d["block_table_t"].shape[1])
+    st = decode_state(d, d["seq_ids_t"], d["seq_lens_t"])
+    kc, vc = d["k_pools_t"][0], d["v_pools_t"][0]
+    kn, vn = d["k_pools_t"][1:], d["v_pools_t"][1:]
+    store_kvcache(d["k_new_t"], d["v_new_t"], kc, vc, kn, vn, d["block_table_t"], mc, ec, st, d["layer"])
+    o = torch.zeros((d["B"], d["Hq"] * d["D"]), dtype=d["q_t"].dtype, device="cuda")
+    paged_attention(d["q_t"], kc, vc, kn, vn, d["block_table_t"], mc, ec, st, d["layer"], o)
+    torch.cuda.synchronize()
+    return (o.cpu().numpy().reshape(d["B"], d["Hq"], d["D"]),
+            [p.cpu().numpy() for p in d["k_pools_t"]], [p.cpu().numpy() for p in d["v_pools_t"]])

@@ -1,0 +1,276 @@
+"""GPU parity for the elastic pool: expand, release rule, compaction with
+block-table remap, and swap.  After every mutation the device state is compared
+with the CPU oracle: tables, counts and bitmap exactly, K/V bytes exactly."""
+import types
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import kv_oracle as O
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+
+class Twin:
+    """The product objects on the GPU next to the oracle on the CPU, driven in lockstep."""
+
+    def __init__(self, L, Hkv, D, bs, nb_org, max_seqs, mbps, seed):
+        from morphserve_b200 import BlockManager
+        self.L, self.Hkv, self.D, self.bs = L, Hkv, D, bs
+        self.rs = np.random.RandomState(seed)
+        shape = (nb_org, L, Hkv, bs, D)
+        self.model = types.SimpleNamespace(
+            k_cache=torch.zeros(shape, dtype=torch.float16, device="cuda"),
+            v_cache=torch.zeros(shape, dtype=torch.float16, device="cuda"),
+            k_cache_new=[], v_cache_new=[], kv_cache_new_block_size=0,
+            gpu_block_manager=BlockManager("GPU", nb_org, max_seqs, mbps, bs))
+        self.engine = types.SimpleNamespace(model=self.model, scheduler=types.SimpleNamespace(num_gpu_blocks=nb_org))
+        self.obm = O.BlockManagerOracle(nb_org, max_seqs, mbps, bs)
+        self.ok = [np.zeros(shape, dtype=np.float16)]
+        self.ov = [np.zeros(shape, dtype=np.float16)]
+        self.chunk = 0
+        self.lens = {}
+
+    # ---- mutations -----------------------------------------------------------
+    def admit(self, seq_id, length):
+        ids = np.array([seq_id], dtype=np.int32)
+        ln = np.array([length], dtype=np.int32)
+        new = self.model.gpu_block_manager.allocate_blocks_for_seqs(H.to_dev(ids), H.to_dev(ln))
+        onew = self.obm.allocate_blocks_for_seqs(ids, ln)
+        np.testing.assert_array_equal(new.cpu().numpy(), onew)
+        self.lens[seq_id] = length
+        # fill the new blocks with data (stands for prefill)
+        for b in onew:
+            kb = self.rs.standard_normal((self.L, self.Hkv, self.bs, self.D)).astype(np.float16)
+            vb = self.rs.standard_normal((self.L, self.Hkv, self.bs, self.D)).astype(np.float16)
+            seg, row = O.locate_block(b, self.obm.num_blocks_org, max(self.chunk, 1))
+            self.ok[seg][row] = kb
+            self.ov[seg][row] = vb
+            kt = self.model.k_cache if seg == 0 else self.model.k_cache_new[seg - 1]
+            vt = self.model.v_cache if seg == 0 else self.model.v_cache_new[seg - 1]
+            kt[row].copy_(H.to_dev(kb))
+            vt[row].copy_(H.to_dev(vb))
+
+    def free(self, seq_ids):
+        ids = np.array(seq_ids, dtype=np.int32)
+        self.model.gpu_block_manager.free_blocks_for_seqs(H.to_dev(ids))
+        self.obm.free_blocks_for_seqs(ids)
+        for s in seq_ids:
+            self.lens.pop(s, None)
+
+    def expand(self, n):
+        from morphserve_b200.server import memory_utils as MU
+        shape = (n, self.L, self.Hkv, self.bs, self.D)
+        MU.attach_kvcache_chunk(self.engine, torch.zeros(shape, dtype=torch.float16, device="cuda"),
+                                torch.zeros(shape, dtype=torch.float16, device="cuda"))
+        O.expand(self.obm, n)
+        self.ok.append(np.zeros(shape, dtype=np.float16))
+        self.ov.append(np.zeros(shape, dtype=np.float16))
+        self.chunk = n
+
+    def decode_step(self, seq_ids, layers):
+        """allocate -> per layer (append, attention); compares attention with the oracle."""
+        from morphserve_b200 import paged_attention, store_kvcache
+        for s in seq_ids:
+            self.lens[s] += 1
+        ids = np.array(seq_ids, dtype=np.int32)
+        lens = np.array([self.lens[s] for s in seq_ids], dtype=np.int32)
+        bm = self.model.gpu_block_manager
+        new = bm.allocate_blocks_for_seqs(H.to_dev(ids), H.to_dev(lens))
+        onew = self.obm.allocate_blocks_for_seqs(ids, lens)
+        np.testing.assert_array_equal(new.cpu().numpy(), onew)
+        c = dict(L=self.L, Hq=self.Hkv * 4, Hkv=self.Hkv, D=self.D, bs=self.bs, scale=self.D ** -0.5,
+                 num_blocks_org=self.obm.num_blocks_org, chunk_blocks=self.chunk)
+        mc, ec = H.cfgs(c, bm.block_table.shape[1])
+        st = H.decode_state(c, H.to_dev(ids), H.to_dev(lens))
+        for layer in layers:
+            q = self.rs.standard_normal((len(ids), c["Hq"], self.D)).astype(np.float16)
+            k = self.rs.standard_normal((len(ids), self.Hkv, self.D)).astype(np.float16)
+            v = self.rs.standard_normal((len(ids), self.Hkv, self.D)).astype(np.float16)
+            store_kvcache(H.to_dev(k), H.to_dev(v), self.model.k_cache, self.model.v_cache, self.model.k_cache_new,
+                          self.model.v_cache_new, bm.block_table, mc, ec, st, layer)
+            O.store_kvcache_decode(k, v, self.ok, self.ov, self.obm.block_table, ids, lens, layer,
+                                   self.obm.num_blocks_org, max(self.chunk, 1))
+            o = torch.zeros((len(ids), c["Hq"] * self.D), dtype=torch.float16, device="cuda")
+            paged_attention(H.to_dev(q), self.model.k_cache, self.model.v_cache, self.model.k_cache_new,
+                            self.model.v_cache_new, bm.block_table, mc, ec, st, layer, o)
+            ex = O.paged_attention_exact(q, self.ok, self.ov, self.obm.block_table, ids, lens, layer, c["scale"],
+                                         self.obm.num_blocks_org, max(self.chunk, 1))
+            np.testing.assert_allclose(o.cpu().numpy().reshape(ex.shape).astype(np.float64), ex, rtol=2e-3, atol=1e-2)
+
+    # ---- comparison ------------------------------------------------------------
+    def check(self, raw_pools=True):
+        bm = self.model.gpu_block_manager
+        np.testing.assert_array_equal(bm.block_table.cpu().numpy(), self.obm.block_table)
+        np.testing.assert_array_equal(bm.num_seq_allocated_blocks.cpu().numpy(), self.obm.num_seq_allocated_blocks)
+        np.testing.assert_array_equal(bm.is_block_free.cpu().numpy(), self.obm.is_block_free)
+        assert bm.num_blocks == self.obm.num_blocks
+        assert int(bm.num_free_blocks) == self.obm.num_free_blocks
+        assert self.engine.scheduler.num_gpu_blocks == self.obm.num_blocks
+        assert len(self.model.k_cache_new) == len(self.ok) - 1
+        if raw_pools:
+            dk = [self.model.k_cache] + self.model.k_cache_new
+            dv = [self.model.v_cache] + self.model.v_cache_new
+            for a, b in zip(dk + dv, self.ok + self.ov):
+                assert a.cpu().numpy().tobytes() == b.tobytes()
+
+
+def _trace(nb_org, chunk, n_chunks, release, L, Hkv, batch, steps, seed, max_len):
+    from morphserve_b200.server import memory_utils as MU
+    bs, D = 16, 128
+    mbps = (max_len + steps * 3) // bs + 2
+    tw = Twin(L, Hkv, D, bs, nb_org, max_seqs=4096, mbps=mbps, seed=seed)
+    rs = np.random.RandomState(seed + 1)
+    next_id = [0]
+
+    def admit_until(frac):
+        while tw.obm.get_num_used_blocks() < frac * tw.obm.num_blocks:
+            ln = int(rs.randint(1, max_len + 1))
+            if (ln + bs - 1) // bs > tw.obm.num_free_blocks:
+                break
+            tw.admit(next_id[0], ln)
+            next_id[0] += 1
+
+    layers = list(range(L))
+    admit_until(0.85)
+    tw.check()
+    running = list(rs.permutation(list(tw.lens))[:batch])
+    for _ in range(steps):
+        tw.decode_step(running, layers)
+    tw.check()
+    for _ in range(n_chunks):
+        tw.expand(chunk)
+    tw.check()
+    admit_until(0.85)
+    running = list(rs.permutation(list(tw.lens))[:batch])
+    for _ in range(steps):
+        tw.decode_step(running, layers)
+    tw.check()
+    # free a seeded random subset until 40 % of the pool is free
+    order = list(rs.permutation(list(tw.lens)))
+    while tw.obm.num_free_blocks < 0.4 * tw.obm.num_blocks + 1 and order:
+        tw.free([order.pop()])
+    tw.check()
+    assert not MU.if_kv_cache_unused(tw.engine) or True    # may or may not be empty; release decides below
+    target = tw.obm.num_blocks_org + (n_chunks - release) * chunk
+    moved = MU.compact_kvcache(tw.engine, target)
+    omoved = O.compact(tw.obm, tw.ok, tw.ov, target, chunk)
+    assert moved == omoved and moved >= 0
+    tw.check()                                   # raw pools: source blocks keep their bytes
+    for _ in range(release):
+        assert MU.release_last_kvcache_chunk(tw.engine)
+        assert O.can_release_last_chunk(tw.obm, len(tw.ok) - 1, chunk)
+        O.release_last_chunk(tw.obm, chunk)
+        tw.ok.pop()
+        tw.ov.pop()
+    tw.check()
+    running = [s for s in running if s in tw.lens][:batch]
+    for _ in range(steps):
+        tw.decode_step(running, layers)
+    tw.check()
+    return moved
+
+
+def test_elastic_trace_small():
+    moved = _trace(nb_org=96, chunk=16, n_chunks=4, release=3, L=2, Hkv=2, batch=6, steps=5, seed=41, max_len=200)
+    assert moved > 0
+
+
+def test_elastic_trace_medium():
+    _trace(nb_org=512, chunk=64, n_chunks=8, release=6, L=2, Hkv=2, batch=24, steps=6, seed=42, max_len=600)
+
+
+def test_release_refused_while_last_chunk_is_live():
+    from morphserve_b200.server import memory_utils as MU
+    tw = Twin(1, 1, 128, 16, 8, max_seqs=16, mbps=8, seed=3)
+    tw.expand(4)
+    for s in range(5):
+        tw.admit(s, 32)          # 10 blocks -> ids 0..9, two of them in the chunk
+    assert not MU.release_last_kvcache_chunk(tw.engine)
+    assert MU.compact_kvcache(tw.engine, 8) == -1      # low region is full: nothing may change
+    tw.check()
+    tw.free([0])
+    assert MU.compact_kvcache(tw.engine, 8) == 2
+    assert O.compact(tw.obm, tw.ok, tw.ov, 8, 4) == 2
+    tw.check()
+    assert MU.release_last_kvcache_chunk(tw.engine)
+    O.release_last_chunk(tw.obm, 4)
+    tw.ok.pop()
+    tw.ov.pop()
+    tw.check()
+
+
+def test_swap_roundtrip_and_chunk_addressing():
+    from morphserve_b200 import swiftllm_c
+    L, Hkv, bs, D = 2, 2, 16, 128
+    rs = np.random.RandomState(8)
+    nb_org, chunk, n_chunks, ncpu = 12, 4, 2, 20
+    elems = chunk * L * Hkv * bs * D
+    P = 2 * elems + 1024                   # "layer parameter size" in elements
+    slab = torch.zeros(n_chunks * P, dtype=torch.float16, device="cuda")
+    k_new, v_new = [], []
+    for j in range(n_chunks):              # chunk j sits j*P elements below chunk 0
+        base = (n_chunks - 1 - j) * P
+        k_new.append(slab[base:base + elems].view(chunk, L, Hkv, bs, D))
+        v_new.append(slab[base + elems:base + 2 * elems].view(chunk, L, Hkv, bs, D))
+    kp = [rs.standard_normal((nb_org, L, Hkv, bs, D)).astype(np.float16)] + \
+         [rs.standard_normal((chunk, L, Hkv, bs, D)).astype(np.float16) for _ in range(n_chunks)]
+    vp = [rs.standard_normal(p.shape).astype(np.float16) for p in kp]
+    k_cache, v_cache = H.to_dev(kp[0]), H.to_dev(vp[0])
+    for j in range(n_chunks):
+        k_new[j].copy_(H.to_dev(kp[1 + j]))
+        v_new[j].copy_(H.to_dev(vp[1 + j]))
+    k_swap = torch.zeros((ncpu, L, Hkv, bs, D), dtype=torch.float16)
+    v_swap = torch.zeros((ncpu, L, Hkv, bs, D), dtype=torch.float16)
+    oks, ovs = k_swap.numpy().copy(), v_swap.numpy().copy()
+
+    # swap out: device ids (runs, a chunk boundary at 15|16, original/elastic boundary at 11|12)
+    src = [3, 4, 5, 10, 11, 12, 13, 14, 15, 16, 19]
+    dst = [0, 1, 2, 7, 8, 9, 10, 11, 12, 13, 5]
+    swiftllm_c.swap_blocks_new_kv_combined(src, dst, False, nb_org, P, chunk, 2, k_cache, v_cache, k_swap, v_swap,
+                                           k_new[0], v_new[0])
+    torch.cuda.synchronize()
+    O.swap_blocks(src, dst, False, kp, vp, oks, ovs, nb_org, chunk)
+    assert k_swap.numpy().tobytes() == oks.tobytes() and v_swap.numpy().tobytes() == ovs.tobytes()
+
+    # swap in to other device blocks, original pool only -> plain variant
+    src2, dst2 = [0, 1, 2, 5], [6, 7, 8, 0]
+    swiftllm_c.swap_blocks(src2, dst2, True, k_cache, v_cache, k_swap, v_swap)
+    O.swap_blocks(src2, dst2, True, kp, vp, oks, ovs, nb_org, chunk)
+    # swap in into elastic blocks: the device address comes from the TARGET id
+    src3, dst3 = [7, 8, 9, 10], [18, 19, 12, 13]
+    swiftllm_c.swap_blocks_new_kv_combined(src3, dst3, True, nb_org, P, chunk, 2, k_cache, v_cache, k_swap, v_swap,
+                                           k_new[0], v_new[0])
+    O.swap_blocks(src3, dst3, True, kp, vp, oks, ovs, nb_org, chunk)
+    torch.cuda.synchronize()
+    got = [k_cache] + k_new + [v_cache] + v_new
+    for a, b in zip(got, kp + vp):
+        assert a.cpu().numpy().tobytes() == b.tobytes()
+    with pytest.raises(RuntimeError):
+        swiftllm_c.swap_blocks([0], [ncpu], False, k_cache, v_cache, k_swap, v_swap)   # host id out of range
+
+
+def test_acquire_new_kvcache_carves_the_slab_like_the_reference():
+    from morphserve_b200 import swiftllm_c
+    L, Hkv, bs, D = 2, 2, 16, 128
+    org_size, quant_size = 1 << 20, 300_001
+    slab = torch.full((org_size,), 7, dtype=torch.uint8, device="cuda")
+    swiftllm_c.register_kv_cache_info(L, Hkv, bs, D)
+    with pytest.raises(RuntimeError):
+        swiftllm_c.acquire_new_kvcache(5)
+    swiftllm_c.register_layer_memory_org_gpu(5, slab.data_ptr(), org_size)
+    swiftllm_c.register_layer_memory_quant(5, 0, quant_size)
+    k, v = swiftllm_c.acquire_new_kvcache(5)
+    ka, va, n = O.chunk_layout(slab.data_ptr(), org_size, quant_size, L, Hkv, bs, D)
+    assert (k.data_ptr(), v.data_ptr(), k.shape[0]) == (ka, va, n)
+    assert tuple(k.shape) == (n, L, Hkv, bs, D) and k.dtype == torch.float16
+    host = slab.cpu().numpy()
+    off = ka - slab.data_ptr()
+    assert (host[:off] == 7).all()                                   # the quantised layer's bytes are untouched
+    assert (host[off:off + 2 * k.numel() * 2] == 0).all()            # chunk is zero-filled
+    swiftllm_c.register_layer_memory_quant(6, 0, org_size - 100)
+    swiftllm_c.register_layer_memory_org_gpu(6, slab.data_ptr(), org_size)
+    with pytest.raises(RuntimeError):
+        swiftllm_c.acquire_new_kvcache(6)

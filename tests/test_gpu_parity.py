@@ -1,0 +1,167 @@
+"""GPU parity: the CUDA path (through the public API -> C ABI) against the
+reference's outputs (golden fixtures) and against the CPU oracle on seeded
+inputs.  Bit-exact for byte/integer work; rtol 2e-3 / atol 1e-2 for attention
+(fp16 data, fp32 accumulation)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import kv_oracle as O
+from tests import helpers as H
+from tests.golden import cases
+
+pytestmark = pytest.mark.gpu
+G = os.path.join(os.path.dirname(__file__), "golden")
+RTOL, ATOL = 2e-3, 1e-2
+
+
+def _close(a, b):
+    np.testing.assert_allclose(np.asarray(a, dtype=np.float64), np.asarray(b, dtype=np.float64), rtol=RTOL, atol=ATOL)
+
+
+@pytest.mark.parametrize("name", list(cases.DECODE_CASES))
+def test_decode_step_matches_reference_fixture(name):
+    c = cases.build_decode_case(**cases.DECODE_CASES[name])
+    gold = np.load(os.path.join(G, f"decode_{name}.npz"))
+    o, kp, vp = H.run_decode_step(H.device_case(c))
+    assert cases.sha256_of(*kp, *vp) == str(gold["pools_after_sha256"]), "KV append is not bit-exact"
+    _close(o, gold["o"])
+    ex = O.paged_attention_exact(c["q"], kp, vp, c["block_table"], c["seq_ids"], c["seq_lens"], c["layer"],
+                                 c["scale"], c["num_blocks_org"], c["chunk_blocks"])
+    _close(o, ex)
+
+
+@pytest.mark.parametrize("name", list(cases.PREFILL_CASES))
+def test_prefill_scatter_matches_reference_fixture(name):
+    from morphserve_b200 import store_kvcache
+    from morphserve_b200.worker.infer_state import LlamaInferState
+    c = cases.build_prefill_case(**cases.PREFILL_CASES[name])
+    gold = np.load(os.path.join(G, f"prefill_{name}.npz"))
+    kp = [H.to_dev(p) for p in c["k_pools"]]
+    vp = [H.to_dev(p) for p in c["v_pools"]]
+    bt = H.to_dev(c["block_table"])
+    npre = len(c["prefill_lens"])
+    z = torch.zeros(0, dtype=torch.int32, device="cuda")
+    st = LlamaInferState(
+        batch_size=len(c["seq_ids"]), num_tokens=c["k"].shape[0], seq_ids=H.to_dev(c["seq_ids"]), softmax_scale=1.0,
+        num_prefill_seqs=npre, num_prefill_tokens=c["num_prefill_tokens"],
+        prefill_seq_start_locs=H.to_dev(c["prefill_start_locs"]), prefill_seq_start_locs_with_end=z,
+        prefill_seq_lens=H.to_dev(c["prefill_lens"]), max_prefill_len=int(c["prefill_lens"].max()),
+        num_decoding_seqs=len(c["decode_lens"]), decoding_seq_lens=H.to_dev(c["decode_lens"]),
+        max_decoding_len=int(c["decode_lens"].max()), seq_block_size=512, num_seq_blocks=1,
+        num_blocks_org=c["num_blocks_org"], kv_cache_new_block_size=c["chunk_blocks"], org_layer_param_size=0,
+        position_cos=z, position_sin=z, ignore_kvcache=False)
+    mc, ec = H.cfgs(c, bt.shape[1])
+    store_kvcache(H.to_dev(c["k"]), H.to_dev(c["v"]), kp[0], vp[0], kp[1:], vp[1:], bt, mc, ec, st, c["layer"])
+    torch.cuda.synchronize()
+    after = [p.cpu().numpy() for p in kp] + [p.cpu().numpy() for p in vp]
+    assert cases.sha256_of(*after) == str(gold["pools_after_sha256"])
+
+
+def test_block_manager_trace_matches_reference_fixture():
+    from morphserve_b200 import BlockManager
+    tr = cases.block_manager_trace()
+    gold = np.load(os.path.join(G, "block_manager_trace.npz"))
+    bm = BlockManager("GPU", tr["num_blocks"], tr["max_seqs"], tr["max_blocks_per_seq"], tr["block_size"])
+    for i, (op, ids, lens) in enumerate(tr["ops"]):
+        if op == "alloc":
+            r = bm.allocate_blocks_for_seqs(H.to_dev(ids), H.to_dev(lens))
+            assert r.dtype == torch.int64
+        elif op == "free":
+            bm.free_blocks_for_seqs(H.to_dev(ids))
+            r = torch.empty(0)
+        else:
+            r = bm.gather_allocated_blocks_and_free(H.to_dev(ids))
+            assert r.dtype == torch.int32
+        np.testing.assert_array_equal(r.cpu().numpy().astype(np.int64), gold[f"ret_{i}"])
+        np.testing.assert_array_equal(bm.block_table.cpu().numpy(), gold[f"table_{i}"])
+        np.testing.assert_array_equal(bm.num_seq_allocated_blocks.cpu().numpy(), gold[f"count_{i}"])
+        np.testing.assert_array_equal(bm.is_block_free.cpu().numpy(), gold[f"free_{i}"])
+        assert int(bm.num_free_blocks) == int(gold[f"nfree_{i}"])
+        assert bm.num_free_blocks.item() == int(gold[f"nfree_{i}"])
+    with pytest.raises(RuntimeError):
+        bm._allocate_blocks(int(bm.num_free_blocks) + 1)
+    ids = H.to_dev(np.array([0], dtype=np.int32))
+    bm.allocate_blocks_for_seqs(ids, H.to_dev(np.array([40], dtype=np.int32)))
+    with pytest.raises(AssertionError):
+        bm.allocate_blocks_for_seqs(ids, H.to_dev(np.array([1], dtype=np.int32)))
+
+
+# (B, Hq, Hkv, max_len, L, layer): every group size of the fast path, odd batch sizes,
+# sequences long enough to be cut into several chunks (merge path) and lengths at block edges
+SWEEP = [
+    (1, 8, 8, 1, 1, 0), (1, 4, 1, 4096, 1, 0), (3, 16, 1, 700, 2, 1), (5, 12, 4, 300, 2, 0),
+    (17, 32, 8, 1536, 2, 1), (64, 32, 32, 768, 1, 0), (9, 2, 1, 2500, 1, 0), (33, 64, 8, 1536, 1, 0),
+]
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,max_len,L,layer", SWEEP)
+def test_decode_attention_sweep_against_oracle(B, Hq, Hkv, max_len, L, layer):
+    rs = np.random.RandomState(B * 1000 + Hq)
+    lens = rs.randint(1, max_len + 1, size=B)
+    lens[0] = max_len
+    if B > 2:
+        lens[1] = max(1, (max_len // 16) * 16)      # exactly full last block
+        lens[2] = 1
+    nb = int(((lens + 15) // 16).sum()) + 5
+    c = cases.build_decode_case(seed=B * 77 + Hq, B=B, Hq=Hq, Hkv=Hkv, D=128, bs=16, L=L, layer=layer,
+                                num_blocks_org=nb, dtype=np.float16, lens=lens)
+    o, kp, vp = H.run_decode_step(H.device_case(c))
+    # append: bit-exact against the oracle
+    kpo, vpo = [p.copy() for p in c["k_pools"]], [p.copy() for p in c["v_pools"]]
+    O.store_kvcache_decode(c["k_new"], c["v_new"], kpo, vpo, c["block_table"], c["seq_ids"], c["seq_lens"],
+                           c["layer"], c["num_blocks_org"], c["chunk_blocks"])
+    for a, b in zip(kp + vp, kpo + vpo):
+        assert a.tobytes() == b.tobytes()
+    ex = O.paged_attention_exact(c["q"], kp, vp, c["block_table"], c["seq_ids"], c["seq_lens"], c["layer"],
+                                 c["scale"], c["num_blocks_org"], c["chunk_blocks"])
+    _close(o, ex)
+    from morphserve_b200.worker.kernels._common import read_attn_error_flags
+    assert read_attn_error_flags(0) == 0
+
+
+def test_every_length_across_block_and_chunk_edges():
+    """lens 1..160 in one batch: every len % 16, single- and multi-block sequences."""
+    lens = np.arange(1, 161)
+    B = len(lens)
+    nb = int(((lens + 15) // 16).sum()) + 3
+    c = cases.build_decode_case(seed=99, B=B, Hq=8, Hkv=2, D=128, bs=16, L=1, layer=0, num_blocks_org=nb,
+                                dtype=np.float16, lens=lens)
+    o, kp, vp = H.run_decode_step(H.device_case(c))
+    ex = O.paged_attention_exact(c["q"], kp, vp, c["block_table"], c["seq_ids"], c["seq_lens"], 0, c["scale"],
+                                 c["num_blocks_org"], 0)
+    _close(o, ex)
+
+
+def test_repeated_layers_reuse_one_plan():
+    """All layers of a step share the plan; counters must re-arm between launches."""
+    from morphserve_b200 import paged_attention
+    L = 4
+    c = cases.build_decode_case(seed=5, B=12, Hq=8, Hkv=2, D=128, bs=16, L=L, layer=0, num_blocks_org=400,
+                                dtype=np.float16, max_len=1500)
+    d = H.device_case(c)
+    mc, ec = H.cfgs(d, d["block_table_t"].shape[1])
+    st = H.decode_state(d, d["seq_ids_t"], d["seq_lens_t"])
+    for rep in range(2):
+        for layer in range(L):
+            o = torch.zeros((d["B"], d["Hq"] * d["D"]), dtype=torch.float16, device="cuda")
+            paged_attention(d["q_t"], d["k_pools_t"][0], d["v_pools_t"][0], [], [], d["block_table_t"], mc, ec, st,
+                            layer, o)
+            ex = O.paged_attention_exact(c["q"], c["k_pools"], c["v_pools"], c["block_table"], c["seq_ids"],
+                                         c["seq_lens"], layer, c["scale"], c["num_blocks_org"], 0)
+            _close(o.cpu().numpy().reshape(ex.shape), ex)
+
+
+def test_plain_kernel_other_shapes():
+    """head_dim 64 / block_size 8 (fp16) and fp32 pools take the plain kernel."""
+    for dtype, D, bs in ((np.float16, 64, 8), (np.float32, 128, 16), (np.float32, 96, 32)):
+        c = cases.build_decode_case(seed=11, B=5, Hq=6, Hkv=3, D=D, bs=bs, L=2, layer=1, num_blocks_org=80,
+                                    dtype=dtype, max_len=300)
+        o, kp, vp = H.run_decode_step(H.device_case(c))
+        ex = O.paged_attention_exact(c["q"], kp, vp, c["block_table"], c["seq_ids"], c["seq_lens"], 1, c["scale"],
+                                     c["num_blocks_org"], 0)
+        _close(o, ex)
+        # the reference stores fp16-rounded values even into an fp32 `o`
+        assert np.array_equal(o, o.astype(np.float16).astype(o.dtype))
