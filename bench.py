@@ -27,7 +27,6 @@ import json
 import os
 import statistics
 import sys
-import threading
 import time
 
 import numpy as np
@@ -183,58 +182,57 @@ class DecodeJob:
 # ----------------------------------------------------------------------------
 class ClockSampler:
     """Samples SM clock and throttle reasons of the GPUs in use while the timed
-    region runs (read-only NVML queries)."""
+    region runs: a separate read-only `nvidia-smi --query-gpu ... -lms` process,
+    so that sampling does not compete with the launching thread."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
     def __init__(self, indices):
-        self.samples, self.reasons, self.max_mhz = [], set(), None
-        self._stop = threading.Event()
-        self._thread = None
-        try:
-            import pynvml as N
-            N.nvmlInit()
-            self.N = N
-            self.handles = [N.nvmlDeviceGetHandleByIndex(i) for i in indices]
-            self.max_mhz = max(N.nvmlDeviceGetMaxClockInfo(h, N.NVML_CLOCK_SM) for h in self.handles)
-        except Exception:
-            self.N = None
-
-    def _run(self):
-        N = self.N
-        names = {}
-        for nm in ("HwSlowdown", "HwThermalSlowdown", "SwThermalSlowdown", "SwPowerCap", "HwPowerBrakeSlowdown"):
-            v = getattr(N, "nvmlClocksThrottleReason" + nm, None)
-            if v is not None:
-                names[v] = {"HwSlowdown": "hw_slowdown", "HwThermalSlowdown": "hw_thermal_slowdown",
-                            "SwThermalSlowdown": "sw_thermal_slowdown", "SwPowerCap": "sw_power_cap",
-                            "HwPowerBrakeSlowdown": "hw_power_brake_slowdown"}[nm]
-        while not self._stop.is_set():
-            for h in self.handles:
-                try:
-                    self.samples.append(N.nvmlDeviceGetClockInfo(h, N.NVML_CLOCK_SM))
-                    r = N.nvmlDeviceGetCurrentClocksThrottleReasons(h)
-                    for bit, nm in names.items():
-                        if r & bit:
-                            self.reasons.add(nm)
-                except Exception:
-                    pass
-            self._stop.wait(0.02)
+        self.indices = set(indices)
+        self.proc = None
+        self.text = ""
 
     def __enter__(self):
-        if self.N is not None:
-            self._thread = threading.Thread(target=self._run, daemon=True)
-            self._thread.start()
+        if self.indices:
+            import subprocess
+            try:
+                self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}",
+                                              "--format=csv,noheader,nounits", "-lms", "25"],
+                                             stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            except Exception:
+                self.proc = None
         return self
 
     def __exit__(self, *a):
-        self._stop.set()
-        if self._thread is not None:
-            self._thread.join()
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.text, _ = self.proc.communicate(timeout=5)
+            except Exception:
+                self.proc.kill()
 
     def summary(self):
-        if not self.samples:
-            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable"]}
-        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
-                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+        mhz, mx, power, reasons = [], None, [], set()
+        for ln in self.text.splitlines():
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 8 or not f[0].isdigit() or int(f[0]) not in self.indices:
+                continue
+            try:
+                mhz.append(float(f[1]))
+                mx = float(f[2])
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for nm, val in zip(self.NAMES, f[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        if not mhz:
+            return {"sm_mhz": None, "sm_max_mhz": mx, "reasons": ["unavailable"]}
+        return {"sm_mhz": statistics.median(mhz), "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(mhz), "power_w_max": max(power) if power else None}
 
 
 # ----------------------------------------------------------------------------

@@ -139,7 +139,7 @@ def test_repeated_layers_reuse_one_plan():
     """All layers of a step share the plan; counters must re-arm between launches."""
     from morphserve_b200 import paged_attention
     L = 4
-    c = cases.build_decode_case(seed=5, B=12, Hq=8, Hkv=2, D=128, bs=16, L=L, layer=0, num_blocks_org=400,
+    c = cases.build_decode_case(seed=5, B=12, Hq=8, Hkv=2, D=128, bs=16, L=L, layer=0, num_blocks_org=1200,
                                 dtype=np.float16, max_len=1500)
     d = H.device_case(c)
     mc, ec = H.cfgs(d, d["block_table_t"].shape[1])
@@ -157,7 +157,7 @@ def test_repeated_layers_reuse_one_plan():
 def test_plain_kernel_other_shapes():
     """head_dim 64 / block_size 8 (fp16) and fp32 pools take the plain kernel."""
     for dtype, D, bs in ((np.float16, 64, 8), (np.float32, 128, 16), (np.float32, 96, 32)):
-        c = cases.build_decode_case(seed=11, B=5, Hq=6, Hkv=3, D=D, bs=bs, L=2, layer=1, num_blocks_org=80,
+        c = cases.build_decode_case(seed=11, B=5, Hq=6, Hkv=3, D=D, bs=bs, L=2, layer=1, num_blocks_org=240,
                                     dtype=dtype, max_len=300)
         o, kp, vp = H.run_decode_step(H.device_case(c))
         ex = O.paged_attention_exact(c["q"], kp, vp, c["block_table"], c["seq_ids"], c["seq_lens"], 1, c["scale"],
