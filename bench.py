@@ -44,6 +44,8 @@ WORKLOADS = {
     "codellama-34b-gqa-decode": dict(cfg=5, B=512, Hq=64, Hkv=8, L=48, max_len=1536, free_frac=0.05),
     # small case for profiler captures and CPU-side dry runs (pool ~1.3 GB: larger than L2)
     "small-gqa-decode": dict(cfg=9, B=64, Hq=32, Hkv=8, L=4, max_len=1536, free_frac=0.10),
+    # the llama3-8b batch with 2 layers: same bytes per attention launch as the full workload, pool ~1.8 GB
+    "llama3-8b-gqa-decode-2layer": dict(cfg=3, B=256, Hq=32, Hkv=8, L=2, max_len=1536, free_frac=0.10),
 }
 D, BS = 128, 16
 FALLBACK_HBM_GBS = 6650.0

@@ -1,6 +1,8 @@
 """Builds ``libmorphkv.so`` (the C-ABI CUDA library) in-tree for sm_100a.
 
-    python -m morphserve_b200.build [--force] [--verbose]
+    python morphserve_b200/build.py [--force] [--verbose]
+
+(run it as a script: importing the package requires the library to exist already)
 
 nvcc cross-compiles without a GPU.  The library links the CUDA runtime
 statically and has no other dependency, so the built file can be copied to the

@@ -15,8 +15,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 @pytest.fixture(scope="module")
 def L():
-    from morphserve_b200.build import build
-    build()
+    import __graft_entry__
+    __graft_entry__.build()
     from morphserve_b200 import _lib
     return _lib
 
