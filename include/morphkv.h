@@ -42,7 +42,8 @@ typedef enum mkv_status {
     MKV_ERR_RANGE = -5,     /* an id (layer, block, segment) is out of range */
     MKV_ERR_CUDA = -6,      /* a CUDA runtime call failed; see mkv_last_cuda_error */
     MKV_ERR_NOSPACE = -7,   /* no room: chunk does not fit / too few free blocks */
-    MKV_ERR_ALIGN = -8      /* a pointer or row size is not aligned as required */
+    MKV_ERR_ALIGN = -8,     /* a pointer or row size is not aligned as required */
+    MKV_ERR_TOO_LARGE = -9  /* the request needs more scratch than the no-allocation entry point has */
 } mkv_status;
 
 /*
@@ -119,6 +120,40 @@ int mkv_paged_attention_decode(
  * stream).  Bit 0: a block-table entry was outside the pool and was skipped.
  */
 int mkv_attn_read_error_flags(int device, void *stream, const void *workspace, int *flags /* host */);
+
+/*
+ * Decode attention for callers that cannot allocate device memory.
+ * (No counterpart in the reference: its wrapper allocates two tensors per call.)
+ *
+ * Who needs it: a caller that is in the middle of capturing work on the stream,
+ * a server that gave all device memory to the KV pool at start-up so that a late
+ * cudaMalloc may fail, or a plug-in that only receives a stream and pointers and
+ * has no allocator of its own.  Such a caller cannot provide the workspace that
+ * mkv_attn_plan / mkv_paged_attention_decode ask for.
+ *
+ * This one call plans and runs the attention of one layer using a scratch array
+ * built into the library: mkv_noalloc_scratch_bytes() = 16 MiB of device memory,
+ * held on every GPU the library is used on from the first use until process exit.
+ * It calls no cudaMalloc / cudaFree / allocating routine and never synchronises.
+ * Results equal mkv_paged_attention_decode's.
+ *
+ *  - Limit: if the batch needs more scratch than the array holds (roughly
+ *    batch * num_q_heads * head_dim beyond 256 x 32 x 128 on a 148-SM part; the
+ *    exact need is mkv_attn_workspace_bytes(...)), the call returns
+ *    MKV_ERR_TOO_LARGE and launches nothing.
+ *  - The first call on each device resolves the array's device address
+ *    (cudaGetSymbolAddress, with that device current).  Make that first call
+ *    outside any stream capture.
+ *  - All calls on a device share the one array, and it keeps the previous
+ *    call's contents; each call re-initialises what it needs at its start.  Two
+ *    calls that overlap on the GPU (different streams without an event between
+ *    them) race on it: order them.
+ */
+int mkv_paged_attention_decode_noalloc(
+    int device, void *stream, const void *q, void *o, const mkv_pool *pool, const int32_t *block_table,
+    int64_t table_stride, const int32_t *seq_ids, const int32_t *seq_lens, int batch, int num_q_heads,
+    int cur_layer, float softmax_scale, int max_blocks_per_seq_in_batch);
+size_t mkv_noalloc_scratch_bytes(void);
 
 /* ---- KV append / scatter --------------------------------------------- */
 /*

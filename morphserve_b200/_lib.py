@@ -1,7 +1,7 @@
 """ctypes binding of ``libmorphkv.so`` (declared in ``include/morphkv.h``).
 
 There is no fallback: importing this module raises if the CUDA library has not
-been built (``python -m morphserve_b200.build``), and every wrapper raises on a
+been built (``python morphserve_b200/build.py``), and every wrapper raises on a
 non-zero status.  Argument errors keep the reference's exception types at the
 Python layer (the callers translate), everything else is a RuntimeError.
 """
@@ -15,7 +15,7 @@ _LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libmorphkv
 
 if not os.path.exists(_LIB_PATH):
     raise ImportError(
-        f"{_LIB_PATH} is missing: build the CUDA library first (python -m morphserve_b200.build). "
+        f"{_LIB_PATH} is missing: build the CUDA library first (python morphserve_b200/build.py). "
         "morphserve_b200 has no CPU or Triton fallback.")
 
 lib = C.CDLL(_LIB_PATH)
@@ -49,6 +49,8 @@ SIGNATURES = {
     "mkv_attn_plan": (_i, [_i, _vp, _vp, _sz, _vp, _i, _i, _i, _i, _i, _i]),
     "mkv_paged_attention_decode": (_i, [_i, _vp, _vp, _vp, _pool, _vp, _i64, _vp, _vp, _i, _i, _i, _f, _i, _vp, _sz]),
     "mkv_attn_read_error_flags": (_i, [_i, _vp, _vp, C.POINTER(_i)]),
+    "mkv_paged_attention_decode_noalloc": (_i, [_i, _vp, _vp, _vp, _pool, _vp, _i64, _vp, _vp, _i, _i, _i, _f, _i]),
+    "mkv_noalloc_scratch_bytes": (_sz, []),
     "mkv_store_kv_decode": (_i, [_i, _vp, _vp, _vp, _pool, _vp, _i64, _vp, _vp, _i, _i]),
     "mkv_store_kv_prefill": (_i, [_i, _vp, _vp, _vp, _pool, _vp, _i64, _vp, _vp, _vp, _i, _i, _i]),
     "mkv_block_need": (_i, [_i, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp]),

@@ -803,3 +803,122 @@ int mkv_attn_read_error_flags(int device, void *stream, const void *workspace, i
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------ entry point that allocates nothing
+//
+// Some hosts of this library may not allocate device memory at the moment they
+// need attention: code running while a CUDA graph is being captured on the
+// stream, a serving loop whose memory budget was handed out in full at start-up
+// (the KV pool is sized to fill the GPU, so a late cudaMalloc can fail), or a
+// plug-in that is only given a stream and raw pointers and owns no allocator.
+// For them the scratch of the decode kernel (plan, split-KV partials, counters)
+// lives in the fixed array below.  Every GPU on which the library is used holds
+// these 16 MiB from the first use until the process exits.
+namespace mkv {
+
+constexpr size_t kBuiltinScratchBytes = (size_t)16 << 20;
+static __device__ __align__(256) unsigned char g_builtin_scratch[kBuiltinScratchBytes];
+
+// Device address of the array on `device`.  In host code the array's NAME is only
+// a handle for the runtime, not a device address, so it is resolved once per
+// device, with that device current, and the resolved pointer is what kernels get.
+static cudaError_t builtin_scratch_address(int device, void **out) {
+    static void *ptrs[64] = {};
+    static bool ready[64] = {};
+    if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
+    if (!ready[device]) {
+        void *ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void **)&ptr, g_builtin_scratch);  // current device == `device`
+        if (e != cudaSuccess) return e;
+        if (ptr == nullptr) return cudaErrorInvalidSymbol;
+        ptrs[device] = ptr;
+        ready[device] = true;
+    }
+    *out = ptrs[device];
+    return cudaSuccess;
+}
+
+}  // namespace mkv
+
+extern "C" {
+
+int mkv_paged_attention_decode_noalloc(int device, void *stream, const void *q, void *o, const mkv_pool *pool,
+                                       const int32_t *block_table, int64_t table_stride, const int32_t *seq_ids,
+                                       const int32_t *seq_lens, int batch, int num_q_heads, int cur_layer,
+                                       float softmax_scale, int max_blocks_per_seq_in_batch) {
+    PoolView pv;
+    int st = validate_pool(pool, &pv);
+    if (st) return st;
+    if (batch < 0 || num_q_heads < 1 || table_stride < 1) return MKV_ERR_SHAPE;
+    if (num_q_heads % pv.num_kv_heads != 0) return MKV_ERR_SHAPE;
+    if (pv.head_dim > 32 * kMaxDimsPerLane) return MKV_ERR_SHAPE;
+    if (cur_layer < 0 || cur_layer >= pv.num_layers) return MKV_ERR_RANGE;
+    if (batch == 0) return MKV_OK;
+    if (!q || !o || !block_table || !seq_ids || !seq_lens) return MKV_ERR_NULL;
+    if (pv.total_blocks < 1) return MKV_ERR_SHAPE;
+    int sms = 0;
+    st = mkv_sm_count(device, &sms);
+    if (st) return st;
+    const bool fast = fast_path_ok(pv, num_q_heads, q, o);
+    WsLayout L;
+    if (fast) {
+        L = make_layout(sms, batch, num_q_heads, pv.num_kv_heads, pv.head_dim, max_blocks_per_seq_in_batch);
+        if (L.total > kBuiltinScratchBytes) return MKV_ERR_TOO_LARGE;  // before anything is launched
+    }
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
+    void *scratch = nullptr;
+    MKV_CUDA_TRY(builtin_scratch_address(device, &scratch));
+    cudaStream_t s = (cudaStream_t)stream;
+    const float scale_log2 = softmax_scale * kLog2e;
+    char *ws = (char *)scratch;
+
+    if (!fast) {  // the plain kernel needs no scratch beyond the error word
+        const int threads = 128;
+        const unsigned grid = (unsigned)ceil_div64((int64_t)batch * num_q_heads, threads / 32);
+        int *flags = &((WsHeader *)ws)->error_flags;
+        if (pv.elem_bytes == 2)
+            attn_decode_plain_kernel<__half><<<grid, threads, 0, s>>>(pv, (const __half *)q, (__half *)o, block_table,
+                                                                     table_stride, seq_ids, seq_lens, batch,
+                                                                     num_q_heads, cur_layer, scale_log2, flags);
+        else
+            attn_decode_plain_kernel<float><<<grid, threads, 0, s>>>(pv, (const float *)q, (float *)o, block_table,
+                                                                    table_stride, seq_ids, seq_lens, batch,
+                                                                    num_q_heads, cur_layer, scale_log2, flags);
+        MKV_LAUNCH_CHECK();
+        return MKV_OK;
+    }
+
+    // The plan kernel rewrites everything that must start clean: header, work and
+    // done counters, the arrival counters of every (sequence, kv head), the item list.
+    attn_plan_kernel<<<1, 1024, 0, s>>>((WsHeader *)ws, (int4 *)(ws + L.items), (int4 *)(ws + L.items_tmp),
+                                        (int2 *)(ws + L.split_info), (int *)(ws + L.arrive), seq_lens, batch,
+                                        pv.num_kv_heads, pv.block_size, L.cap_items);
+    MKV_LAUNCH_CHECK();
+    AttnParams p;
+    p.pool = pv;
+    p.q = (const __half *)q;
+    p.o = (__half *)o;
+    p.block_table = block_table;
+    p.table_stride = table_stride;
+    p.seq_ids = seq_ids;
+    p.seq_lens = seq_lens;
+    p.batch = batch;
+    p.num_q_heads = num_q_heads;
+    p.group = num_q_heads / pv.num_kv_heads;
+    p.cur_layer = cur_layer;
+    p.scale_log2 = scale_log2;
+    p.hdr = (WsHeader *)ws;
+    p.items = (const int4 *)(ws + L.items);
+    p.split_info = (const int2 *)(ws + L.split_info);
+    p.arrive = (int *)(ws + L.arrive);
+    p.lse = (float *)(ws + L.lse);
+    p.part_o = (float *)(ws + L.part_o);
+    cudaError_t e = launch_decode<8, 3>(p, sms, s);
+    if (e != cudaSuccess) return set_cuda_error(e);
+    return MKV_OK;
+}
+
+size_t mkv_noalloc_scratch_bytes(void) { return kBuiltinScratchBytes; }
+
+}  // extern "C"

@@ -67,6 +67,7 @@ const char *mkv_status_string(int status) {
         case MKV_ERR_CUDA: return "CUDA runtime error";
         case MKV_ERR_NOSPACE: return "not enough space";
         case MKV_ERR_ALIGN: return "pointer or row size not aligned as required";
+        case MKV_ERR_TOO_LARGE: return "request exceeds the built-in scratch of the no-allocation entry point";
         default: return "unknown status";
     }
 }
