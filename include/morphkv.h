@@ -98,7 +98,8 @@ size_t mkv_attn_workspace_bytes(int device, int batch, int num_q_heads, int num_
                                 int head_dim, int max_blocks_per_seq_in_batch);
 
 int mkv_attn_plan(int device, void *stream, void *workspace, size_t workspace_bytes,
-                  const int32_t *seq_lens /* device [batch] */, int batch, int num_q_heads,
+                  const int32_t *seq_lens /* device [batch] */, const int32_t *seq_ids /* device [batch] */,
+                  int batch, int num_q_heads,
                   int num_kv_heads, int head_dim, int block_size,
                   int max_blocks_per_seq_in_batch /* host upper bound of ceil(len/block_size) */);
 
@@ -114,6 +115,15 @@ int mkv_paged_attention_decode(
     int batch, int num_q_heads, int cur_layer, float softmax_scale,
     int max_blocks_per_seq_in_batch, /* the value given to mkv_attn_plan */
     void *workspace, size_t workspace_bytes);
+
+/*
+ * Tuning knobs of the decode kernel (process-wide; not needed for normal use):
+ * warps per SM and ring stages (values <= 0 keep the current ones), kernel
+ * flavour (1 = continuous tile stream, 0 = per-item ring, < 0 keeps), and the
+ * number of work units planned per worker warp (<= 0 keeps).  Changing the item
+ * factor changes mkv_attn_workspace_bytes: re-query it and plan again.
+ */
+int mkv_attn_configure(int warps, int stages, int stream_kernel, double item_factor);
 
 /*
  * Copies the device-side error word of a workspace to `*flags` (synchronises the

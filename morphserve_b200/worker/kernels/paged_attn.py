@@ -18,15 +18,15 @@ from ..._lib import check, lib
 from ._common import attn_workspace, device_and_stream, make_pool, require_cuda
 
 
-def _plan_for(infer_state, ws, dev, stream, lens, batch, hq, hkv, d, bs, max_blocks):
-    token = (ws.generation, dev, batch, max_blocks, lens.data_ptr())
+def _plan_for(infer_state, ws, dev, stream, lens, seq_ids, batch, hq, hkv, d, bs, max_blocks):
+    token = (ws.generation, dev, batch, max_blocks, lens.data_ptr(), seq_ids.data_ptr())
     state = getattr(infer_state, "__dict__", None)
     if state is not None and state.get("_mkv_plan_token") == token:
         return
     ws.generation += 1
     token = (ws.generation,) + token[1:]
-    check(lib.mkv_attn_plan(dev, stream, ws.tensor.data_ptr(), ws.nbytes, lens.data_ptr(), batch, hq, hkv, d, bs,
-                            max_blocks), "mkv_attn_plan")
+    check(lib.mkv_attn_plan(dev, stream, ws.tensor.data_ptr(), ws.nbytes, lens.data_ptr(), seq_ids.data_ptr(), batch,
+                            hq, hkv, d, bs, max_blocks), "mkv_attn_plan")
     if state is not None:
         state["_mkv_plan_token"] = token
 
@@ -68,7 +68,7 @@ def paged_attention(
     max_blocks = min((max_len + bs - 1) // bs, block_table.shape[1])
 
     ws = attn_workspace(dev, batch, hq, hkv, d, max_blocks)
-    _plan_for(infer_state, ws, dev, stream, lens, batch, hq, hkv, d, bs, max_blocks)
+    _plan_for(infer_state, ws, dev, stream, lens, seq_ids, batch, hq, hkv, d, bs, max_blocks)
     check(lib.mkv_paged_attention_decode(
         dev, stream, q.data_ptr(), o.data_ptr(), pool, block_table.data_ptr(), block_table.stride(0),
         seq_ids.data_ptr(), lens.data_ptr(), batch, hq, cur_layer, float(infer_state.softmax_scale),

@@ -90,7 +90,7 @@ def test_host_side_argument_validation(L):
     assert lib.mkv_paged_attention_decode(0, None, 1, 1, C.byref(p), 1, 4, 1, 1, 3, 5, 0, 0.1, 4, None, 0) == -2
     assert lib.mkv_paged_attention_decode(0, None, 1, 1, C.byref(p), 1, 4, 1, 1, 3, 4, 7, 0.1, 4, None, 0) == -5
     assert lib.mkv_paged_attention_decode(0, None, 1, 1, C.byref(p), 1, 4, 1, 1, 0, 4, 0, 0.1, 4, None, 0) == 0
-    assert lib.mkv_attn_plan(0, None, None, 0, 1, 4, 4, 2, 128, 16, 8) == -4
+    assert lib.mkv_attn_plan(0, None, None, 0, 1, 1, 4, 4, 2, 128, 16, 8) == -4
     assert lib.mkv_bitmap_select(0, None, 1, 5, 2, 1, 1, 0, 1, None, None) == -2
     assert lib.mkv_copy_blocks(0, None, C.byref(p), None, None, 3) == -1
     assert lib.mkv_copy_blocks(0, None, C.byref(p), None, None, 0) == 0

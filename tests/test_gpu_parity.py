@@ -17,6 +17,15 @@ G = os.path.join(os.path.dirname(__file__), "golden")
 RTOL, ATOL = 2e-3, 1e-2
 
 
+@pytest.fixture(params=["stream", "item"], autouse=True)
+def attention_kernel_flavour(request):
+    """Every test in this file runs with both decode-attention kernels."""
+    from morphserve_b200._lib import lib
+    assert lib.mkv_attn_configure(-1, -1, 1 if request.param == "stream" else 0, -1.0) == 0
+    yield request.param
+    lib.mkv_attn_configure(-1, -1, 1, -1.0)
+
+
 def _close(a, b):
     np.testing.assert_allclose(np.asarray(a, dtype=np.float64), np.asarray(b, dtype=np.float64), rtol=RTOL, atol=ATOL)
 
