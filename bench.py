@@ -42,6 +42,10 @@ WORKLOADS = {
     "llama2-7b-mha-decode": dict(cfg=2, B=64, Hq=32, Hkv=32, L=32, max_len=768, free_frac=0.30),
     # BASELINE configs[4], sequence-sharded form
     "codellama-34b-gqa-decode": dict(cfg=5, B=512, Hq=64, Hkv=8, L=48, max_len=1536, free_frac=0.05),
+    # BASELINE configs[4], head-sharded form: every rank holds Hkv/N KV heads (and their query heads) of ALL
+    # 512*N sequences; the attention outputs are all-gathered over NVLink (NCCL) after every layer
+    "codellama-34b-gqa-decode-headshard": dict(cfg=5, B=512, Hq=64, Hkv=8, L=48, max_len=1536, free_frac=0.05,
+                                               head_shard=True),
     # small case for profiler captures and CPU-side dry runs (pool ~1.3 GB: larger than L2)
     "small-gqa-decode": dict(cfg=9, B=64, Hq=32, Hkv=8, L=4, max_len=1536, free_frac=0.10),
     # the llama3-8b batch with 2 layers: same bytes per attention launch as the full workload, pool ~1.8 GB
@@ -62,11 +66,47 @@ def measured_peak():
 
 
 # ----------------------------------------------------------------------------
+# sharding (host logic; covered by the 2-rank gloo tests)
+# ----------------------------------------------------------------------------
+def shard_workload(w, rank, world):
+    """What one rank runs.  Sequence sharding (default): the rank's own batch of
+    w["B"] sequences, drawn from its own seed, all KV heads - no data crosses
+    ranks.  Head sharding: the global batch of w["B"]*world sequences (same seed
+    on every rank, so block tables agree) and the rank's contiguous slice of
+    Hkv/world KV heads with their Hq/world query heads."""
+    w = dict(w)
+    if w.get("head_shard"):
+        if w["Hkv"] % world != 0:
+            raise ValueError(f"head sharding needs num_kv_heads ({w['Hkv']}) divisible by the number of ranks ({world})")
+        w["B_global"] = w["B"] * world
+        w["B"] = w["B_global"]
+        w["Hq_global"], w["Hkv_global"] = w["Hq"], w["Hkv"]
+        w["Hq"], w["Hkv"] = w["Hq"] // world, w["Hkv"] // world
+        w["head_offset"] = rank * w["Hq"]
+        w["seed"] = 1000 * w["cfg"]
+        w["tokens_per_step"] = w["B_global"]          # whole job, counted once
+    else:
+        w["B_global"] = w["B"] * world
+        w["seed"] = 1000 * w["cfg"] + rank
+        w["tokens_per_step"] = w["B"] * world
+    return w
+
+
+def max_over_ranks(value, dist, device):
+    """Slowest rank's time (dist is torch.distributed or None)."""
+    if dist is None:
+        return float(value)
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+# ----------------------------------------------------------------------------
 # synthetic workload
 # ----------------------------------------------------------------------------
 def draw_lengths_and_tables(w, rank, growth_tokens):
     """Seeded lengths and a block table built from a shuffled free list."""
-    g = torch.Generator().manual_seed(1000 * w["cfg"] + rank)
+    g = torch.Generator().manual_seed(w.get("seed", 1000 * w["cfg"] + rank))
     lens = torch.randint(1, w["max_len"] + 1, (w["B"],), generator=g, dtype=torch.int64)
     need = (lens + BS - 1) // BS
     live = int(need.sum())
@@ -123,6 +163,14 @@ class DecodeJob:
         self.o = torch.zeros((L, B, Hq * D), dtype=torch.float16, device=device)
         self.nb = nb
         self._z = torch.zeros(0, dtype=torch.int32, device=device)
+        self.dist = None
+        if w.get("head_shard"):
+            import torch.distributed as dist
+            if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+                self.dist = dist
+                n = dist.get_world_size()
+                # gathered outputs, [rank, sequence, local heads * D]: the consumer reads the permuted view
+                self.o_full = torch.empty((L, n, B, Hq * D), dtype=torch.float16, device=device)
 
     def infer_state(self, seq_ids, lens_dev):
         B, Hkv = self.w["B"], self.w["Hkv"]
@@ -141,6 +189,8 @@ class DecodeJob:
         for layer in range(self.w["L"]):
             mk.store_kvcache(kn[layer], vn[layer], self.k_cache, self.v_cache, [], [], bt, mc, ec, st, layer)
             mk.paged_attention(q[layer], self.k_cache, self.v_cache, [], [], bt, mc, ec, st, layer, o[layer])
+            if self.dist is not None:      # head sharding: one all-gather of the output shards per layer
+                self.dist.all_gather_into_tensor(self.o_full[layer].view(-1, o[layer].shape[-1]), o[layer])
 
     def step_resident(self):
         """One decode step with every input already in HBM."""
@@ -156,24 +206,45 @@ class DecodeJob:
         self.hv = self.vn.cpu().pin_memory()
         self.ho = torch.empty(self.o.shape, dtype=torch.float16).pin_memory()
         self.dq, self.dk, self.dv = torch.empty_like(self.q), torch.empty_like(self.kn), torch.empty_like(self.vn)
+        L = self.w["L"]
+        self.s_in, self.s_out = torch.cuda.Stream(self.dev), torch.cuda.Stream(self.dev)
+        self.ev_in = [torch.cuda.Event() for _ in range(L)]
+        self.ev_out = [torch.cuda.Event() for _ in range(L)]
         return self.hq.nbytes + self.hk.nbytes + self.hv.nbytes + 8 * self.w["B"], self.ho.nbytes
 
     def step_host(self):
         """The same step as a caller with host data makes it: metadata from Python
-        lists (as the reference's LlamaModel.forward builds it), q/k/v from pinned
-        memory, the attention output read back."""
+        lists (as the reference's LlamaModel.forward builds it), the q/k/v of each
+        layer copied from pinned memory, the attention output of each layer read
+        back.  Copies run on two side streams, layer by layer, so that layer l+1's
+        inputs arrive and layer l-1's output leaves while layer l computes; the
+        step ends when the last output byte is on the host."""
+        main = torch.cuda.current_stream()
         self.lens_host += 1
         seq_ids = torch.tensor(self.seq_ids_list, dtype=torch.int32, device=self.dev)
         lens = torch.tensor(self.lens_host.tolist(), dtype=torch.int32, device=self.dev)
         self.lens_dev = lens
-        self.dq.copy_(self.hq, non_blocking=True)
-        self.dk.copy_(self.hk, non_blocking=True)
-        self.dv.copy_(self.hv, non_blocking=True)
+        L = self.w["L"]
+        with torch.cuda.stream(self.s_in):
+            for layer in range(L):
+                self.dq[layer].copy_(self.hq[layer], non_blocking=True)
+                self.dk[layer].copy_(self.hk[layer], non_blocking=True)
+                self.dv[layer].copy_(self.hv[layer], non_blocking=True)
+                self.ev_in[layer].record(self.s_in)
         self.bm.allocate_blocks_for_seqs(seq_ids, lens)
         st = self.infer_state(seq_ids, lens)
-        self.layers(st, self.dq, self.dk, self.dv, self.o)
-        self.ho.copy_(self.o, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        mk, mc, ec, bt = self.mk, self.model_config, self.engine_config, self.bm.block_table
+        for layer in range(L):
+            main.wait_event(self.ev_in[layer])
+            mk.store_kvcache(self.dk[layer], self.dv[layer], self.k_cache, self.v_cache, [], [], bt, mc, ec, st, layer)
+            mk.paged_attention(self.dq[layer], self.k_cache, self.v_cache, [], [], bt, mc, ec, st, layer,
+                               self.o[layer])
+            self.ev_out[layer].record(main)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(self.ev_out[layer])
+                self.ho[layer].copy_(self.o[layer], non_blocking=True)
+        self.s_out.synchronize()
+        main.synchronize()
 
     def kv_bytes_per_layer(self):
         return 2 * 2 * self.w["Hkv"] * D * int(self.lens_host.sum())
@@ -300,22 +371,25 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
-    w = WORKLOADS[args.workload]
     K, W = args.steps, max(args.warmup, 0)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    config = {"workload": args.workload, "baseline_config": w["cfg"], "batch_per_gpu": w["B"],
-              "num_q_heads": w["Hq"], "num_kv_heads": w["Hkv"], "head_dim": D, "block_size": BS,
-              "num_layers": w["L"], "context_len": f"uniform[1,{w['max_len']}] + 1 per step",
-              "sharding": f"sequence x{world}", "l2": "inputs_exceed_l2"}
+    base = WORKLOADS[args.workload]
+    w = shard_workload(base, rank, world)
+    head_shard = bool(base.get("head_shard"))
+    config = {"workload": args.workload, "baseline_config": base["cfg"], "global_batch": w["B_global"],
+              "batch_per_gpu": w["B"], "num_q_heads": base["Hq"], "num_kv_heads": base["Hkv"], "head_dim": D,
+              "block_size": BS, "num_layers": w["L"], "context_len": f"uniform[1,{w['max_len']}] + 1 per step",
+              "sharding": (f"kv heads x{world} + all-gather of o per layer" if head_shard else f"sequence x{world}"),
+              "l2": "inputs_exceed_l2"}
 
     if args.impl == "reference":
         if rank != 0:
             return
-        val, info = cpu_reference_sample(w, steps=K, warmup=min(W, 2))
+        val, info = cpu_reference_sample(base, steps=K, warmup=min(W, 2))
         line = {"impl": "reference", "metric": "decode_tokens_per_s", "value": val, "unit": "tokens/s",
-                "n_gpus": args.gpus, "steps": K, "warmup": W, "ms_per_step": 1e3 * w["B"] / val,
+                "n_gpus": args.gpus, "steps": K, "warmup": W, "ms_per_step": 1e3 * base["B"] / val,
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
                 "data": "synthetic", "config": config,
                 "cpu_baseline": dict(value=val, unit="tokens/s", **info),
@@ -356,11 +430,8 @@ def main():
         barrier()
     ms = e0.elapsed_time(e1)
     launches = sum(v - calls0.get(k, 0) for k, v in _lib.CALLS.items())
-    t = torch.tensor([ms], dtype=torch.float64, device=device)
-    if dist is not None:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_max = float(t.item())
-    value = world * w["B"] * K / (ms_max * 1e-3)
+    ms_max = max_over_ranks(ms, dist, device)
+    value = w["tokens_per_step"] * K / (ms_max * 1e-3)
 
     # ---- per-kernel timing for the roofline (attention only, append only) -----
     st = job.infer_state(job.seq_ids, job.lens_dev)
@@ -401,21 +472,20 @@ def main():
             job.step_host()
         e1.record()
         barrier()
-        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
-        if dist is not None:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e = {"value": world * w["B"] * Ke / (float(t.item()) * 1e-3), "unit": "tokens/s",
+        e2e_ms = max_over_ranks(e0.elapsed_time(e1), dist, device)
+        e2e = {"value": w["tokens_per_step"] * Ke / (e2e_ms * 1e-3), "unit": "tokens/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": Ke}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        v, info = cpu_reference_sample(w, steps=3, warmup=1)
+        v, info = cpu_reference_sample(base, steps=3, warmup=1)
         cpu = dict(value=v, unit="tokens/s", **info)
 
     if rank == 0:
         line = {
             "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K,
-            "warmup": max(W, 3), "ms_per_step": ms_max / K, "higher_is_better": True, "scaling": "weak",
+            "warmup": max(W, 3), "ms_per_step": ms_max / K, "higher_is_better": True,
+            "scaling": "weak",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": config,
             "kv_gbs_whole_step": world * kv_bytes / (ms_max * 1e-3) / 1e9,
             "roofline": {"kernel": "attn_decode_f16_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,

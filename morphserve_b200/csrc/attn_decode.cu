@@ -36,6 +36,7 @@ constexpr int kSortBins = 1024;
 constexpr unsigned kMagic = 0x4d4b5631u;  // "MKV1"
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kNegBig = -1e20f;       // the reference's mask / initial max
+constexpr int kClaimAhead = 3;          // tiles before the end of a unit at which the next one is claimed
 
 struct alignas(256) WsHeader {
     unsigned magic;
@@ -277,6 +278,75 @@ struct AttnParams {
     float *part_o;
 };
 
+// Merge of the split-KV partials of one (sequence, kv head): for each of the G query
+// heads, o = sum_s 2^(lse_s - m) o_s / sum_s 2^(lse_s - m).  Called by the warp that
+// arrived last.  Loads are issued in batches (2 heads x 4 chunks) before any of them
+// is used, so a merge costs a couple of L2 round trips instead of one per load.
+__device__ __forceinline__ void merge_splits(const AttnParams &p, int b, int hq0, int G, int nsplit, int64_t base,
+                                             int lane) {
+    constexpr int SB = 4;
+    for (int r = 0; r < G; r += 2) {
+        const bool two = (r + 1) < G;
+        const int hqa = hq0 + r, hqb = hq0 + (two ? r + 1 : r);
+        float ma = -INFINITY, mb = -INFINITY, wa = 0.f, wb = 0.f;
+        float4 acca = make_float4(0.f, 0.f, 0.f, 0.f), accb = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = 0; s0 < nsplit; s0 += SB) {
+            float la[SB], lb[SB];
+            float4 va[SB], vb[SB];
+#pragma unroll
+            for (int i = 0; i < SB; ++i) {
+                const bool ok = (s0 + i) < nsplit;
+                const int64_t row = base + (ok ? s0 + i : s0);
+                la[i] = __ldcg(p.lse + row * p.num_q_heads + hqa);
+                lb[i] = __ldcg(p.lse + row * p.num_q_heads + hqb);
+                va[i] = __ldcg(reinterpret_cast<const float4 *>(p.part_o + (row * p.num_q_heads + hqa) * kD + lane * 4));
+                vb[i] = __ldcg(reinterpret_cast<const float4 *>(p.part_o + (row * p.num_q_heads + hqb) * kD + lane * 4));
+                if (!ok) {
+                    la[i] = -INFINITY;
+                    lb[i] = -INFINITY;
+                }
+            }
+            float na = ma, nb = mb;
+#pragma unroll
+            for (int i = 0; i < SB; ++i) {
+                na = fmaxf(na, la[i]);
+                nb = fmaxf(nb, lb[i]);
+            }
+            const float sa = exp2f(ma - na), sb = exp2f(mb - nb);  // 0 on the first batch (m = -inf)
+            acca.x *= sa; acca.y *= sa; acca.z *= sa; acca.w *= sa; wa *= sa;
+            accb.x *= sb; accb.y *= sb; accb.z *= sb; accb.w *= sb; wb *= sb;
+#pragma unroll
+            for (int i = 0; i < SB; ++i) {
+                const float ea = exp2f(la[i] - na), eb = exp2f(lb[i] - nb);  // 0 for the padding entries
+                acca.x += ea * va[i].x; acca.y += ea * va[i].y; acca.z += ea * va[i].z; acca.w += ea * va[i].w;
+                accb.x += eb * vb[i].x; accb.y += eb * vb[i].y; accb.z += eb * vb[i].z; accb.w += eb * vb[i].w;
+                wa += ea;
+                wb += eb;
+            }
+            ma = na;
+            mb = nb;
+        }
+        {
+            const float inv = 1.f / wa;
+            __half2 h01 = __floats2half2_rn(acca.x * inv, acca.y * inv);
+            __half2 h23 = __floats2half2_rn(acca.z * inv, acca.w * inv);
+            uint2 pk;
+            pk.x = *reinterpret_cast<uint32_t *>(&h01);
+            pk.y = *reinterpret_cast<uint32_t *>(&h23);
+            *reinterpret_cast<uint2 *>(p.o + ((int64_t)b * p.num_q_heads + hqa) * kD + lane * 4) = pk;
+        }
+        if (two) {
+            const float inv = 1.f / wb;
+            __half2 h01 = __floats2half2_rn(accb.x * inv, accb.y * inv);
+            __half2 h23 = __floats2half2_rn(accb.z * inv, accb.w * inv);
+            uint2 pk;
+            pk.x = *reinterpret_cast<uint32_t *>(&h01);
+            pk.y = *reinterpret_cast<uint32_t *>(&h23);
+            *reinterpret_cast<uint2 *>(p.o + ((int64_t)b * p.num_q_heads + hqb) * kD + lane * 4) = pk;
+        }
+    }
+}
+
 struct WorkMeta {
     bool valid;
     int b, h, start, nblk, split, nsplit, prow, len;
@@ -310,16 +380,16 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
         if (!m.valid) return;
         const unsigned bc = idx / (unsigned)Hkv;
         m.h = (int)(idx - bc * (unsigned)Hkv);
-        const int4 it = __ldg(p.items + 2 * bc);
-        const int2 si = __ldg(p.split_info + it.x);
+        const int4 it = __ldg(p.items + 2 * bc);       // (batch index, first block, blocks, chunk index)
+        const int4 it1 = __ldg(p.items + 2 * bc + 1);  // (len, chunks, partial row, table row)
         m.b = it.x;
         m.start = it.y;
         m.nblk = it.z;
         m.split = it.w;
-        m.nsplit = si.x;
-        m.prow = si.y + it.w;
-        m.len = __ldg(p.seq_lens + it.x);
-        const int64_t row = __ldg(p.seq_ids + it.x);
+        m.nsplit = it1.y;
+        m.prow = it1.z;
+        m.len = it1.x;
+        const int64_t row = it1.w;
         m.table = p.block_table + row * p.table_stride + it.y;
         m.ids = (lane < m.nblk) ? __ldg(m.table + lane) : 0;
     };
@@ -392,7 +462,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
             }
         }
 
-        fetch(nxt);  // overlaps with the prologue loads in flight
+        // The next unit is claimed late (kClaimAhead tiles before this one ends, or now if it is
+        // that short): a warp that holds an unstarted unit for long hurts the longest-first balance.
+        const int claim_at = max(cur.nblk - kClaimAhead, 0);
 
         float oacc[16][4];
 #pragma unroll
@@ -404,6 +476,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
             __syncwarp();
             if (j + STAGES - 1 < cur.nblk) issue_tile(j + STAGES - 1);
             cp_async_commit();
+            if (j == claim_at) fetch(nxt);
 
             const uint32_t st = ring + (j % STAGES) * kStageBytes;
             // S = Q K^T   (16 heads x 16 tokens)
@@ -518,32 +591,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
             if (old == cur.nsplit - 1) {  // every chunk of this (sequence, kv head) is in the workspace
                 __threadfence();
                 if (lane == 0) *cnt = 0;
-                const int64_t base = cur.prow - cur.split;
-                for (int r = 0; r < G; ++r) {
-                    const int hq = hq0 + r;
-                    float mx = -INFINITY;
-                    for (int s = 0; s < cur.nsplit; ++s)
-                        mx = fmaxf(mx, __ldcg(p.lse + (base + s) * p.num_q_heads + hq));
-                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                    float wsum = 0.f;
-                    for (int s = 0; s < cur.nsplit; ++s) {
-                        const float w = exp2f(__ldcg(p.lse + (base + s) * p.num_q_heads + hq) - mx);
-                        const float4 v = __ldcg(reinterpret_cast<const float4 *>(
-                            p.part_o + ((base + s) * p.num_q_heads + hq) * kD + lane * 4));
-                        acc.x += w * v.x;
-                        acc.y += w * v.y;
-                        acc.z += w * v.z;
-                        acc.w += w * v.w;
-                        wsum += w;
-                    }
-                    const float inv = 1.f / wsum;
-                    __half2 h01 = __floats2half2_rn(acc.x * inv, acc.y * inv);
-                    __half2 h23 = __floats2half2_rn(acc.z * inv, acc.w * inv);
-                    uint2 pk;
-                    pk.x = *reinterpret_cast<uint32_t *>(&h01);
-                    pk.y = *reinterpret_cast<uint32_t *>(&h23);
-                    *reinterpret_cast<uint2 *>(p.o + ((int64_t)cur.b * p.num_q_heads + hq) * kD + lane * 4) = pk;
-                }
+                merge_splits(p, cur.b, hq0, G, cur.nsplit, (int64_t)cur.prow - cur.split, lane);
             }
         }
     }
@@ -596,14 +644,17 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_stream_kernel(c
     const int v_tok = (((lane >> 3) & 1) << 3) + (lane & 7);
     const int v_half = lane >> 4;
 
+    int l_nblk = 0, l_pos = 0;  // loader side: blocks of its current item, next block to issue
+
     // ---- next-item pipeline: 0 claim -> 1 descriptor -> 2 block ids -> 3 ready ; 4 = no work left
     int pstate = 0;
     unsigned p_idx = 0;
     int4 n0 = make_int4(0, 0, 0, 0), n1 = make_int4(0, 0, 0, 0);  // (b,start,nblk,split) (len,nsplit,prow,row)
     int n_h = 0, n_ids = 0, n_ids2 = 0;
     const int32_t *n_table = nullptr;
-    auto advance = [&]() {
+    auto advance = [&](bool force) {
         if (pstate == 0) {
+            if (l_nblk - l_pos > kClaimAhead + 1 && !force) return;  // claim late: keeps the longest-first balance
             if (lane == 0) p_idx = atomicAdd(&hdr->work_counter, 1u);
             pstate = 1;
         } else if (pstate == 1) {
@@ -626,7 +677,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_stream_kernel(c
     };
 
     // ---- loader side
-    int l_nblk = 0, l_pos = 0, l_win = 0, l_ids = 0, l_ids2 = 0;
+    int l_win = 0, l_ids = 0, l_ids2 = 0;
     const int32_t *l_table = nullptr;
     int64_t l_head_off = 0;
     bool l_done = false;
@@ -652,7 +703,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_stream_kernel(c
     auto loader_has_tile = [&]() -> bool {
         if (l_done) return false;
         if (l_pos < l_nblk) return true;
-        while (pstate < 3) advance();  // normally ready long before it is needed
+        while (pstate < 3) advance(true);  // normally ready before it is needed
         if (pstate == 4) {
             l_done = true;
             return false;
@@ -720,7 +771,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_stream_kernel(c
             ++issued;
         }
         cp_async_commit();
-        advance();
+        advance(false);
     }
 
 #pragma unroll 1
@@ -732,7 +783,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_stream_kernel(c
             ++issued;
         }
         cp_async_commit();
-        advance();
+        advance(false);
 
         if (c_pos == c_nblk) {  // first tile of the next item
             const int4 d0 = dq[(cq % QD) * 2];
@@ -865,32 +916,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_stream_kernel(c
                 if (old == c_nsplit - 1) {
                     __threadfence();
                     if (lane == 0) *cnt = 0;
-                    const int64_t base = c_prow - c_split;
-                    for (int r = 0; r < G; ++r) {
-                        const int hq = hq0 + r;
-                        float mx = -INFINITY;
-                        for (int s = 0; s < c_nsplit; ++s)
-                            mx = fmaxf(mx, __ldcg(p.lse + (base + s) * p.num_q_heads + hq));
-                        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                        float wsum = 0.f;
-                        for (int s = 0; s < c_nsplit; ++s) {
-                            const float w = exp2f(__ldcg(p.lse + (base + s) * p.num_q_heads + hq) - mx);
-                            const float4 v = __ldcg(reinterpret_cast<const float4 *>(
-                                p.part_o + ((base + s) * p.num_q_heads + hq) * kD + lane * 4));
-                            acc.x += w * v.x;
-                            acc.y += w * v.y;
-                            acc.z += w * v.z;
-                            acc.w += w * v.w;
-                            wsum += w;
-                        }
-                        const float inv = 1.f / wsum;
-                        __half2 h01 = __floats2half2_rn(acc.x * inv, acc.y * inv);
-                        __half2 h23 = __floats2half2_rn(acc.z * inv, acc.w * inv);
-                        uint2 pk;
-                        pk.x = *reinterpret_cast<uint32_t *>(&h01);
-                        pk.y = *reinterpret_cast<uint32_t *>(&h23);
-                        *reinterpret_cast<uint2 *>(p.o + ((int64_t)c_b * p.num_q_heads + hq) * kD + lane * 4) = pk;
-                    }
+                    merge_splits(p, c_b, hq0, G, c_nsplit, (int64_t)c_prow - c_split, lane);
                 }
             }
         }
@@ -994,7 +1020,7 @@ __global__ void attn_decode_plain_kernel(const __grid_constant__ PoolView pool, 
 // ------------------------------------------------------------------ host side
 struct AttnConfig {
     int warps = 8, stages = 3;
-    int stream = 1;  // 1 = continuous tile stream kernel, 0 = per-item ring kernel
+    int stream = 0;  // 1 = continuous tile stream kernel, 0 = per-item ring kernel (default: measured faster)
     bool init = false;
 };
 static AttnConfig g_attn_cfg;

@@ -23,7 +23,7 @@ def attention_kernel_flavour(request):
     from morphserve_b200._lib import lib
     assert lib.mkv_attn_configure(-1, -1, 1 if request.param == "stream" else 0, -1.0) == 0
     yield request.param
-    lib.mkv_attn_configure(-1, -1, 1, -1.0)
+    lib.mkv_attn_configure(-1, -1, 0, -1.0)
 
 
 def _close(a, b):
