@@ -46,6 +46,12 @@ WORKLOADS = {
     # 512*N sequences; the attention outputs are all-gathered over NVLink (NCCL) after every layer
     "codellama-34b-gqa-decode-headshard": dict(cfg=5, B=512, Hq=64, Hkv=8, L=48, max_len=1536, free_frac=0.05,
                                                head_shard=True),
+    # BASELINE configs[3] pool shape: compaction of a 16384-block pool down to 10240 (copy + remap timing only)
+    "kv-resize": dict(cfg=4, resize=True, L=32, Hq=32, Hkv=8, B=128, max_len=1536, nb_org=8192, chunk=1024,
+                      n_chunks=8, release=6),
+    # the same with 4 layers (pool 4 GB) for profiler captures
+    "kv-resize-small": dict(cfg=4, resize=True, L=4, Hq=32, Hkv=8, B=128, max_len=1536, nb_org=8192, chunk=1024,
+                            n_chunks=8, release=6),
     # small case for profiler captures and CPU-side dry runs (pool ~1.3 GB: larger than L2)
     "small-gqa-decode": dict(cfg=9, B=64, Hq=32, Hkv=8, L=4, max_len=1536, free_frac=0.10),
     # the llama3-8b batch with 2 layers: same bytes per attention launch as the full workload, pool ~1.8 GB
@@ -53,6 +59,11 @@ WORKLOADS = {
 }
 D, BS = 128, 16
 FALLBACK_HBM_GBS = 6650.0
+# DRAM bytes (read + write) per attention launch divided by the algorithmic K/V bytes, from the ncu capture
+# summarised in profiles/attn_decode_f16_kernel__llama3-8b-gqa-decode-2layer.md (same batch and bytes per launch as
+# llama3-8b-gqa-decode; 863.6 MB moved for 851 MB of K/V).  Traffic grows with the units processed, so the
+# ratio is applied to the live byte count of the timed launches.
+NCU_TRAFFIC_RATIO = {"llama3-8b-gqa-decode": 1.0148, "llama3-8b-gqa-decode-2layer": 1.0148}
 
 
 def measured_peak():
@@ -361,6 +372,63 @@ def cpu_reference_sample(w, steps, warmup, layers_sampled=2, seqs_sampled=None):
 
 
 # ----------------------------------------------------------------------------
+# elastic resize: compaction copy + block-table remap
+# ----------------------------------------------------------------------------
+def resize_bench(w, K, W, device):
+    """A pool of nb_org + n_chunks*chunk blocks with 60 % of its blocks live at seeded
+    random positions is compacted below the boundary that frees `release` chunks
+    (plan + block copies + table remap, one call), K times from the same state."""
+    from types import SimpleNamespace
+
+    import morphserve_b200 as mk
+    from morphserve_b200.server import memory_utils as MU
+    L, Hkv = w["L"], w["Hkv"]
+    nb_org, chunk, n_chunks = w["nb_org"], w["chunk"], w["n_chunks"]
+    total = nb_org + chunk * n_chunks
+    target = nb_org + (n_chunks - w["release"]) * chunk
+    g = torch.Generator().manual_seed(1000 * w["cfg"])
+    shape = lambda n: (n, L, Hkv, BS, D)                                     # noqa: E731
+    model = SimpleNamespace(k_cache=torch.randn(shape(nb_org), dtype=torch.float16, device=device),
+                            v_cache=torch.randn(shape(nb_org), dtype=torch.float16, device=device),
+                            k_cache_new=[], v_cache_new=[], kv_cache_new_block_size=0,
+                            gpu_block_manager=mk.BlockManager("GPU", nb_org, 4096, 128, BS))
+    engine = SimpleNamespace(model=model, scheduler=SimpleNamespace(num_gpu_blocks=nb_org))
+    for _ in range(n_chunks):
+        MU.attach_kvcache_chunk(engine, torch.randn(shape(chunk), dtype=torch.float16, device=device),
+                                torch.randn(shape(chunk), dtype=torch.float16, device=device))
+    bm = model.gpu_block_manager
+    # 60 % live blocks owned by sequences of 48 blocks each, positions from a seeded permutation
+    n_live = int(0.6 * total)
+    perm = torch.randperm(total, generator=g)[:n_live]
+    per_seq = 48
+    n_seq = n_live // per_seq
+    table = torch.full((4096, 128), -1, dtype=torch.int32)
+    table[:n_seq, :per_seq] = perm[: n_seq * per_seq].view(n_seq, per_seq).to(torch.int32)
+    counts = torch.zeros(4096, dtype=torch.int32)
+    counts[:n_seq] = per_seq
+    free = torch.ones(total, dtype=torch.bool)
+    free[perm[: n_seq * per_seq]] = False
+    state = (table.to(device), counts.to(device), free.to(device))
+    block_bytes = 2 * L * Hkv * BS * D * 2
+    times, moved = [], 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for it in range(W + K):
+        bm.block_table.copy_(state[0])
+        bm.num_seq_allocated_blocks.copy_(state[1])
+        bm.is_block_free = state[2].clone()
+        torch.cuda.synchronize()
+        e0.record()
+        moved = MU.compact_kvcache(engine, target)
+        e1.record()
+        torch.cuda.synchronize()
+        if it >= W:
+            times.append(e0.elapsed_time(e1))
+    ms = statistics.median(times)
+    return {"moved_blocks": moved, "ms_per_compaction": ms, "copy_bytes": 2 * moved * block_bytes,
+            "copy_gbs_incl_plan_and_remap": 2 * moved * block_bytes / (ms * 1e-3) / 1e9}
+
+
+# ----------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -376,6 +444,23 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     base = WORKLOADS[args.workload]
+    if base.get("resize"):
+        assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+        torch.cuda.set_device(local_rank)
+        if rank == 0:
+            r = resize_bench(base, K, max(W, 3), torch.device("cuda", local_rank))
+            peak, peak_kind = measured_peak()
+            print(json.dumps({"metric": "compaction_copy_gbs", "value": r["copy_gbs_incl_plan_and_remap"],
+                              "unit": "GB/s", "n_gpus": 1, "steps": K, "warmup": max(W, 3),
+                              "ms_per_step": r["ms_per_compaction"], "higher_is_better": True, "dtype": "u8",
+                              "data": "synthetic", "config": {"workload": args.workload, **{k: v for k, v in base.items()
+                                                                                          if k != "resize"}},
+                              "roofline": {"kernel": "copy_blocks_kernel", "bound": "hbm",
+                                           "achieved": r["copy_gbs_incl_plan_and_remap"], "peak": peak,
+                                           "peak_kind": peak_kind, "unit": "GB/s",
+                                           "frac": r["copy_gbs_incl_plan_and_remap"] / peak, "traffic": None},
+                              "resize": r}))
+        return
     w = shard_workload(base, rank, world)
     head_shard = bool(base.get("head_shard"))
     config = {"workload": args.workload, "baseline_config": base["cfg"], "global_batch": w["B_global"],
@@ -404,6 +489,8 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            del os.environ["NCCL_DEBUG"]        # keeps NCCL's banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=device)
 
     def barrier():
@@ -489,7 +576,9 @@ def main():
             "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": config,
             "kv_gbs_whole_step": world * kv_bytes / (ms_max * 1e-3) / 1e9,
             "roofline": {"kernel": "attn_decode_f16_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
-                         "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": (NCU_TRAFFIC_RATIO[args.workload] * attn_bytes
+                                     if args.workload in NCU_TRAFFIC_RATIO else None),
                          "algorithmic_bytes_per_launch": attn_bytes, "ms_per_launch": attn_ms,
                          "append_ms_per_launch": append_ms},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks.summary(),
