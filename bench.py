@@ -52,6 +52,8 @@ WORKLOADS = {
     # the same with 4 layers (pool 4 GB) for profiler captures
     "kv-resize-small": dict(cfg=4, resize=True, L=4, Hq=32, Hkv=8, B=128, max_len=1536, nb_org=8192, chunk=1024,
                             n_chunks=8, release=6),
+    # llama3-8b batch, 2 layers, every context exactly 768 tokens (no length spread): isolates scheduling effects
+    "llama3-8b-gqa-decode-2layer-uniform": dict(cfg=3, B=256, Hq=32, Hkv=8, L=2, min_len=768, max_len=768, free_frac=0.10),
     # small case for profiler captures and CPU-side dry runs (pool ~1.3 GB: larger than L2)
     "small-gqa-decode": dict(cfg=9, B=64, Hq=32, Hkv=8, L=4, max_len=1536, free_frac=0.10),
     # the llama3-8b batch with 2 layers: same bytes per attention launch as the full workload, pool ~1.8 GB
@@ -118,7 +120,7 @@ def max_over_ranks(value, dist, device):
 def draw_lengths_and_tables(w, rank, growth_tokens):
     """Seeded lengths and a block table built from a shuffled free list."""
     g = torch.Generator().manual_seed(w.get("seed", 1000 * w["cfg"] + rank))
-    lens = torch.randint(1, w["max_len"] + 1, (w["B"],), generator=g, dtype=torch.int64)
+    lens = torch.randint(w.get("min_len", 1), w["max_len"] + 1, (w["B"],), generator=g, dtype=torch.int64)
     need = (lens + BS - 1) // BS
     live = int(need.sum())
     growth = w["B"] * ((growth_tokens + BS - 1) // BS + 1)
@@ -236,16 +238,21 @@ class DecodeJob:
         lens = torch.tensor(self.lens_host.tolist(), dtype=torch.int32, device=self.dev)
         self.lens_dev = lens
         L = self.w["L"]
-        with torch.cuda.stream(self.s_in):
-            for layer in range(L):
+
+        def copy_in(layer):
+            with torch.cuda.stream(self.s_in):
                 self.dq[layer].copy_(self.hq[layer], non_blocking=True)
                 self.dk[layer].copy_(self.hk[layer], non_blocking=True)
                 self.dv[layer].copy_(self.hv[layer], non_blocking=True)
                 self.ev_in[layer].record(self.s_in)
+
+        copy_in(0)
         self.bm.allocate_blocks_for_seqs(seq_ids, lens)
         st = self.infer_state(seq_ids, lens)
         mk, mc, ec, bt = self.mk, self.model_config, self.engine_config, self.bm.block_table
         for layer in range(L):
+            if layer + 1 < L:
+                copy_in(layer + 1)                   # next layer's inputs travel while this layer computes
             main.wait_event(self.ev_in[layer])
             mk.store_kvcache(self.dk[layer], self.dv[layer], self.k_cache, self.v_cache, [], [], bt, mc, ec, st, layer)
             mk.paged_attention(self.dq[layer], self.k_cache, self.v_cache, [], [], bt, mc, ec, st, layer,

@@ -36,7 +36,7 @@ constexpr int kSortBins = 1024;
 constexpr unsigned kMagic = 0x4d4b5631u;  // "MKV1"
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kNegBig = -1e20f;       // the reference's mask / initial max
-constexpr int kClaimAhead = 3;          // tiles before the end of a unit at which the next one is claimed
+constexpr int kClaimAhead = 6;          // tiles before the end of a unit at which the next one is claimed
 
 struct alignas(256) WsHeader {
     unsigned magic;
@@ -372,26 +372,40 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
     const unsigned total_units = (unsigned)hdr->n_items * (unsigned)Hkv;
     const bool row0 = g < G, row1 = (g + 8) < G;
 
-    auto fetch = [&](WorkMeta &m) {
-        unsigned idx = 0;
-        if (lane == 0) idx = atomicAdd(&hdr->work_counter, 1u);
-        idx = __shfl_sync(0xffffffffu, idx, 0);
-        m.valid = idx < total_units;
-        if (!m.valid) return;
-        const unsigned bc = idx / (unsigned)Hkv;
-        m.h = (int)(idx - bc * (unsigned)Hkv);
-        const int4 it = __ldg(p.items + 2 * bc);       // (batch index, first block, blocks, chunk index)
-        const int4 it1 = __ldg(p.items + 2 * bc + 1);  // (len, chunks, partial row, table row)
-        m.b = it.x;
-        m.start = it.y;
-        m.nblk = it.z;
-        m.split = it.w;
-        m.nsplit = it1.y;
-        m.prow = it1.z;
-        m.len = it1.x;
-        const int64_t row = it1.w;
-        m.table = p.block_table + row * p.table_stride + it.y;
-        m.ids = (lane < m.nblk) ? __ldg(m.table + lane) : 0;
+    // Claiming the next unit is a chain of three dependent global accesses (counter ->
+    // unit descriptor -> block ids).  It is cut into three steps that run one per tile
+    // iteration, so that each step finds the previous one's result already landed.
+    int fstage = 0;  // 0 claim, 1 read descriptor, 2 read block ids, 3 done
+    unsigned f_idx = 0;
+    int4 f_it = make_int4(0, 0, 0, 0), f_it1 = make_int4(0, 0, 0, 0);
+    auto fetch_step = [&](WorkMeta &m) {
+        if (fstage == 0) {
+            if (lane == 0) f_idx = atomicAdd(&hdr->work_counter, 1u);
+            fstage = 1;
+        } else if (fstage == 1) {
+            const unsigned idx = __shfl_sync(0xffffffffu, f_idx, 0);
+            m.valid = idx < total_units;
+            if (!m.valid) {
+                fstage = 3;
+            } else {
+                const unsigned bc = idx / (unsigned)Hkv;
+                m.h = (int)(idx - bc * (unsigned)Hkv);
+                f_it = __ldg(p.items + 2 * bc);       // (batch index, first block, blocks, chunk index)
+                f_it1 = __ldg(p.items + 2 * bc + 1);  // (len, chunks, partial row, table row)
+                fstage = 2;
+            }
+        } else if (fstage == 2) {
+            m.b = f_it.x;
+            m.start = f_it.y;
+            m.nblk = f_it.z;
+            m.split = f_it.w;
+            m.len = f_it1.x;
+            m.nsplit = f_it1.y;
+            m.prow = f_it1.z;
+            m.table = p.block_table + (int64_t)f_it1.w * p.table_stride + f_it.y;
+            m.ids = (lane < m.nblk) ? __ldg(m.table + lane) : 0;
+            fstage = 3;
+        }
     };
 
     // lane-constant pieces of the shared-memory addressing (bytes inside a 4 KiB tile)
@@ -402,11 +416,41 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
     const int v_tok = (((lane >> 3) & 1) << 3) + (lane & 7);
     const int v_half = lane >> 4;
 
+    // One tile (K and V of one block for kv head `head_off`) into a ring stage.
+    auto issue_raw = [&](int64_t blk, int64_t head_off, uint32_t st) {
+        if (!block_in_pool(p.pool, blk)) {
+            if (lane == 0) atomicOr(&hdr->error_flags, 1);
+            blk = 0;
+        }
+        int seg;
+        int64_t brow;
+        locate_block(p.pool, blk, seg, brow);
+        const char *kt = p.pool.k_base[seg] + brow * p.pool.block_bytes + head_off;
+        const char *vt = p.pool.v_base[seg] + brow * p.pool.block_bytes + head_off;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int id = i * 32 + lane;           // 16-byte piece of the tile
+            const int r = id >> 4, c = id & 15;     // token row, piece in the row
+            const uint32_t off = r * 256 + ((c ^ (r & 7)) << 4);
+            cp_async16(st + off, kt + id * 16);
+            cp_async16(st + kTileBytes + off, vt + id * 16);
+        }
+    };
+
+    // The ring is continuous across units: tile j of a unit sits in stage (ring_pos + j) % STAGES,
+    // and while a unit consumes its last STAGES-1 tiles the freed stages already receive the
+    // first tiles of the next unit (`pre` of them), so the ring never runs empty at a boundary.
+    unsigned ring_pos = 0;
+    int pre = 0;
+
     WorkMeta nxt;
-    fetch(nxt);
+    nxt.valid = false;
+    while (fstage < 3) fetch_step(nxt);
     while (nxt.valid) {
         const WorkMeta cur = nxt;
-        __syncwarp();  // the previous item's ldmatrix reads are done before the ring is refilled
+        const int pre_cur = pre;
+        pre = 0;
+        __syncwarp();  // the previous unit's ldmatrix reads are done before its stages are refilled
 
         // ---- tile loader ------------------------------------------------------
         int ids_cur = cur.ids;
@@ -420,31 +464,16 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
                 const int nj = (win + 1) * 32 + lane;
                 ids_nxt = (nj < cur.nblk) ? __ldg(cur.table + nj) : 0;
             }
-            int64_t blk = __shfl_sync(0xffffffffu, ids_cur, j & 31);
-            if (!block_in_pool(p.pool, blk)) {
-                if (lane == 0) atomicOr(&hdr->error_flags, 1);
-                blk = 0;
-            }
-            int seg;
-            int64_t brow;
-            locate_block(p.pool, blk, seg, brow);
-            const char *kt = p.pool.k_base[seg] + brow * p.pool.block_bytes + head_off;
-            const char *vt = p.pool.v_base[seg] + brow * p.pool.block_bytes + head_off;
-            const uint32_t st = ring + (j % STAGES) * kStageBytes;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int id = i * 32 + lane;           // 16-byte piece of the tile
-                const int r = id >> 4, c = id & 15;     // token row, piece in the row
-                const uint32_t off = r * 256 + ((c ^ (r & 7)) << 4);
-                cp_async16(st + off, kt + id * 16);
-                cp_async16(st + kTileBytes + off, vt + id * 16);
-            }
+            const int64_t blk = __shfl_sync(0xffffffffu, ids_cur, j & 31);
+            issue_raw(blk, head_off, ring + ((ring_pos + (unsigned)j) % STAGES) * kStageBytes);
         };
 
 #pragma unroll
         for (int s = 0; s < STAGES - 1; ++s) {
-            if (s < cur.nblk) issue_tile(s);
-            cp_async_commit();
+            if (s >= pre_cur) {  // tiles below pre_cur were issued during the previous unit's tail
+                if (s < cur.nblk) issue_tile(s);
+                cp_async_commit();
+            }
         }
 
         // ---- Q fragments (A operand, rows = query heads of the group) -----------
@@ -474,11 +503,20 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
         for (int j = 0; j < cur.nblk; ++j) {
             cp_async_wait<STAGES - 2>();
             __syncwarp();
-            if (j + STAGES - 1 < cur.nblk) issue_tile(j + STAGES - 1);
+            if (j + STAGES - 1 < cur.nblk) {
+                issue_tile(j + STAGES - 1);
+            } else if (fstage == 3 && nxt.valid && pre < nxt.nblk) {
+                // nothing left to fetch for this unit: start on the next one (pre <= j+STAGES-1-nblk < STAGES-1)
+                const int64_t blk = __shfl_sync(0xffffffffu, nxt.ids, pre);
+                issue_raw(blk, ((int64_t)p.cur_layer * Hkv + nxt.h) * kTileBytes,
+                          ring + ((ring_pos + (unsigned)(cur.nblk + pre)) % STAGES) * kStageBytes);
+                ++pre;
+            }
             cp_async_commit();
-            if (j == claim_at) fetch(nxt);
+            if (j == claim_at) fstage = 0;
+            if (j >= claim_at && fstage < 3) fetch_step(nxt);
 
-            const uint32_t st = ring + (j % STAGES) * kStageBytes;
+            const uint32_t st = ring + ((ring_pos + (unsigned)j) % STAGES) * kStageBytes;
             // S = Q K^T   (16 heads x 16 tokens)
             float sc[2][4];
 #pragma unroll
@@ -546,7 +584,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
                 mma_16816(oacc[2 * np + 1], pa, b2, b3);
             }
         }
-        cp_async_wait<0>();
+        ring_pos = (ring_pos + (unsigned)cur.nblk) % STAGES;
+        while (fstage < 3) fetch_step(nxt);  // short unit: finish the claim now
 
         // ---- epilogue ---------------------------------------------------------
         l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
@@ -595,6 +634,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
             }
         }
     }
+    cp_async_wait<0>();
     // the last worker to run dry re-arms the counters for the next launch
     if (lane == 0) {
         const unsigned workers = gridDim.x * WARPS;
