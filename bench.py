@@ -445,6 +445,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-fused-append", action="store_true",
+                    help="launch the decode KV append as its own kernel (the reference's two-call structure) "
+                         "instead of fusing it into the attention launch")
     args = ap.parse_args()
     K, W = args.steps, max(args.warmup, 0)
     rank = int(os.environ.get("RANK", "0"))
@@ -505,7 +508,10 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    import morphserve_b200
     from morphserve_b200 import _lib
+    morphserve_b200.set_fused_decode_append(not args.no_fused_append)
+    config["decode_append"] = "own launch" if args.no_fused_append else "fused into the attention launch"
     job = DecodeJob(w, rank, growth_tokens=2 * (K + W) + 16, device=device)
 
     # ---- leg 1: inputs resident in HBM ----------------------------------------

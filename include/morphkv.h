@@ -117,13 +117,28 @@ int mkv_paged_attention_decode(
     void *workspace, size_t workspace_bytes);
 
 /*
+ * mkv_store_kv_decode + mkv_paged_attention_decode of one layer in ONE launch:
+ * the warp that attends over the block holding token len-1 of a (sequence, kv
+ * head) also writes that token's new K/V row (k_new, v_new: device
+ * [batch, num_kv_heads, head_dim]) into the pool and into its staged tile.
+ * Same results as the two separate calls (the append is bit-exact); saves one
+ * launch per layer.  Shapes outside the fast path fall back to the two kernels.
+ * Replaces the pair of call sites worker/layers/transformer_layer.py:117-126 and
+ * :181-187 when the caller opts in.
+ */
+int mkv_paged_attention_decode_append(
+    int device, void *stream, const void *q, void *o, const void *k_new, const void *v_new,
+    const mkv_pool *pool, const int32_t *block_table, int64_t table_stride, const int32_t *seq_ids,
+    const int32_t *seq_lens, int batch, int num_q_heads, int cur_layer, float softmax_scale,
+    int max_blocks_per_seq_in_batch, void *workspace, size_t workspace_bytes);
+
+/*
  * Tuning knobs of the decode kernel (process-wide; not needed for normal use):
- * warps per SM and ring stages (values <= 0 keep the current ones), kernel
- * flavour (1 = continuous tile stream, 0 = per-item ring, < 0 keeps), and the
+ * warps per SM and ring stages (values <= 0 keep the current ones) and the
  * number of work units planned per worker warp (<= 0 keeps).  Changing the item
  * factor changes mkv_attn_workspace_bytes: re-query it and plan again.
  */
-int mkv_attn_configure(int warps, int stages, int stream_kernel, double item_factor);
+int mkv_attn_configure(int warps, int stages, double item_factor);
 
 /*
  * Copies the device-side error word of a workspace to `*flags` (synchronises the

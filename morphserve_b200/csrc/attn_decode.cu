@@ -261,6 +261,8 @@ struct AttnParams {
     PoolView pool;
     const __half *q;
     __half *o;
+    const __half *k_new;  // fused append: [batch, Hkv, D] rows of the newest token, or nullptr
+    const __half *v_new;
     const int32_t *block_table;
     int64_t table_stride;
     const int32_t *seq_ids;
@@ -491,6 +493,18 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
             }
         }
 
+        // Fused append: the unit that holds the block of token len-1 also stores that token's new
+        // K/V row.  No other unit reads that (sequence, kv head) tile in this launch, so the row is
+        // patched into the staged tile and written to the pool by this warp alone.
+        // lanes 0-15 carry the 16 pieces of the K row, lanes 16-31 those of the V row.
+        const int new_blk = (cur.len - 1) >> 4;  // logical block of the newest token
+        const bool has_new = p.k_new != nullptr && new_blk >= cur.start && new_blk < cur.start + cur.nblk;
+        uint4 new_row = make_uint4(0u, 0u, 0u, 0u);
+        if (has_new) {
+            const __half *src = (lane < 16 ? p.k_new : p.v_new) + ((int64_t)cur.b * Hkv + cur.h) * kD + (lane & 15) * 8;
+            new_row = __ldg(reinterpret_cast<const uint4 *>(src));
+        }
+
         // The next unit is claimed late (kClaimAhead tiles before this one ends, or now if it is
         // that short): a warp that holds an unstarted unit for long hurts the longest-first balance.
         const int claim_at = max(cur.nblk - kClaimAhead, 0);
@@ -517,6 +531,24 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
             if (j >= claim_at && fstage < 3) fetch_step(nxt);
 
             const uint32_t st = ring + ((ring_pos + (unsigned)j) % STAGES) * kStageBytes;
+            if (has_new && cur.start + j == new_blk) {
+                const int slot = (cur.len - 1) & 15, c = lane & 15;
+                const uint32_t off = (lane < 16 ? 0 : kTileBytes) + slot * 256;
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(st + off + ((c ^ (slot & 7)) << 4)),
+                             "r"(new_row.x), "r"(new_row.y), "r"(new_row.z), "r"(new_row.w)
+                             : "memory");
+                // the same row into the pool, for the steps to come
+                const int64_t blk = __ldg(cur.table + j);
+                if (block_in_pool(p.pool, blk)) {
+                    int seg;
+                    int64_t brow;
+                    locate_block(p.pool, blk, seg, brow);
+                    char *dst = (lane < 16 ? p.pool.k_base[seg] : p.pool.v_base[seg]) + brow * p.pool.block_bytes +
+                                head_off + slot * 256 + c * 16;
+                    *reinterpret_cast<uint4 *>(dst) = new_row;
+                }
+                __syncwarp();
+            }
             // S = Q K^T   (16 heads x 16 tokens)
             float sc[2][4];
 #pragma unroll
@@ -646,332 +678,6 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
     }
 }
 
-// ------------------------------------------------------------------ decode kernel, continuous tile stream
-//
-// Same arithmetic as attn_decode_f16_kernel, different pipeline.  There the ring of
-// a warp drains at the end of every work item and refills after the next item's
-// metadata has been fetched, which leaves no loads in flight for a few microseconds
-// per item.  Here every warp keeps ONE stream of tiles running across item
-// boundaries: the loader side walks ahead into the next item(s) while the consumer
-// side finishes the current one, the next item's descriptor is claimed and fetched
-// by a small state machine that advances one step per tile (so none of its loads is
-// waited for), and the query fragments of an item are prefetched into registers
-// when the loader enters the item.  Item descriptors travel from the loader side to
-// the consumer side through a per-warp queue in shared memory.
-template <int WARPS, int STAGES>
-__global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_stream_kernel(const __grid_constant__ AttnParams p) {
-    extern __shared__ __align__(1024) uint8_t smem[];
-    constexpr int QD = STAGES + 1;                                  // descriptor queue depth
-    constexpr int kWarpBytes = STAGES * kStageBytes + QD * 32;
-    const int lane = threadIdx.x & 31;
-    const int warp = threadIdx.x >> 5;
-    const int g = lane >> 2, t = lane & 3;
-    uint8_t *wbase = smem + warp * kWarpBytes;
-    const uint32_t ring = smem_u32(wbase);
-    int4 *dq = reinterpret_cast<int4 *>(wbase + STAGES * kStageBytes);  // [QD][2]
-
-    WsHeader *hdr = p.hdr;
-    if (hdr->magic != kMagic || hdr->batch != p.batch) {
-        if (threadIdx.x == 0) atomicOr(&hdr->error_flags, 2);
-        return;
-    }
-    const int Hkv = p.pool.num_kv_heads;
-    const int G = p.group;
-    const unsigned total_units = (unsigned)hdr->n_items * (unsigned)Hkv;
-    const bool row0 = g < G, row1 = (g + 8) < G;
-    const int k_tok = ((lane >> 4) << 3) + (lane & 7);
-    const int k_half = (lane >> 3) & 1;
-    const int v_tok = (((lane >> 3) & 1) << 3) + (lane & 7);
-    const int v_half = lane >> 4;
-
-    int l_nblk = 0, l_pos = 0;  // loader side: blocks of its current item, next block to issue
-
-    // ---- next-item pipeline: 0 claim -> 1 descriptor -> 2 block ids -> 3 ready ; 4 = no work left
-    int pstate = 0;
-    unsigned p_idx = 0;
-    int4 n0 = make_int4(0, 0, 0, 0), n1 = make_int4(0, 0, 0, 0);  // (b,start,nblk,split) (len,nsplit,prow,row)
-    int n_h = 0, n_ids = 0, n_ids2 = 0;
-    const int32_t *n_table = nullptr;
-    auto advance = [&](bool force) {
-        if (pstate == 0) {
-            if (l_nblk - l_pos > kClaimAhead + 1 && !force) return;  // claim late: keeps the longest-first balance
-            if (lane == 0) p_idx = atomicAdd(&hdr->work_counter, 1u);
-            pstate = 1;
-        } else if (pstate == 1) {
-            const unsigned idx = __shfl_sync(0xffffffffu, p_idx, 0);
-            if (idx >= total_units) {
-                pstate = 4;
-            } else {
-                const unsigned bc = idx / (unsigned)Hkv;
-                n_h = (int)(idx - bc * (unsigned)Hkv);
-                n0 = __ldg(p.items + 2 * bc);
-                n1 = __ldg(p.items + 2 * bc + 1);
-                pstate = 2;
-            }
-        } else if (pstate == 2) {
-            n_table = p.block_table + (int64_t)n1.w * p.table_stride + n0.y;
-            n_ids = (lane < n0.z) ? __ldg(n_table + lane) : 0;
-            n_ids2 = (32 + lane < n0.z) ? __ldg(n_table + 32 + lane) : 0;
-            pstate = 3;
-        }
-    };
-
-    // ---- loader side
-    int l_win = 0, l_ids = 0, l_ids2 = 0;
-    const int32_t *l_table = nullptr;
-    int64_t l_head_off = 0;
-    bool l_done = false;
-    unsigned lq = 0;           // items entered by the loader
-    uint32_t qn[8][4];         // query fragments of the item the loader entered last
-    unsigned qn_tag = 0xffffffffu;
-#pragma unroll
-    for (int kk = 0; kk < 8; ++kk) qn[kk][0] = qn[kk][1] = qn[kk][2] = qn[kk][3] = 0u;
-
-    auto load_q = [&](uint32_t (&dst)[8][4], int b, int h) {
-        const __half *qb = p.q + ((int64_t)b * p.num_q_heads + (int64_t)h * G) * kD;
-        const uint32_t *q0 = reinterpret_cast<const uint32_t *>(qb + (int64_t)g * kD) + t;
-        const uint32_t *q1 = reinterpret_cast<const uint32_t *>(qb + (int64_t)(g + 8) * kD) + t;
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-            dst[kk][0] = row0 ? __ldg(q0 + kk * 8) : 0u;
-            dst[kk][1] = row1 ? __ldg(q1 + kk * 8) : 0u;
-            dst[kk][2] = row0 ? __ldg(q0 + kk * 8 + 4) : 0u;
-            dst[kk][3] = row1 ? __ldg(q1 + kk * 8 + 4) : 0u;
-        }
-    };
-
-    auto loader_has_tile = [&]() -> bool {
-        if (l_done) return false;
-        if (l_pos < l_nblk) return true;
-        while (pstate < 3) advance(true);  // normally ready before it is needed
-        if (pstate == 4) {
-            l_done = true;
-            return false;
-        }
-        l_nblk = n0.z;
-        l_pos = 0;
-        l_win = 0;
-        l_ids = n_ids;
-        l_ids2 = n_ids2;
-        l_table = n_table;
-        l_head_off = ((int64_t)p.cur_layer * Hkv + n_h) * kTileBytes;
-        if (lane == 0) {
-            dq[(lq % QD) * 2] = make_int4(n0.x, n_h, n0.y, n0.z);        // b, h, start, nblk
-            dq[(lq % QD) * 2 + 1] = make_int4(n0.w, n1.y, n1.z, n1.x);   // split, nsplit, prow, len
-        }
-        load_q(qn, n0.x, n_h);
-        qn_tag = lq;
-        ++lq;
-        pstate = 0;
-        return true;
-    };
-
-    auto issue = [&](unsigned n) {
-        const int j = l_pos;
-        if ((j >> 5) != l_win) {
-            l_ids = l_ids2;
-            ++l_win;
-            const int nj = (l_win + 1) * 32 + lane;
-            l_ids2 = (nj < l_nblk) ? __ldg(l_table + nj) : 0;
-        }
-        int64_t blk = __shfl_sync(0xffffffffu, l_ids, j & 31);
-        if (!block_in_pool(p.pool, blk)) {
-            if (lane == 0) atomicOr(&hdr->error_flags, 1);
-            blk = 0;
-        }
-        int seg;
-        int64_t brow;
-        locate_block(p.pool, blk, seg, brow);
-        const char *kt = p.pool.k_base[seg] + brow * p.pool.block_bytes + l_head_off;
-        const char *vt = p.pool.v_base[seg] + brow * p.pool.block_bytes + l_head_off;
-        const uint32_t st = ring + (n % STAGES) * kStageBytes;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int id = i * 32 + lane;
-            const int r = id >> 4, c = id & 15;
-            const uint32_t off = r * 256 + ((c ^ (r & 7)) << 4);
-            cp_async16(st + off, kt + id * 16);
-            cp_async16(st + kTileBytes + off, vt + id * 16);
-        }
-        ++l_pos;
-    };
-
-    // ---- consumer side
-    unsigned cq = 0;
-    int c_b = 0, c_h = 0, c_start = 0, c_nblk = 0, c_split = 0, c_nsplit = 1, c_prow = 0, c_len = 0, c_pos = 0;
-    uint32_t qf[8][4];
-    float oacc[16][4];
-    float m0 = kNegBig, m1 = kNegBig, l0 = 0.f, l1 = 0.f;
-
-    unsigned issued = 0, consumed = 0;
-#pragma unroll 1
-    for (int s = 0; s < STAGES - 1; ++s) {
-        if (loader_has_tile()) {
-            issue(issued);
-            ++issued;
-        }
-        cp_async_commit();
-        advance(false);
-    }
-
-#pragma unroll 1
-    while (consumed < issued) {
-        cp_async_wait<STAGES - 2>();
-        __syncwarp();
-        if (loader_has_tile()) {
-            issue(issued);
-            ++issued;
-        }
-        cp_async_commit();
-        advance(false);
-
-        if (c_pos == c_nblk) {  // first tile of the next item
-            const int4 d0 = dq[(cq % QD) * 2];
-            const int4 d1 = dq[(cq % QD) * 2 + 1];
-            c_b = d0.x; c_h = d0.y; c_start = d0.z; c_nblk = d0.w;
-            c_split = d1.x; c_nsplit = d1.y; c_prow = d1.z; c_len = d1.w;
-            c_pos = 0;
-            if (qn_tag == cq) {
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {
-                    qf[kk][0] = qn[kk][0]; qf[kk][1] = qn[kk][1]; qf[kk][2] = qn[kk][2]; qf[kk][3] = qn[kk][3];
-                }
-            } else {
-                load_q(qf, c_b, c_h);
-            }
-            ++cq;
-#pragma unroll
-            for (int n = 0; n < 16; ++n) oacc[n][0] = oacc[n][1] = oacc[n][2] = oacc[n][3] = 0.f;
-            m0 = kNegBig; m1 = kNegBig; l0 = 0.f; l1 = 0.f;
-        }
-
-        const uint32_t st = ring + (consumed % STAGES) * kStageBytes;
-        float sc[2][4];
-#pragma unroll
-        for (int jj = 0; jj < 2; ++jj) sc[jj][0] = sc[jj][1] = sc[jj][2] = sc[jj][3] = 0.f;
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-            uint32_t b0, b1, b2, b3;
-            const int c = 2 * kk + k_half;
-            ldmatrix_x4(b0, b1, b2, b3, st + k_tok * 256 + ((c ^ (k_tok & 7)) << 4));
-            mma_16816(sc[0], qf[kk], b0, b1);
-            mma_16816(sc[1], qf[kk], b2, b3);
-        }
-        const int valid = c_len - (c_start + c_pos) * kBS;
-#pragma unroll
-        for (int jj = 0; jj < 2; ++jj) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int tok = jj * 8 + 2 * t + (e & 1);
-                const float v = sc[jj][e] * p.scale_log2;
-                sc[jj][e] = (tok < valid) ? v : kNegBig;
-            }
-        }
-        float mx0 = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
-        float mx1 = fmaxf(fmaxf(sc[0][2], sc[0][3]), fmaxf(sc[1][2], sc[1][3]));
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-        const float a0 = fast_exp2(m0 - mn0), a1 = fast_exp2(m1 - mn1);
-        m0 = mn0;
-        m1 = mn1;
-        float ps0 = 0.f, ps1 = 0.f;
-#pragma unroll
-        for (int jj = 0; jj < 2; ++jj) {
-            sc[jj][0] = fast_exp2(sc[jj][0] - mn0);
-            sc[jj][1] = fast_exp2(sc[jj][1] - mn0);
-            sc[jj][2] = fast_exp2(sc[jj][2] - mn1);
-            sc[jj][3] = fast_exp2(sc[jj][3] - mn1);
-            ps0 += sc[jj][0] + sc[jj][1];
-            ps1 += sc[jj][2] + sc[jj][3];
-        }
-        l0 = l0 * a0 + ps0;
-        l1 = l1 * a1 + ps1;
-#pragma unroll
-        for (int n = 0; n < 16; ++n) {
-            oacc[n][0] *= a0;
-            oacc[n][1] *= a0;
-            oacc[n][2] *= a1;
-            oacc[n][3] *= a1;
-        }
-        uint32_t pa[4];
-        pa[0] = pack_half2(sc[0][0], sc[0][1]);
-        pa[1] = pack_half2(sc[0][2], sc[0][3]);
-        pa[2] = pack_half2(sc[1][0], sc[1][1]);
-        pa[3] = pack_half2(sc[1][2], sc[1][3]);
-#pragma unroll
-        for (int np = 0; np < 8; ++np) {
-            uint32_t b0, b1, b2, b3;
-            const int c = 2 * np + v_half;
-            ldmatrix_x4_trans(b0, b1, b2, b3, st + kTileBytes + v_tok * 256 + ((c ^ (v_tok & 7)) << 4));
-            mma_16816(oacc[2 * np], pa, b0, b1);
-            mma_16816(oacc[2 * np + 1], pa, b2, b3);
-        }
-        ++c_pos;
-        ++consumed;
-
-        if (c_pos == c_nblk) {  // last tile of the item: write the result (loads of the next item stay in flight)
-            float s0 = l0, s1 = l1;
-            s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
-            s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
-            s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
-            s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
-            const float inv0 = 1.f / s0, inv1 = 1.f / s1;
-            const int hq0 = c_h * G;
-            if (c_nsplit == 1) {
-                __half *ob = p.o + ((int64_t)c_b * p.num_q_heads + hq0) * kD;
-#pragma unroll
-                for (int n = 0; n < 16; ++n) {
-                    if (row0)
-                        *reinterpret_cast<__half2 *>(ob + (int64_t)g * kD + n * 8 + 2 * t) =
-                            __floats2half2_rn(oacc[n][0] * inv0, oacc[n][1] * inv0);
-                    if (row1)
-                        *reinterpret_cast<__half2 *>(ob + (int64_t)(g + 8) * kD + n * 8 + 2 * t) =
-                            __floats2half2_rn(oacc[n][2] * inv1, oacc[n][3] * inv1);
-                }
-            } else {
-                float *po = p.part_o + ((int64_t)c_prow * p.num_q_heads + hq0) * kD;
-                float *pl = p.lse + (int64_t)c_prow * p.num_q_heads + hq0;
-#pragma unroll
-                for (int n = 0; n < 16; ++n) {
-                    if (row0)
-                        __stcg(reinterpret_cast<float2 *>(po + (int64_t)g * kD + n * 8 + 2 * t),
-                               make_float2(oacc[n][0] * inv0, oacc[n][1] * inv0));
-                    if (row1)
-                        __stcg(reinterpret_cast<float2 *>(po + (int64_t)(g + 8) * kD + n * 8 + 2 * t),
-                               make_float2(oacc[n][2] * inv1, oacc[n][3] * inv1));
-                }
-                if (t == 0) {
-                    if (row0) __stcg(pl + g, log2f(s0) + m0);
-                    if (row1) __stcg(pl + g + 8, log2f(s1) + m1);
-                }
-                __threadfence();
-                __syncwarp();
-                int *cnt = p.arrive + (int64_t)c_b * Hkv + c_h;
-                int old = 0;
-                if (lane == 0) old = atomicAdd(cnt, 1);
-                old = __shfl_sync(0xffffffffu, old, 0);
-                if (old == c_nsplit - 1) {
-                    __threadfence();
-                    if (lane == 0) *cnt = 0;
-                    merge_splits(p, c_b, hq0, G, c_nsplit, (int64_t)c_prow - c_split, lane);
-                }
-            }
-        }
-    }
-    cp_async_wait<0>();
-    if (lane == 0) {
-        const unsigned workers = gridDim.x * WARPS;
-        const unsigned d = atomicAdd(&hdr->done_counter, 1u);
-        if (d == workers - 1) {
-            hdr->work_counter = 0;
-            hdr->done_counter = 0;
-        }
-    }
-}
-
 // ------------------------------------------------------------------ plain kernel
 template <typename T>
 __device__ __forceinline__ float to_f32(T x);
@@ -1060,7 +766,6 @@ __global__ void attn_decode_plain_kernel(const __grid_constant__ PoolView pool, 
 // ------------------------------------------------------------------ host side
 struct AttnConfig {
     int warps = 8, stages = 3;
-    int stream = 0;  // 1 = continuous tile stream kernel, 0 = per-item ring kernel (default: measured faster)
     bool init = false;
 };
 static AttnConfig g_attn_cfg;
@@ -1070,8 +775,6 @@ static AttnConfig &attn_config() {
     if (!c.init) {
         const char *e = getenv("MKV_ATTN_VARIANT");  // tuning knob: "<warps>x<stages>"
         if (e) sscanf(e, "%dx%d", &c.warps, &c.stages);
-        const char *k = getenv("MKV_ATTN_KERNEL");   // tuning knob: "stream" or "item"
-        if (k) c.stream = (k[0] == 's');
         c.init = true;
     }
     return c;
@@ -1093,33 +796,8 @@ static cudaError_t launch_decode(const AttnParams &p, int sm_count, cudaStream_t
     return cudaGetLastError();
 }
 
-template <int WARPS, int STAGES>
-static cudaError_t launch_decode_stream(const AttnParams &p, int sm_count, cudaStream_t s) {
-    const int smem = WARPS * (STAGES * kStageBytes + (STAGES + 1) * 32);
-    static bool configured[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_f16_stream_kernel<WARPS, STAGES>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return e;
-        configured[dev] = true;
-    }
-    attn_decode_f16_stream_kernel<WARPS, STAGES><<<sm_count, WARPS * 32, smem, s>>>(p);
-    return cudaGetLastError();
-}
-
 static cudaError_t launch_decode_configured(const AttnParams &p, int sms, cudaStream_t s) {
     const AttnConfig &c = attn_config();
-    if (c.stream) {
-        if (c.warps == 6 && c.stages == 4) return launch_decode_stream<6, 4>(p, sms, s);
-        if (c.warps == 9 && c.stages == 3) return launch_decode_stream<9, 3>(p, sms, s);
-        if (c.warps == 7 && c.stages == 4) return launch_decode_stream<7, 4>(p, sms, s);
-        if (c.warps == 10 && c.stages == 2) return launch_decode_stream<10, 2>(p, sms, s);
-        if (c.warps == 12 && c.stages == 2) return launch_decode_stream<12, 2>(p, sms, s);
-        if (c.warps == 5 && c.stages == 5) return launch_decode_stream<5, 5>(p, sms, s);
-        return launch_decode_stream<8, 3>(p, sms, s);
-    }
     if (c.warps == 6 && c.stages == 4) return launch_decode<6, 4>(p, sms, s);
     if (c.warps == 12 && c.stages == 2) return launch_decode<12, 2>(p, sms, s);
     if (c.warps == 9 && c.stages == 3) return launch_decode<9, 3>(p, sms, s);
@@ -1171,11 +849,11 @@ int mkv_attn_plan(int device, void *stream, void *workspace, size_t workspace_by
     return MKV_OK;
 }
 
-int mkv_paged_attention_decode(int device, void *stream, const void *q, void *o, const mkv_pool *pool,
-                               const int32_t *block_table, int64_t table_stride, const int32_t *seq_ids,
-                               const int32_t *seq_lens, int batch, int num_q_heads, int cur_layer,
-                               float softmax_scale, int max_blocks_per_seq_in_batch, void *workspace,
-                               size_t workspace_bytes) {
+static int attention_decode_impl(int device, void *stream, const void *q, void *o, const void *k_new,
+                                 const void *v_new, const mkv_pool *pool, const int32_t *block_table,
+                                 int64_t table_stride, const int32_t *seq_ids, const int32_t *seq_lens, int batch,
+                                 int num_q_heads, int cur_layer, float softmax_scale,
+                                 int max_blocks_per_seq_in_batch, void *workspace, size_t workspace_bytes) {
     PoolView pv;
     int st = validate_pool(pool, &pv);
     if (st) return st;
@@ -1191,6 +869,14 @@ int mkv_paged_attention_decode(int device, void *stream, const void *q, void *o,
     cudaStream_t s = (cudaStream_t)stream;
     const float scale_log2 = softmax_scale * kLog2e;
 
+    if ((k_new == nullptr) != (v_new == nullptr)) return MKV_ERR_NULL;
+    if (k_new && (((uintptr_t)k_new | (uintptr_t)v_new) % 16 != 0 || !fast_path_ok(pv, num_q_heads, q, o))) {
+        // no fused path for this shape / alignment: append with the copy kernel, then attend
+        int rc = mkv_store_kv_decode(device, stream, k_new, v_new, pool, block_table, table_stride, seq_ids, seq_lens,
+                                     batch, cur_layer);
+        if (rc) return rc;
+        k_new = v_new = nullptr;
+    }
     if (!fast_path_ok(pv, num_q_heads, q, o)) {
         int *flags = nullptr;
         if (workspace && workspace_bytes >= sizeof(WsHeader) && ((uintptr_t)workspace % 256) == 0)
@@ -1221,6 +907,8 @@ int mkv_paged_attention_decode(int device, void *stream, const void *q, void *o,
     p.pool = pv;
     p.q = (const __half *)q;
     p.o = (__half *)o;
+    p.k_new = (const __half *)k_new;
+    p.v_new = (const __half *)v_new;
     p.block_table = block_table;
     p.table_stride = table_stride;
     p.seq_ids = seq_ids;
@@ -1242,13 +930,33 @@ int mkv_paged_attention_decode(int device, void *stream, const void *q, void *o,
     return MKV_OK;
 }
 
-int mkv_attn_configure(int warps, int stages, int stream_kernel, double item_factor_value) {
+int mkv_paged_attention_decode(int device, void *stream, const void *q, void *o, const mkv_pool *pool,
+                               const int32_t *block_table, int64_t table_stride, const int32_t *seq_ids,
+                               const int32_t *seq_lens, int batch, int num_q_heads, int cur_layer,
+                               float softmax_scale, int max_blocks_per_seq_in_batch, void *workspace,
+                               size_t workspace_bytes) {
+    return attention_decode_impl(device, stream, q, o, nullptr, nullptr, pool, block_table, table_stride, seq_ids,
+                                 seq_lens, batch, num_q_heads, cur_layer, softmax_scale,
+                                 max_blocks_per_seq_in_batch, workspace, workspace_bytes);
+}
+
+int mkv_paged_attention_decode_append(int device, void *stream, const void *q, void *o, const void *k_new,
+                                      const void *v_new, const mkv_pool *pool, const int32_t *block_table,
+                                      int64_t table_stride, const int32_t *seq_ids, const int32_t *seq_lens,
+                                      int batch, int num_q_heads, int cur_layer, float softmax_scale,
+                                      int max_blocks_per_seq_in_batch, void *workspace, size_t workspace_bytes) {
+    if (batch > 0 && (!k_new || !v_new)) return MKV_ERR_NULL;
+    return attention_decode_impl(device, stream, q, o, k_new, v_new, pool, block_table, table_stride, seq_ids,
+                                 seq_lens, batch, num_q_heads, cur_layer, softmax_scale,
+                                 max_blocks_per_seq_in_batch, workspace, workspace_bytes);
+}
+
+int mkv_attn_configure(int warps, int stages, double item_factor_value) {
     AttnConfig &c = attn_config();
     if (warps > 0 && stages > 1) {
         c.warps = warps;
         c.stages = stages;
     }
-    if (stream_kernel >= 0) c.stream = stream_kernel ? 1 : 0;
     if (item_factor_value > 0.0) {
         item_factor();
         g_item_factor = item_factor_value;
@@ -1363,6 +1071,8 @@ int mkv_paged_attention_decode_noalloc(int device, void *stream, const void *q, 
     p.pool = pv;
     p.q = (const __half *)q;
     p.o = (__half *)o;
+    p.k_new = nullptr;
+    p.v_new = nullptr;
     p.block_table = block_table;
     p.table_stride = table_stride;
     p.seq_ids = seq_ids;

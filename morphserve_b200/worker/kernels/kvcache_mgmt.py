@@ -13,6 +13,32 @@ import torch
 from ..._lib import check, lib
 from ._common import device_and_stream, make_pool, require_cuda
 
+# Opt-in: when True, store_kvcache does not launch the decode append itself; it leaves the new
+# K/V rows with the infer state and the paged_attention call of the same layer appends them inside
+# its own kernel (one launch per layer instead of two).  The pool then changes when attention runs,
+# not when store_kvcache returns - which is when the reference's layer code first reads it anyway
+# (worker/layers/transformer_layer.py:117-126 then :181-187).  Off by default.
+FUSE_DECODE_APPEND = False
+
+
+def set_fused_decode_append(enabled: bool) -> None:
+    global FUSE_DECODE_APPEND
+    FUSE_DECODE_APPEND = bool(enabled)
+
+
+def flush_pending_append(infer_state, pool, block_table, dev, stream) -> None:
+    """Append rows that were left for a fused attention call that did not come."""
+    state = getattr(infer_state, "__dict__", None)
+    pending = state.pop("_mkv_pending_append", None) if state is not None else None
+    if pending is None:
+        return
+    layer, k_dec, v_dec = pending
+    n_pre = infer_state.num_prefill_seqs
+    check(lib.mkv_store_kv_decode(
+        dev, stream, k_dec.data_ptr(), v_dec.data_ptr(), pool, block_table.data_ptr(), block_table.stride(0),
+        infer_state.seq_ids[n_pre:].data_ptr(), infer_state.decoding_seq_lens.data_ptr(),
+        infer_state.num_decoding_seqs, layer), "mkv_store_kv_decode")
+
 
 def store_kvcache(
     k: torch.Tensor,            # [num_tokens, num_kv_heads, head_dim]
@@ -49,10 +75,15 @@ def store_kvcache(
             "mkv_store_kv_prefill")
     n_dec = infer_state.num_decoding_seqs
     if n_dec > 0:
-        row = k.stride(0) * k.element_size()
-        off = infer_state.num_prefill_tokens * row
+        k_dec = k[infer_state.num_prefill_tokens:]
+        v_dec = v[infer_state.num_prefill_tokens:]
+        state = getattr(infer_state, "__dict__", None)
+        if FUSE_DECODE_APPEND and state is not None and k.dtype == torch.float16:
+            flush_pending_append(infer_state, pool, block_table, dev, stream)
+            state["_mkv_pending_append"] = (cur_layer, k_dec, v_dec)
+            return
         seq_ids = infer_state.seq_ids[n_pre:]
         check(lib.mkv_store_kv_decode(
-            dev, stream, k.data_ptr() + off, v.data_ptr() + off, pool, block_table.data_ptr(), stride,
+            dev, stream, k_dec.data_ptr(), v_dec.data_ptr(), pool, block_table.data_ptr(), stride,
             seq_ids.data_ptr(), infer_state.decoding_seq_lens.data_ptr(), n_dec, cur_layer),
             "mkv_store_kv_decode")

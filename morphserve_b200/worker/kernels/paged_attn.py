@@ -16,6 +16,7 @@ import torch
 
 from ..._lib import check, lib
 from ._common import attn_workspace, device_and_stream, make_pool, require_cuda
+from .kvcache_mgmt import flush_pending_append
 
 
 def _plan_for(infer_state, ws, dev, stream, lens, seq_ids, batch, hq, hkv, d, bs, max_blocks):
@@ -69,6 +70,19 @@ def paged_attention(
 
     ws = attn_workspace(dev, batch, hq, hkv, d, max_blocks)
     _plan_for(infer_state, ws, dev, stream, lens, seq_ids, batch, hq, hkv, d, bs, max_blocks)
+    state = getattr(infer_state, "__dict__", None)
+    pending = state.get("_mkv_pending_append") if state is not None else None
+    if pending is not None and pending[0] == cur_layer:
+        # store_kvcache left this layer's new rows to be appended inside the attention kernel
+        del state["_mkv_pending_append"]
+        check(lib.mkv_paged_attention_decode_append(
+            dev, stream, q.data_ptr(), o.data_ptr(), pending[1].data_ptr(), pending[2].data_ptr(), pool,
+            block_table.data_ptr(), block_table.stride(0), seq_ids.data_ptr(), lens.data_ptr(), batch, hq,
+            cur_layer, float(infer_state.softmax_scale), max_blocks, ws.tensor.data_ptr(), ws.nbytes),
+            "mkv_paged_attention_decode_append")
+        return
+    if pending is not None:
+        flush_pending_append(infer_state, pool, block_table, dev, stream)
     check(lib.mkv_paged_attention_decode(
         dev, stream, q.data_ptr(), o.data_ptr(), pool, block_table.data_ptr(), block_table.stride(0),
         seq_ids.data_ptr(), lens.data_ptr(), batch, hq, cur_layer, float(infer_state.softmax_scale),

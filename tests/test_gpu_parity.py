@@ -17,13 +17,14 @@ G = os.path.join(os.path.dirname(__file__), "golden")
 RTOL, ATOL = 2e-3, 1e-2
 
 
-@pytest.fixture(params=["stream", "item"], autouse=True)
-def attention_kernel_flavour(request):
-    """Every test in this file runs with both decode-attention kernels."""
-    from morphserve_b200._lib import lib
-    assert lib.mkv_attn_configure(-1, -1, 1 if request.param == "stream" else 0, -1.0) == 0
+@pytest.fixture(params=["separate", "fused_append"], autouse=True)
+def append_mode(request):
+    """Every test in this file runs twice: with the decode append as its own kernel, and with
+    the append fused into the attention kernel."""
+    import morphserve_b200
+    morphserve_b200.set_fused_decode_append(request.param == "fused_append")
     yield request.param
-    lib.mkv_attn_configure(-1, -1, 0, -1.0)
+    morphserve_b200.set_fused_decode_append(False)
 
 
 def _close(a, b):
@@ -43,7 +44,7 @@ def test_decode_step_matches_reference_fixture(name):
 
 
 @pytest.mark.parametrize("name", list(cases.PREFILL_CASES))
-def test_prefill_scatter_matches_reference_fixture(name):
+def test_prefill_scatter_matches_reference_fixture(name, append_mode):
     from morphserve_b200 import store_kvcache
     from morphserve_b200.worker.infer_state import LlamaInferState
     c = cases.build_prefill_case(**cases.PREFILL_CASES[name])
@@ -63,7 +64,16 @@ def test_prefill_scatter_matches_reference_fixture(name):
         num_blocks_org=c["num_blocks_org"], kv_cache_new_block_size=c["chunk_blocks"], org_layer_param_size=0,
         position_cos=z, position_sin=z, ignore_kvcache=False)
     mc, ec = H.cfgs(c, bt.shape[1])
-    store_kvcache(H.to_dev(c["k"]), H.to_dev(c["v"]), kp[0], vp[0], kp[1:], vp[1:], bt, mc, ec, st, c["layer"])
+    k_dev, v_dev = H.to_dev(c["k"]), H.to_dev(c["v"])
+    store_kvcache(k_dev, v_dev, kp[0], vp[0], kp[1:], vp[1:], bt, mc, ec, st, c["layer"])
+    if append_mode == "fused_append":
+        # the decode rows of the mixed batch are appended by the attention call of the same layer
+        from morphserve_b200 import paged_attention
+        nd = len(c["decode_lens"])
+        mc.num_q_heads = c["Hkv"] * 2
+        q = torch.randn((nd, mc.num_q_heads, c["D"]), dtype=torch.float16, device="cuda")
+        o = torch.empty((nd, mc.num_q_heads * c["D"]), dtype=torch.float16, device="cuda")
+        paged_attention(q, kp[0], vp[0], kp[1:], vp[1:], bt, mc, ec, st, c["layer"], o)
     torch.cuda.synchronize()
     after = [p.cpu().numpy() for p in kp] + [p.cpu().numpy() for p in vp]
     assert cases.sha256_of(*after) == str(gold["pools_after_sha256"])
