@@ -54,6 +54,8 @@ WORKLOADS = {
                             n_chunks=8, release=6),
     # llama3-8b batch, 2 layers, every context exactly 768 tokens (no length spread): isolates scheduling effects
     "llama3-8b-gqa-decode-2layer-uniform": dict(cfg=3, B=256, Hq=32, Hkv=8, L=2, min_len=768, max_len=768, free_frac=0.10),
+    # block swap between the pool and the host swap space (Llama-3-8B block = 2 x 1 MiB): 1024 blocks per direction
+    "kv-swap": dict(cfg=3, swap=True, L=32, Hq=32, Hkv=8, nb=4096, n_swap=1024),
     # small case for profiler captures and CPU-side dry runs (pool ~1.3 GB: larger than L2)
     "small-gqa-decode": dict(cfg=9, B=64, Hq=32, Hkv=8, L=4, max_len=1536, free_frac=0.10),
     # the llama3-8b batch with 2 layers: same bytes per attention launch as the full workload, pool ~1.8 GB
@@ -436,6 +438,54 @@ def resize_bench(w, K, W, device):
 
 
 # ----------------------------------------------------------------------------
+# block swap
+# ----------------------------------------------------------------------------
+def swap_bench(w, K, W, device):
+    """Swap-out then swap-in of n_swap blocks with fully fragmented (seeded random) ids on both
+    sides: the reference-style path (pageable host memory, one cudaMemcpyAsync per run for K and V)
+    and the pinned path (one zero-copy kernel per direction, ids on the GPU)."""
+    import morphserve_b200 as mk
+    L, Hkv, nb, n = w["L"], w["Hkv"], w["nb"], w["n_swap"]
+    g = torch.Generator().manual_seed(1000 * w["cfg"] + 3)
+    shape = (nb, L, Hkv, BS, D)
+    k_cache = torch.randn(shape, dtype=torch.float16, device=device)
+    v_cache = torch.randn(shape, dtype=torch.float16, device=device)
+    dev_ids = torch.randperm(nb, generator=g)[:n]
+    host_ids = torch.randperm(n, generator=g)
+    block_bytes = 2 * L * Hkv * BS * D * 2
+    out = {"blocks": n, "bytes_per_direction": n * block_bytes}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for name, pinned in (("pageable_memcpy", False), ("pinned_kernel", True)):
+        k_swap = torch.zeros((n, L, Hkv, BS, D), dtype=torch.float16)
+        v_swap = torch.zeros((n, L, Hkv, BS, D), dtype=torch.float16)
+        if pinned:
+            k_swap, v_swap = k_swap.pin_memory(), v_swap.pin_memory()
+            d_ids, h_ids = dev_ids.to(device), host_ids.to(device)
+        else:
+            d_ids, h_ids = dev_ids.tolist(), host_ids.tolist()
+        t_out, t_in = [], []
+        for it in range(W + K):
+            torch.cuda.synchronize()
+            e0.record()
+            mk.swiftllm_c.swap_blocks(d_ids, h_ids, False, k_cache, v_cache, k_swap, v_swap)
+            e1.record()
+            torch.cuda.synchronize()
+            if it >= W:
+                t_out.append(e0.elapsed_time(e1))
+            e0.record()
+            mk.swiftllm_c.swap_blocks(h_ids, d_ids, True, k_cache, v_cache, k_swap, v_swap)
+            e1.record()
+            torch.cuda.synchronize()
+            if it >= W:
+                t_in.append(e0.elapsed_time(e1))
+        out[name] = {"swap_out_gbs": n * block_bytes / (statistics.median(t_out) * 1e-3) / 1e9,
+                     "swap_in_gbs": n * block_bytes / (statistics.median(t_in) * 1e-3) / 1e9,
+                     "swap_out_ms": statistics.median(t_out), "swap_in_ms": statistics.median(t_in)}
+        del k_swap, v_swap
+    return out
+
+
+# ----------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -454,6 +504,15 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     base = WORKLOADS[args.workload]
+    if base.get("swap"):
+        assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+        torch.cuda.set_device(local_rank)
+        if rank == 0:
+            r = swap_bench(base, max(K, 3) if K < 10 else 5, 2, torch.device("cuda", local_rank))
+            print(json.dumps({"metric": "swap_gbs", "value": r["pinned_kernel"]["swap_out_gbs"], "unit": "GB/s",
+                              "n_gpus": 1, "higher_is_better": True, "dtype": "u8", "data": "synthetic",
+                              "config": {"workload": args.workload}, "swap": r}))
+        return
     if base.get("resize"):
         assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
         torch.cuda.set_device(local_rank)

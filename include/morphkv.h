@@ -300,6 +300,21 @@ int mkv_swap_blocks(int device, void *stream, const mkv_pool *pool, void *k_swap
                     void *v_swap /* host */, int64_t num_swap_blocks, const int64_t *src_ids /* host */,
                     const int64_t *dst_ids /* host */, int64_t n, int is_swap_in, int64_t *num_copies);
 
+/*
+ * The same block copies as mkv_swap_blocks done by ONE kernel that reads / writes
+ * the swap space directly, for a swap space in pinned (device-addressable) host
+ * memory.  Ids are DEVICE arrays, so the ids that BlockManager produces on the
+ * GPU (worker/model.py:476-477) need no .tolist() round trip, and fragmented id
+ * lists cost one launch instead of two copies per run.  Ids out of range are
+ * skipped.  MKV_ERR_ALIGN if the swap space is not host memory the device can
+ * address (use mkv_swap_blocks for pageable memory, as worker/model.py:196-204
+ * allocates it).
+ */
+int mkv_swap_blocks_pinned(int device, void *stream, const mkv_pool *pool, void *k_swap /* pinned host */,
+                           void *v_swap /* pinned host */, int64_t num_swap_blocks,
+                           const int64_t *src_ids /* device */, const int64_t *dst_ids /* device */, int64_t n,
+                           int is_swap_in);
+
 #ifdef __cplusplus
 }
 #endif

@@ -68,6 +68,7 @@ SIGNATURES = {
     "mkv_remap_block_table": (_i, [_i, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _i64]),
     "mkv_swap_blocks": (_i, [_i, _vp, _pool, _vp, _vp, _i64, C.POINTER(_i64), C.POINTER(_i64), _i64, _i,
                              C.POINTER(_i64)]),
+    "mkv_swap_blocks_pinned": (_i, [_i, _vp, _pool, _vp, _vp, _i64, _vp, _vp, _i64, _i]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

@@ -10,9 +10,15 @@ constexpr int kSliceBytes = kCopyThreads * kVecPerThread * 16;     // 32 KiB per
 
 // Work item = (pair, K|V, slice).  grid-stride over items; each thread issues
 // all its loads before its stores so that 128 B per thread are in flight.
-__global__ void __launch_bounds__(kCopyThreads) copy_blocks_kernel(const __grid_constant__ PoolView pool, const int64_t *__restrict__ src_ids,
+// MODE 0: pool -> pool (compaction).  MODE 1: host swap space -> pool (swap in).
+// MODE 2: pool -> host swap space (swap out).  The host side must be pinned memory
+// that the device can address (zero-copy over PCIe / NVLink-C2C).
+template <int MODE>
+__global__ void __launch_bounds__(kCopyThreads) copy_blocks_kernel(const __grid_constant__ PoolView pool,
+                                                                  const int64_t *__restrict__ src_ids,
                                                                   const int64_t *__restrict__ dst_ids, int64_t n,
-                                                                  int slices_per_block) {
+                                                                  int slices_per_block, char *host_k, char *host_v,
+                                                                  int64_t host_blocks) {
     const int64_t items = n * 2 * slices_per_block;
     const int64_t vec_per_block = pool.block_bytes / 16;
     for (int64_t item = blockIdx.x; item < items; item += gridDim.x) {
@@ -21,14 +27,28 @@ __global__ void __launch_bounds__(kCopyThreads) copy_blocks_kernel(const __grid_
         const int which = rem / slices_per_block;
         const int slice = rem - which * slices_per_block;
         const int64_t s = src_ids[pair], d = dst_ids[pair];
-        if (!block_in_pool(pool, s) || !block_in_pool(pool, d)) continue;
-        int sseg, dseg;
-        int64_t srow, drow;
-        locate_block(pool, s, sseg, srow);
-        locate_block(pool, d, dseg, drow);
-        const uint4 *sp = reinterpret_cast<const uint4 *>((which ? pool.v_base[sseg] : pool.k_base[sseg]) +
-                                                          srow * pool.block_bytes);
-        uint4 *dp = reinterpret_cast<uint4 *>((which ? pool.v_base[dseg] : pool.k_base[dseg]) + drow * pool.block_bytes);
+        const uint4 *sp;
+        uint4 *dp;
+        if (MODE == 1) {
+            if (s < 0 || s >= host_blocks) continue;
+            sp = reinterpret_cast<const uint4 *>((which ? host_v : host_k) + s * pool.block_bytes);
+        } else {
+            if (!block_in_pool(pool, s)) continue;
+            int seg;
+            int64_t row;
+            locate_block(pool, s, seg, row);
+            sp = reinterpret_cast<const uint4 *>((which ? pool.v_base[seg] : pool.k_base[seg]) + row * pool.block_bytes);
+        }
+        if (MODE == 2) {
+            if (d < 0 || d >= host_blocks) continue;
+            dp = reinterpret_cast<uint4 *>((which ? host_v : host_k) + d * pool.block_bytes);
+        } else {
+            if (!block_in_pool(pool, d)) continue;
+            int seg;
+            int64_t row;
+            locate_block(pool, d, seg, row);
+            dp = reinterpret_cast<uint4 *>((which ? pool.v_base[seg] : pool.k_base[seg]) + row * pool.block_bytes);
+        }
         const int64_t v0 = (int64_t)slice * (kSliceBytes / 16) + threadIdx.x;
         uint4 r[kVecPerThread];
 #pragma unroll
@@ -96,7 +116,44 @@ int mkv_copy_blocks(int device, void *stream, const mkv_pool *pool, const int64_
     const int64_t items = n * 2 * slices;
     int64_t grid = (int64_t)sms * 8;  // 8 x 256 threads resident per SM
     if (grid > items) grid = items;
-    copy_blocks_kernel<<<(unsigned)grid, kCopyThreads, 0, (cudaStream_t)stream>>>(pv, src_ids, dst_ids, n, slices);
+    copy_blocks_kernel<0><<<(unsigned)grid, kCopyThreads, 0, (cudaStream_t)stream>>>(pv, src_ids, dst_ids, n, slices,
+                                                                                     nullptr, nullptr, 0);
+    MKV_LAUNCH_CHECK();
+    return MKV_OK;
+}
+
+int mkv_swap_blocks_pinned(int device, void *stream, const mkv_pool *pool, void *k_swap, void *v_swap,
+                           int64_t num_swap_blocks, const int64_t *src_ids, const int64_t *dst_ids, int64_t n,
+                           int is_swap_in) {
+    PoolView pv;
+    int st = validate_pool(pool, &pv);
+    if (st) return st;
+    if (n < 0 || num_swap_blocks < 0) return MKV_ERR_SHAPE;
+    if (n == 0) return MKV_OK;
+    if (!k_swap || !v_swap || !src_ids || !dst_ids) return MKV_ERR_NULL;
+    if (pv.block_bytes % 16 != 0 || (((uintptr_t)k_swap | (uintptr_t)v_swap) % 16) != 0) return MKV_ERR_ALIGN;
+    for (int i = 0; i < pv.num_segments; ++i)
+        if ((((uintptr_t)pv.k_base[i]) | ((uintptr_t)pv.v_base[i])) % 16 != 0) return MKV_ERR_ALIGN;
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
+    // the swap space must be host memory the device can address
+    for (void *hp : {k_swap, v_swap}) {
+        cudaPointerAttributes attr;
+        MKV_CUDA_TRY(cudaPointerGetAttributes(&attr, hp));
+        if (attr.type != cudaMemoryTypeHost && attr.type != cudaMemoryTypeManaged) return MKV_ERR_ALIGN;
+    }
+    int sms = 148;
+    mkv_sm_count(device, &sms);
+    const int slices = (int)ceil_div64(pv.block_bytes, kSliceBytes);
+    const int64_t items = n * 2 * slices;
+    int64_t grid = (int64_t)sms * 4;
+    if (grid > items) grid = items;
+    if (is_swap_in)
+        copy_blocks_kernel<1><<<(unsigned)grid, kCopyThreads, 0, (cudaStream_t)stream>>>(
+            pv, src_ids, dst_ids, n, slices, (char *)k_swap, (char *)v_swap, num_swap_blocks);
+    else
+        copy_blocks_kernel<2><<<(unsigned)grid, kCopyThreads, 0, (cudaStream_t)stream>>>(
+            pv, src_ids, dst_ids, n, slices, (char *)k_swap, (char *)v_swap, num_swap_blocks);
     MKV_LAUNCH_CHECK();
     return MKV_OK;
 }

@@ -18,9 +18,20 @@ from .worker.kernels._common import device_and_stream, make_pool
 _state = {"kv_info": None, "org_gpu": {}, "quant": {}}
 
 
+def _as_list(xs):
+    return [int(x) for x in (xs.tolist() if isinstance(xs, torch.Tensor) else xs)]
+
+
 def _ids(xs):
+    xs = _as_list(xs)
     n = len(xs)
-    return (C.c_int64 * n)(*[int(x) for x in xs]), n
+    return (C.c_int64 * n)(*xs), n
+
+
+def _dev_ids(xs, device):
+    if isinstance(xs, torch.Tensor):
+        return xs.to(device=device, dtype=torch.int64).contiguous()
+    return torch.tensor(_as_list(xs), dtype=torch.int64, device=device)
 
 
 def _swap(src, dst, is_swap_in, pool, k_cache, k_swap, v_swap):
@@ -29,6 +40,20 @@ def _swap(src, dst, is_swap_in, pool, k_cache, k_swap, v_swap):
     if k_swap.is_cuda or v_swap.is_cuda:
         raise RuntimeError("k_swap / v_swap must be host tensors")
     dev, stream = device_and_stream(k_cache)
+    if k_swap.is_pinned() and v_swap.is_pinned():
+        # one kernel reads / writes the pinned swap space directly; ids may stay on the GPU
+        if not isinstance(src, torch.Tensor):       # host lists: keep the range check of the copy path
+            host_ids = _as_list(src if is_swap_in else dst)
+            dev_ids = _as_list(dst if is_swap_in else src)
+            total = pool.num_blocks_org + (pool.num_segments - 1) * pool.chunk_blocks
+            if host_ids and (min(host_ids) < 0 or max(host_ids) >= k_swap.shape[0]
+                             or min(dev_ids) < 0 or max(dev_ids) >= total):
+                raise MorphKVError(-5, "mkv_swap_blocks_pinned")
+        s, d = _dev_ids(src, k_cache.device), _dev_ids(dst, k_cache.device)
+        check(lib.mkv_swap_blocks_pinned(dev, stream, pool, k_swap.data_ptr(), v_swap.data_ptr(), k_swap.shape[0],
+                                         s.data_ptr(), d.data_ptr(), s.shape[0], 1 if is_swap_in else 0),
+              "mkv_swap_blocks_pinned")
+        return
     s, n = _ids(src)
     d, _ = _ids(dst)
     check(lib.mkv_swap_blocks(dev, stream, pool, k_swap.data_ptr(), v_swap.data_ptr(), k_swap.shape[0],
@@ -36,7 +61,9 @@ def _swap(src, dst, is_swap_in, pool, k_cache, k_swap, v_swap):
 
 
 def swap_blocks(source_block_ids, target_block_ids, is_swap_in, k_cache, v_cache, k_swap, v_swap):
-    """csrc/src/block_swapping.cpp:22-85.  Asynchronous on the current stream."""
+    """csrc/src/block_swapping.cpp:22-85.  Asynchronous on the current stream.  Pageable swap space:
+    run-coalesced cudaMemcpyAsync like the reference.  Pinned swap space: one zero-copy kernel; the id
+    arguments may then also be device tensors (no .tolist() needed)."""
     pool = make_pool(k_cache, v_cache, [], [], k_cache.shape[0], 0)
     _swap(source_block_ids, target_block_ids, is_swap_in, pool, k_cache, k_swap, v_swap)
 
@@ -49,7 +76,7 @@ def swap_blocks_new_kv_combined(source_block_ids, target_block_ids, is_swap_in, 
     reference's allocator produces (:159-160).  The device address always comes
     from the device-side id (the reference uses the source id on swap-in, :156-161)."""
     dev_ids = target_block_ids if is_swap_in else source_block_ids
-    top = max([int(x) for x in dev_ids], default=0)
+    top = max(_as_list(dev_ids), default=0)
     n_chunks = 1 + max(0, (top - num_blocks_org) // kv_cache_new_block_size) if top >= num_blocks_org else 1
     if n_chunks + 1 > MKV_MAX_SEGMENTS:
         raise RuntimeError("block id beyond the supported number of elastic chunks")

@@ -202,7 +202,8 @@ def test_release_refused_while_last_chunk_is_live():
     tw.check()
 
 
-def test_swap_roundtrip_and_chunk_addressing():
+@pytest.mark.parametrize("pinned", [False, True])
+def test_swap_roundtrip_and_chunk_addressing(pinned):
     from morphserve_b200 import swiftllm_c
     L, Hkv, bs, D = 2, 2, 16, 128
     rs = np.random.RandomState(8)
@@ -224,6 +225,8 @@ def test_swap_roundtrip_and_chunk_addressing():
         v_new[j].copy_(H.to_dev(vp[1 + j]))
     k_swap = torch.zeros((ncpu, L, Hkv, bs, D), dtype=torch.float16)
     v_swap = torch.zeros((ncpu, L, Hkv, bs, D), dtype=torch.float16)
+    if pinned:      # pinned swap space: one zero-copy kernel instead of run-coalesced copies
+        k_swap, v_swap = k_swap.pin_memory(), v_swap.pin_memory()
     oks, ovs = k_swap.numpy().copy(), v_swap.numpy().copy()
 
     # swap out: device ids (runs, a chunk boundary at 15|16, original/elastic boundary at 11|12)
@@ -241,9 +244,11 @@ def test_swap_roundtrip_and_chunk_addressing():
     O.swap_blocks(src2, dst2, True, kp, vp, oks, ovs, nb_org, chunk)
     # swap in into elastic blocks: the device address comes from the TARGET id
     src3, dst3 = [7, 8, 9, 10], [18, 19, 12, 13]
+    if pinned:      # ids may stay on the GPU
+        src3, dst3 = torch.tensor(src3, device="cuda"), torch.tensor(dst3, device="cuda", dtype=torch.int32)
     swiftllm_c.swap_blocks_new_kv_combined(src3, dst3, True, nb_org, P, chunk, 2, k_cache, v_cache, k_swap, v_swap,
                                            k_new[0], v_new[0])
-    O.swap_blocks(src3, dst3, True, kp, vp, oks, ovs, nb_org, chunk)
+    O.swap_blocks([7, 8, 9, 10], [18, 19, 12, 13], True, kp, vp, oks, ovs, nb_org, chunk)
     torch.cuda.synchronize()
     got = [k_cache] + k_new + [v_cache] + v_new
     for a, b in zip(got, kp + vp):
