@@ -356,7 +356,9 @@ struct WorkMeta {
     int ids;               // lane l: block id of tile l of the item
 };
 
-template <int WARPS, int STAGES>
+// HI: the GQA group has more than 8 query heads, so rows 8-15 of the tensor-core tile carry data.
+// For G <= 8 (every Llama shape) their softmax, rescale and write-out work is compiled out.
+template <int WARPS, int STAGES, bool HI>
 __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __grid_constant__ AttnParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const int lane = threadIdx.x & 31;
@@ -372,7 +374,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
     const int Hkv = p.pool.num_kv_heads;
     const int G = p.group;
     const unsigned total_units = (unsigned)hdr->n_items * (unsigned)Hkv;
-    const bool row0 = g < G, row1 = (g + 8) < G;
+    const bool row0 = g < G, row1 = HI && (g + 8) < G;
 
     // Claiming the next unit is a chain of three dependent global accesses (counter ->
     // unit descriptor -> block ids).  It is cut into three steps that run one per tile
@@ -573,13 +575,18 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
                 }
             }
             float mx0 = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
-            float mx1 = fmaxf(fmaxf(sc[0][2], sc[0][3]), fmaxf(sc[1][2], sc[1][3]));
+            float mx1 = HI ? fmaxf(fmaxf(sc[0][2], sc[0][3]), fmaxf(sc[1][2], sc[1][3])) : kNegBig;
             mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
             mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            if (HI) {
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            }
             const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-            const float a0 = fast_exp2(m0 - mn0), a1 = fast_exp2(m1 - mn1);
+            // The running maxima settle after the first tiles of a sequence; when none moved in the whole
+            // warp the 64 accumulator rescales are skipped (they would multiply by exactly 1).
+            const bool moved = (mn0 != m0) || (HI && mn1 != m1);
+            const float a0 = fast_exp2(m0 - mn0), a1 = HI ? fast_exp2(m1 - mn1) : 1.f;
             m0 = mn0;
             m1 = mn1;
             float ps0 = 0.f, ps1 = 0.f;
@@ -587,19 +594,27 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
             for (int jj = 0; jj < 2; ++jj) {
                 sc[jj][0] = fast_exp2(sc[jj][0] - mn0);
                 sc[jj][1] = fast_exp2(sc[jj][1] - mn0);
-                sc[jj][2] = fast_exp2(sc[jj][2] - mn1);
-                sc[jj][3] = fast_exp2(sc[jj][3] - mn1);
                 ps0 += sc[jj][0] + sc[jj][1];
-                ps1 += sc[jj][2] + sc[jj][3];
+                if (HI) {
+                    sc[jj][2] = fast_exp2(sc[jj][2] - mn1);
+                    sc[jj][3] = fast_exp2(sc[jj][3] - mn1);
+                    ps1 += sc[jj][2] + sc[jj][3];
+                } else {
+                    sc[jj][2] = sc[jj][3] = 0.f;  // rows 8-15 are padding: P = 0 keeps their accumulators at 0
+                }
             }
             l0 = l0 * a0 + ps0;  // per-thread share of the row sum; reduced over the quad at the end
-            l1 = l1 * a1 + ps1;
+            if (HI) l1 = l1 * a1 + ps1;
+            if (__any_sync(0xffffffffu, moved)) {
 #pragma unroll
-            for (int n = 0; n < 16; ++n) {
-                oacc[n][0] *= a0;
-                oacc[n][1] *= a0;
-                oacc[n][2] *= a1;
-                oacc[n][3] *= a1;
+                for (int n = 0; n < 16; ++n) {
+                    oacc[n][0] *= a0;
+                    oacc[n][1] *= a0;
+                    if (HI) {
+                        oacc[n][2] *= a1;
+                        oacc[n][3] *= a1;
+                    }
+                }
             }
             // P (16 heads x 16 tokens) as the A operand of O += P V
             uint32_t pa[4];
@@ -780,20 +795,26 @@ static AttnConfig &attn_config() {
     return c;
 }
 
-template <int WARPS, int STAGES>
-static cudaError_t launch_decode(const AttnParams &p, int sm_count, cudaStream_t s) {
+template <int WARPS, int STAGES, bool HI>
+static cudaError_t launch_decode_hi(const AttnParams &p, int sm_count, cudaStream_t s) {
     const int smem = WARPS * STAGES * kStageBytes;
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_f16_kernel<WARPS, STAGES>,
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_f16_kernel<WARPS, STAGES, HI>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
-    attn_decode_f16_kernel<WARPS, STAGES><<<sm_count, WARPS * 32, smem, s>>>(p);
+    attn_decode_f16_kernel<WARPS, STAGES, HI><<<sm_count, WARPS * 32, smem, s>>>(p);
     return cudaGetLastError();
+}
+
+template <int WARPS, int STAGES>
+static cudaError_t launch_decode(const AttnParams &p, int sm_count, cudaStream_t s) {
+    return p.group > 8 ? launch_decode_hi<WARPS, STAGES, true>(p, sm_count, s)
+                       : launch_decode_hi<WARPS, STAGES, false>(p, sm_count, s);
 }
 
 static cudaError_t launch_decode_configured(const AttnParams &p, int sms, cudaStream_t s) {
