@@ -9,12 +9,17 @@
 //     `chunk` blocks so that there are a few work items per resident warp, and
 //     sorts the (sequence, chunk) items longest first.
 //   decode kernel (once per layer): one persistent thread block per SM; every
-//     WARP is an independent worker that pulls (item, kv head) pairs from a
-//     global counter, streams the item's K/V tiles through a private
+//     WARP is an independent worker that pulls (item, kv head) units from a
+//     global counter, streams the unit's K/V tiles through a private
 //     cp.async ring in shared memory (XOR-swizzled for ldmatrix), and keeps an
-//     fp32 online softmax in base 2.  A sequence cut into several chunks goes
-//     through fp32 partials in the workspace; the warp that finishes a
+//     fp32 online softmax in base 2.  The next unit is claimed in three
+//     non-blocking steps a few tiles before the current one ends and its first
+//     tiles are fetched into the stages the current unit frees, so the ring
+//     stays full across unit boundaries.  A sequence cut into several chunks
+//     goes through fp32 partials in the workspace; the warp that finishes a
 //     (sequence, kv head) last merges them (no second launch, no waiting).
+//     Optionally the unit that owns the newest token's block also appends that
+//     token's K/V row (fused store_kvcache).
 //   plain kernel: any dtype / head_dim / block size, one warp per (seq, q head).
 //
 // No kernel here waits on another thread block, so nothing can spin forever.
@@ -51,7 +56,7 @@ struct alignas(256) WsHeader {
 };
 
 struct WsLayout {
-    size_t items, items_tmp, split_info, arrive, lse, part_o, total;
+    size_t items, items_tmp, arrive, lse, part_o, total;
     int cap_items;
 };
 
@@ -81,7 +86,6 @@ static WsLayout make_layout(int sm_count, int batch, int num_q_heads, int num_kv
     size_t off = sizeof(WsHeader);
     L.items = off;       off = align256(off + (size_t)cap * 2 * sizeof(int4));  // 2 x int4 per item
     L.items_tmp = off;   off = align256(off + (size_t)cap * 2 * sizeof(int4));
-    L.split_info = off;  off = align256(off + (size_t)batch * sizeof(int2));
     L.arrive = off;      off = align256(off + (size_t)batch * num_kv_heads * sizeof(int));
     L.lse = off;         off = align256(off + (size_t)cap * num_q_heads * sizeof(float));
     L.part_o = off;      off = align256(off + (size_t)cap * num_q_heads * head_dim * sizeof(float));
@@ -121,7 +125,7 @@ __device__ __forceinline__ int plan_scan(int v, int &total, int *warp_sums) {
     return warp_sums[wid] + incl - v;
 }
 
-__global__ void __launch_bounds__(1024) attn_plan_kernel(WsHeader *hdr, int4 *items, int4 *items_tmp, int2 *split_info,
+__global__ void __launch_bounds__(1024) attn_plan_kernel(WsHeader *hdr, int4 *items, int4 *items_tmp,
                                                        int *arrive, const int32_t *__restrict__ seq_lens,
                                                        const int32_t *__restrict__ seq_ids, int batch,
                                                        int num_kv_heads, int block_size, int cap_items) {
@@ -169,7 +173,6 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(WsHeader *hdr, int4 *it
         const int off_i = plan_scan(ns, tot_i, warp_sums);
         const int off_r = plan_scan(pr, tot_r, warp_sums);
         if (b < batch) {
-            split_info[b] = make_int2(ns, carry_rows + off_r);
             for (int s = 0; s < ns; ++s) {
                 int pos = carry_items + off_i + s;
                 int n = min(chunk, nblk - s * chunk);
@@ -274,7 +277,6 @@ struct AttnParams {
     float scale_log2;   // softmax_scale * log2(e)
     WsHeader *hdr;
     const int4 *items;
-    const int2 *split_info;
     int *arrive;
     float *lse;
     float *part_o;
@@ -864,7 +866,7 @@ int mkv_attn_plan(int device, void *stream, void *workspace, size_t workspace_by
     if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
     char *ws = (char *)workspace;
     attn_plan_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(
-        (WsHeader *)ws, (int4 *)(ws + L.items), (int4 *)(ws + L.items_tmp), (int2 *)(ws + L.split_info),
+        (WsHeader *)ws, (int4 *)(ws + L.items), (int4 *)(ws + L.items_tmp),
         (int *)(ws + L.arrive), seq_lens, seq_ids, batch, num_kv_heads, block_size, L.cap_items);
     MKV_LAUNCH_CHECK();
     return MKV_OK;
@@ -941,7 +943,6 @@ static int attention_decode_impl(int device, void *stream, const void *q, void *
     p.scale_log2 = scale_log2;
     p.hdr = (WsHeader *)ws;
     p.items = (const int4 *)(ws + L.items);
-    p.split_info = (const int2 *)(ws + L.split_info);
     p.arrive = (int *)(ws + L.arrive);
     p.lse = (float *)(ws + L.lse);
     p.part_o = (float *)(ws + L.part_o);
@@ -1085,7 +1086,7 @@ int mkv_paged_attention_decode_noalloc(int device, void *stream, const void *q, 
     // The plan kernel rewrites everything that must start clean: header, work and
     // done counters, the arrival counters of every (sequence, kv head), the item list.
     attn_plan_kernel<<<1, 1024, 0, s>>>((WsHeader *)ws, (int4 *)(ws + L.items), (int4 *)(ws + L.items_tmp),
-                                        (int2 *)(ws + L.split_info), (int *)(ws + L.arrive), seq_lens, seq_ids,
+                                        (int *)(ws + L.arrive), seq_lens, seq_ids,
                                         batch, pv.num_kv_heads, pv.block_size, L.cap_items);
     MKV_LAUNCH_CHECK();
     AttnParams p;
@@ -1105,7 +1106,6 @@ int mkv_paged_attention_decode_noalloc(int device, void *stream, const void *q, 
     p.scale_log2 = scale_log2;
     p.hdr = (WsHeader *)ws;
     p.items = (const int4 *)(ws + L.items);
-    p.split_info = (const int2 *)(ws + L.split_info);
     p.arrive = (int *)(ws + L.arrive);
     p.lse = (float *)(ws + L.lse);
     p.part_o = (float *)(ws + L.part_o);
