@@ -56,6 +56,10 @@ WORKLOADS = {
     "llama3-8b-gqa-decode-2layer-uniform": dict(cfg=3, B=256, Hq=32, Hkv=8, L=2, min_len=768, max_len=768, free_frac=0.10),
     # block swap between the pool and the host swap space (Llama-3-8B block = 2 x 1 MiB): 1024 blocks per direction
     "kv-swap": dict(cfg=3, swap=True, L=32, Hq=32, Hkv=8, nb=4096, n_swap=1024),
+    # the same with the all-gather folded into the attention launch: every rank stores its output slice straight
+    # into all ranks' full-width matrices (peer-mapped symmetric memory), one barrier per layer
+    "codellama-34b-gqa-decode-headshard-push": dict(cfg=5, B=512, Hq=64, Hkv=8, L=48, max_len=1536, free_frac=0.05,
+                                                    head_shard=True, push=True),
     # small case for profiler captures and CPU-side dry runs (pool ~1.3 GB: larger than L2)
     "small-gqa-decode": dict(cfg=9, B=64, Hq=32, Hkv=8, L=4, max_len=1536, free_frac=0.10),
     # the llama3-8b batch with 2 layers: same bytes per attention launch as the full workload, pool ~1.8 GB
@@ -184,8 +188,17 @@ class DecodeJob:
             if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
                 self.dist = dist
                 n = dist.get_world_size()
-                # gathered outputs, [rank, sequence, local heads * D]: the consumer reads the permuted view
-                self.o_full = torch.empty((L, n, B, Hq * D), dtype=torch.float16, device=device)
+                if w.get("push"):
+                    # full-width output matrices [layer, sequence, all heads * D] in symmetric memory: every
+                    # rank can store into every other rank's copy
+                    import torch.distributed._symmetric_memory as symm
+                    self.o_full = symm.empty((L, B, w["Hq_global"] * D), dtype=torch.float16, device=device)
+                    self.symm = symm.rendezvous(self.o_full, dist.group.WORLD)
+                    self.peer_ptrs = [int(x) for x in self.symm.buffer_ptrs]
+                    self.layer_bytes = B * w["Hq_global"] * D * 2
+                else:
+                    # gathered outputs, [rank, sequence, local heads * D]: the consumer reads the permuted view
+                    self.o_full = torch.empty((L, n, B, Hq * D), dtype=torch.float16, device=device)
 
     def infer_state(self, seq_ids, lens_dev):
         B, Hkv = self.w["B"], self.w["Hkv"]
@@ -201,6 +214,14 @@ class DecodeJob:
 
     def layers(self, st, q, kn, vn, o):
         mk, mc, ec, bt = self.mk, self.model_config, self.engine_config, self.bm.block_table
+        if self.dist is not None and self.w.get("push"):
+            w = self.w
+            for layer in range(w["L"]):
+                mk.paged_attention_push(q[layer], self.k_cache, self.v_cache, [], [], bt, mc, ec, st, layer,
+                                        [p + layer * self.layer_bytes for p in self.peer_ptrs],
+                                        w["Hq_global"] * D, w["head_offset"] * D, k_new=kn[layer], v_new=vn[layer])
+                self.symm.barrier()        # every rank's slice of this layer has landed everywhere
+            return
         for layer in range(self.w["L"]):
             mk.store_kvcache(kn[layer], vn[layer], self.k_cache, self.v_cache, [], [], bt, mc, ec, st, layer)
             mk.paged_attention(q[layer], self.k_cache, self.v_cache, [], [], bt, mc, ec, st, layer, o[layer])
@@ -535,7 +556,9 @@ def main():
     config = {"workload": args.workload, "baseline_config": base["cfg"], "global_batch": w["B_global"],
               "batch_per_gpu": w["B"], "num_q_heads": base["Hq"], "num_kv_heads": base["Hkv"], "head_dim": D,
               "block_size": BS, "num_layers": w["L"], "context_len": f"uniform[1,{w['max_len']}] + 1 per step",
-              "sharding": (f"kv heads x{world} + all-gather of o per layer" if head_shard else f"sequence x{world}"),
+              "sharding": ((f"kv heads x{world}, o pushed to all ranks from the attention epilogue" if base.get("push")
+                            else f"kv heads x{world} + all-gather of o per layer") if head_shard
+                           else f"sequence x{world}"),
               "l2": "inputs_exceed_l2"}
 
     if args.impl == "reference":

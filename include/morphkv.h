@@ -133,6 +133,27 @@ int mkv_paged_attention_decode_append(
     int max_blocks_per_seq_in_batch, void *workspace, size_t workspace_bytes);
 
 /*
+ * Decode attention whose result is PUSHED into several output matrices at once:
+ * row b, columns [out_col_offset + hq*head_dim, +head_dim) of every
+ * out_ptrs[i] (row stride out_row_stride elements, fp16).  Made for KV-head
+ * sharding across GPUs (no counterpart in the single-GPU reference): each rank
+ * attends over its own KV heads and stores its column slice straight into every
+ * rank's full-width [batch, Hq_total*head_dim] matrix through peer-mapped
+ * pointers - plain stores over NVLink from the kernel's epilogue, so the
+ * "all-gather" rides inside the attention launch.  Nothing is loaded from a
+ * peer.  The caller makes the peers' stores visible before reading its matrix
+ * (a barrier across the ranks after the launch).  out_ptrs is a HOST array of
+ * n_out <= 8 device-accessible pointers; k_new / v_new as in
+ * mkv_paged_attention_decode_append, or NULL.  fp16 / head_dim 128 / block 16.
+ */
+int mkv_paged_attention_decode_push(
+    int device, void *stream, const void *q, void *const *out_ptrs, int n_out, int64_t out_row_stride,
+    int64_t out_col_offset, const void *k_new, const void *v_new, const mkv_pool *pool,
+    const int32_t *block_table, int64_t table_stride, const int32_t *seq_ids, const int32_t *seq_lens,
+    int batch, int num_q_heads, int cur_layer, float softmax_scale, int max_blocks_per_seq_in_batch,
+    void *workspace, size_t workspace_bytes);
+
+/*
  * Tuning knobs of the decode kernel (process-wide; not needed for normal use):
  * warps per SM and ring stages (values <= 0 keep the current ones) and the
  * number of work units planned per worker warp (<= 0 keeps).  Changing the item

@@ -28,7 +28,7 @@ from .worker.block_manager import BlockManager
 from .worker.infer_state import LlamaInferState
 from .worker.kernels import block_mgmt, kvcache_mgmt, paged_attn
 from .worker.kernels.kvcache_mgmt import set_fused_decode_append, store_kvcache
-from .worker.kernels.paged_attn import paged_attention
+from .worker.kernels.paged_attn import paged_attention, paged_attention_push
 
 __version__ = "0.1.0"
 
@@ -75,5 +75,5 @@ def install_as_swiftllm(overwrite: bool = True) -> None:
                 setattr(sys.modules[parent], parts[-1], mod)
 
 
-__all__ = ["paged_attention", "store_kvcache", "set_fused_decode_append", "BlockManager", "LlamaInferState",
+__all__ = ["paged_attention", "paged_attention_push", "store_kvcache", "set_fused_decode_append", "BlockManager", "LlamaInferState",
            "swiftllm_c", "memory_utils", "install_as_swiftllm"]

@@ -263,7 +263,13 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
 struct AttnParams {
     PoolView pool;
     const __half *q;
-    __half *o;
+    // Result: row b, columns [out_col_off + hq*128, +128) of every matrix in out[0..n_out).  Normally one
+    // local [batch, Hq*128] matrix; with head sharding the same slice is stored into every rank's full-width
+    // matrix (out[] then holds peer-mapped pointers: plain stores over NVLink, nothing is loaded from a peer).
+    __half *out[8];
+    int n_out;
+    int64_t out_row_stride;
+    int64_t out_col_off;
     const __half *k_new;  // fused append: [batch, Hkv, D] rows of the newest token, or nullptr
     const __half *v_new;
     const int32_t *block_table;
@@ -337,7 +343,8 @@ __device__ __forceinline__ void merge_splits(const AttnParams &p, int b, int hq0
             uint2 pk;
             pk.x = *reinterpret_cast<uint32_t *>(&h01);
             pk.y = *reinterpret_cast<uint32_t *>(&h23);
-            *reinterpret_cast<uint2 *>(p.o + ((int64_t)b * p.num_q_heads + hqa) * kD + lane * 4) = pk;
+            const int64_t at = (int64_t)b * p.out_row_stride + p.out_col_off + (int64_t)hqa * kD + lane * 4;
+            for (int r = 0; r < p.n_out; ++r) *reinterpret_cast<uint2 *>(p.out[r] + at) = pk;
         }
         if (two) {
             const float inv = 1.f / wb;
@@ -346,7 +353,8 @@ __device__ __forceinline__ void merge_splits(const AttnParams &p, int b, int hq0
             uint2 pk;
             pk.x = *reinterpret_cast<uint32_t *>(&h01);
             pk.y = *reinterpret_cast<uint32_t *>(&h23);
-            *reinterpret_cast<uint2 *>(p.o + ((int64_t)b * p.num_q_heads + hqb) * kD + lane * 4) = pk;
+            const int64_t at = (int64_t)b * p.out_row_stride + p.out_col_off + (int64_t)hqb * kD + lane * 4;
+            for (int r = 0; r < p.n_out; ++r) *reinterpret_cast<uint2 *>(p.out[r] + at) = pk;
         }
     }
 }
@@ -644,15 +652,18 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
         const float inv0 = 1.f / l0, inv1 = 1.f / l1;
         const int hq0 = cur.h * G;  // first query head of the group
         if (cur.nsplit == 1) {
-            __half *ob = p.o + ((int64_t)cur.b * p.num_q_heads + hq0) * kD;
+            const int64_t at = (int64_t)cur.b * p.out_row_stride + p.out_col_off + (int64_t)hq0 * kD;
+            for (int r = 0; r < p.n_out; ++r) {
+                __half *ob = p.out[r] + at;
 #pragma unroll
-            for (int n = 0; n < 16; ++n) {
-                if (row0)
-                    *reinterpret_cast<__half2 *>(ob + (int64_t)g * kD + n * 8 + 2 * t) =
-                        __floats2half2_rn(oacc[n][0] * inv0, oacc[n][1] * inv0);
-                if (row1)
-                    *reinterpret_cast<__half2 *>(ob + (int64_t)(g + 8) * kD + n * 8 + 2 * t) =
-                        __floats2half2_rn(oacc[n][2] * inv1, oacc[n][3] * inv1);
+                for (int n = 0; n < 16; ++n) {
+                    if (row0)
+                        *reinterpret_cast<__half2 *>(ob + (int64_t)g * kD + n * 8 + 2 * t) =
+                            __floats2half2_rn(oacc[n][0] * inv0, oacc[n][1] * inv0);
+                    if (row1)
+                        *reinterpret_cast<__half2 *>(ob + (int64_t)(g + 8) * kD + n * 8 + 2 * t) =
+                            __floats2half2_rn(oacc[n][2] * inv1, oacc[n][3] * inv1);
+                }
             }
         } else {
             float *po = p.part_o + ((int64_t)cur.prow * p.num_q_heads + hq0) * kD;
@@ -872,8 +883,15 @@ int mkv_attn_plan(int device, void *stream, void *workspace, size_t workspace_by
     return MKV_OK;
 }
 
-static int attention_decode_impl(int device, void *stream, const void *q, void *o, const void *k_new,
-                                 const void *v_new, const mkv_pool *pool, const int32_t *block_table,
+struct OutputSpec {  // where the attention result goes (see AttnParams::out)
+    void *const *ptrs;
+    int n;
+    int64_t row_stride, col_off;
+};
+
+static int attention_decode_impl(int device, void *stream, const void *q, void *o, const OutputSpec *push,
+                                 const void *k_new, const void *v_new, const mkv_pool *pool,
+                                 const int32_t *block_table,
                                  int64_t table_stride, const int32_t *seq_ids, const int32_t *seq_lens, int batch,
                                  int num_q_heads, int cur_layer, float softmax_scale,
                                  int max_blocks_per_seq_in_batch, void *workspace, size_t workspace_bytes) {
@@ -929,7 +947,17 @@ static int attention_decode_impl(int device, void *stream, const void *q, void *
     AttnParams p;
     p.pool = pv;
     p.q = (const __half *)q;
-    p.o = (__half *)o;
+    if (push) {
+        p.n_out = push->n;
+        for (int i = 0; i < push->n; ++i) p.out[i] = (__half *)push->ptrs[i];
+        p.out_row_stride = push->row_stride;
+        p.out_col_off = push->col_off;
+    } else {
+        p.n_out = 1;
+        p.out[0] = (__half *)o;
+        p.out_row_stride = (int64_t)num_q_heads * kD;
+        p.out_col_off = 0;
+    }
     p.k_new = (const __half *)k_new;
     p.v_new = (const __half *)v_new;
     p.block_table = block_table;
@@ -957,7 +985,7 @@ int mkv_paged_attention_decode(int device, void *stream, const void *q, void *o,
                                const int32_t *seq_lens, int batch, int num_q_heads, int cur_layer,
                                float softmax_scale, int max_blocks_per_seq_in_batch, void *workspace,
                                size_t workspace_bytes) {
-    return attention_decode_impl(device, stream, q, o, nullptr, nullptr, pool, block_table, table_stride, seq_ids,
+    return attention_decode_impl(device, stream, q, o, nullptr, nullptr, nullptr, pool, block_table, table_stride, seq_ids,
                                  seq_lens, batch, num_q_heads, cur_layer, softmax_scale,
                                  max_blocks_per_seq_in_batch, workspace, workspace_bytes);
 }
@@ -968,8 +996,32 @@ int mkv_paged_attention_decode_append(int device, void *stream, const void *q, v
                                       int batch, int num_q_heads, int cur_layer, float softmax_scale,
                                       int max_blocks_per_seq_in_batch, void *workspace, size_t workspace_bytes) {
     if (batch > 0 && (!k_new || !v_new)) return MKV_ERR_NULL;
-    return attention_decode_impl(device, stream, q, o, k_new, v_new, pool, block_table, table_stride, seq_ids,
+    return attention_decode_impl(device, stream, q, o, nullptr, k_new, v_new, pool, block_table, table_stride, seq_ids,
                                  seq_lens, batch, num_q_heads, cur_layer, softmax_scale,
+                                 max_blocks_per_seq_in_batch, workspace, workspace_bytes);
+}
+
+int mkv_paged_attention_decode_push(int device, void *stream, const void *q, void *const *out_ptrs, int n_out,
+                                    int64_t out_row_stride, int64_t out_col_offset, const void *k_new,
+                                    const void *v_new, const mkv_pool *pool, const int32_t *block_table,
+                                    int64_t table_stride, const int32_t *seq_ids, const int32_t *seq_lens, int batch,
+                                    int num_q_heads, int cur_layer, float softmax_scale,
+                                    int max_blocks_per_seq_in_batch, void *workspace, size_t workspace_bytes) {
+    if (n_out < 1 || n_out > 8) return MKV_ERR_SHAPE;
+    if (!out_ptrs) return MKV_ERR_NULL;
+    if (out_row_stride < (int64_t)num_q_heads * 128 + out_col_offset || out_col_offset < 0) return MKV_ERR_SHAPE;
+    if ((out_row_stride % 8) != 0 || (out_col_offset % 8) != 0) return MKV_ERR_ALIGN;
+    for (int i = 0; i < n_out; ++i) {
+        if (!out_ptrs[i]) return MKV_ERR_NULL;
+        if (((uintptr_t)out_ptrs[i]) % 16 != 0) return MKV_ERR_ALIGN;
+    }
+    PoolView pv;
+    int st = validate_pool(pool, &pv);
+    if (st) return st;
+    if (!fast_path_ok(pv, num_q_heads, q, out_ptrs[0])) return MKV_ERR_SHAPE;  // fp16, head_dim 128, block 16 only
+    OutputSpec spec{out_ptrs, n_out, out_row_stride, out_col_offset};
+    return attention_decode_impl(device, stream, q, out_ptrs[0], &spec, k_new, v_new, pool, block_table,
+                                 table_stride, seq_ids, seq_lens, batch, num_q_heads, cur_layer, softmax_scale,
                                  max_blocks_per_seq_in_batch, workspace, workspace_bytes);
 }
 
@@ -1092,7 +1144,10 @@ int mkv_paged_attention_decode_noalloc(int device, void *stream, const void *q, 
     AttnParams p;
     p.pool = pv;
     p.q = (const __half *)q;
-    p.o = (__half *)o;
+    p.n_out = 1;
+    p.out[0] = (__half *)o;
+    p.out_row_stride = (int64_t)num_q_heads * kD;
+    p.out_col_off = 0;
     p.k_new = nullptr;
     p.v_new = nullptr;
     p.block_table = block_table;

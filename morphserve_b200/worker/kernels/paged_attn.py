@@ -12,6 +12,8 @@ chunks exist, :893-895); elastic blocks are resolved in the kernel.
 """
 from __future__ import annotations
 
+import ctypes as C
+
 import torch
 
 from ..._lib import check, lib
@@ -87,3 +89,49 @@ def paged_attention(
         dev, stream, q.data_ptr(), o.data_ptr(), pool, block_table.data_ptr(), block_table.stride(0),
         seq_ids.data_ptr(), lens.data_ptr(), batch, hq, cur_layer, float(infer_state.softmax_scale),
         max_blocks, ws.tensor.data_ptr(), ws.nbytes), "mkv_paged_attention_decode")
+
+
+def paged_attention_push(
+    q: torch.Tensor,                # [num_decoding_seqs, local num_q_heads, head_dim]
+    k_cache: torch.Tensor,          # this rank's KV heads only: [num_blocks, num_layers, local num_kv_heads, 16, 128]
+    v_cache: torch.Tensor,
+    k_cache_new: list,
+    v_cache_new: list,
+    block_table: torch.Tensor,
+    model_config,                   # num_q_heads / num_kv_heads are the LOCAL counts
+    engine_config,
+    infer_state,
+    cur_layer: int,
+    out_ptrs,                       # device addresses of every destination matrix [batch, out_row_stride] fp16
+    out_row_stride: int,            # elements per destination row (= total query heads * head_dim)
+    out_col_offset: int,            # first column of this rank's slice (= first local query head * head_dim)
+    k_new: torch.Tensor = None,     # optional fused append of the newest token's rows [batch, local kv heads, 128]
+    v_new: torch.Tensor = None,
+):
+    """Decode attention for KV-head sharding (no counterpart in the single-GPU reference): the result is
+    stored into the same column slice of every matrix in ``out_ptrs`` - the local one and, through
+    peer-mapped pointers, the other ranks' - from inside the kernel, replacing attention + all-gather.
+    The caller runs a barrier across the ranks before anyone reads its matrix."""
+    assert q.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous() and block_table.is_contiguous()
+    require_cuda(q, "q")
+    batch = infer_state.num_decoding_seqs
+    if batch == 0:
+        return
+    dev, stream = device_and_stream(q)
+    hq, hkv, d = model_config.num_q_heads, model_config.num_kv_heads, model_config.head_dim
+    bs = engine_config.block_size
+    pool = make_pool(k_cache, v_cache, k_cache_new, v_cache_new,
+                     infer_state.num_blocks_org, infer_state.kv_cache_new_block_size)
+    lens = infer_state.decoding_seq_lens
+    seq_ids = infer_state.seq_ids[infer_state.num_prefill_seqs:]
+    max_len = getattr(infer_state, "max_decoding_len", None) or engine_config.max_blocks_per_seq * bs
+    max_blocks = min((max_len + bs - 1) // bs, block_table.shape[1])
+    ws = attn_workspace(dev, batch, hq, hkv, d, max_blocks)
+    _plan_for(infer_state, ws, dev, stream, lens, seq_ids, batch, hq, hkv, d, bs, max_blocks)
+    ptrs = (C.c_void_p * len(out_ptrs))(*[int(x) for x in out_ptrs])
+    check(lib.mkv_paged_attention_decode_push(
+        dev, stream, q.data_ptr(), ptrs, len(out_ptrs), int(out_row_stride), int(out_col_offset),
+        k_new.data_ptr() if k_new is not None else None, v_new.data_ptr() if v_new is not None else None,
+        pool, block_table.data_ptr(), block_table.stride(0), seq_ids.data_ptr(), lens.data_ptr(), batch, hq,
+        cur_layer, float(infer_state.softmax_scale), max_blocks, ws.tensor.data_ptr(), ws.nbytes),
+        "mkv_paged_attention_decode_push")

@@ -102,6 +102,14 @@ def test_block_manager_trace_matches_reference_fixture():
         assert bm.num_free_blocks.item() == int(gold[f"nfree_{i}"])
     with pytest.raises(RuntimeError):
         bm._allocate_blocks(int(bm.num_free_blocks) + 1)
+    # _allocate_blocks / _free_blocks (worker/block_manager.py:64-85): first-fit ascending, then back
+    before = bm.is_block_free.clone()
+    nfree = int(bm.num_free_blocks)
+    got = bm._allocate_blocks(5)
+    expect = torch.nonzero(before)[:5].view(-1)
+    assert torch.equal(got, expect) and not bm.is_block_free[got].any() and int(bm.num_free_blocks) == nfree - 5
+    bm._free_blocks(got)
+    assert torch.equal(bm.is_block_free, before) and int(bm.num_free_blocks) == nfree
     ids = H.to_dev(np.array([0], dtype=np.int32))
     bm.allocate_blocks_for_seqs(ids, H.to_dev(np.array([40], dtype=np.int32)))
     with pytest.raises(AssertionError):
@@ -184,3 +192,32 @@ def test_plain_kernel_other_shapes():
         _close(o, ex)
         # the reference stores fp16-rounded values even into an fp32 `o`
         assert np.array_equal(o, o.astype(np.float16).astype(o.dtype))
+
+
+def test_push_variant_writes_the_column_slice_of_every_destination():
+    """mkv_paged_attention_decode_push with two destination matrices on one GPU (they stand for two ranks'
+    buffers): both get this "rank's" heads at the column offset, nothing else is touched, and the fused
+    append still lands in the pool."""
+    from morphserve_b200 import paged_attention, paged_attention_push
+    c = cases.build_decode_case(seed=31, B=21, Hq=8, Hkv=2, D=128, bs=16, L=2, layer=1, num_blocks_org=900,
+                                dtype=np.float16, max_len=1200)
+    d = H.device_case(c)
+    mc, ec = H.cfgs(d, d["block_table_t"].shape[1])
+    st = H.decode_state(d, d["seq_ids_t"], d["seq_lens_t"])
+    kc, vc = d["k_pools_t"][0], d["v_pools_t"][0]
+    total_heads, first_head = 24, 8                      # this shard holds heads 8..15 of 24
+    outs = [torch.full((d["B"], total_heads * 128), 7.0, dtype=torch.float16, device="cuda") for _ in range(2)]
+    paged_attention_push(d["q_t"], kc, vc, [], [], d["block_table_t"], mc, ec, st, d["layer"],
+                         [o.data_ptr() for o in outs], total_heads * 128, first_head * 128,
+                         k_new=d["k_new_t"], v_new=d["v_new_t"])
+    ref = torch.zeros((d["B"], d["Hq"] * 128), dtype=torch.float16, device="cuda")
+    st2 = H.decode_state(d, d["seq_ids_t"], d["seq_lens_t"])
+    paged_attention(d["q_t"], kc, vc, [], [], d["block_table_t"], mc, ec, st2, d["layer"], ref)   # pool already appended
+    torch.cuda.synchronize()
+    kpo, vpo = [p.copy() for p in c["k_pools"]], [p.copy() for p in c["v_pools"]]
+    O.store_kvcache_decode(c["k_new"], c["v_new"], kpo, vpo, c["block_table"], c["seq_ids"], c["seq_lens"],
+                           c["layer"], c["num_blocks_org"], 0)
+    assert kc.cpu().numpy().tobytes() == kpo[0].tobytes() and vc.cpu().numpy().tobytes() == vpo[0].tobytes()
+    for o in outs:
+        assert torch.equal(o[:, first_head * 128:(first_head + 8) * 128], ref)
+        assert (o[:, : first_head * 128] == 7.0).all() and (o[:, (first_head + 8) * 128:] == 7.0).all()
