@@ -124,7 +124,7 @@ int mkv_paged_attention_decode(
  * Same results as the two separate calls (the append is bit-exact); saves one
  * launch per layer.  Shapes outside the fast path fall back to the two kernels.
  * Replaces the pair of call sites worker/layers/transformer_layer.py:117-126 and
- * :181-187 when the caller opts in (see INTEGRATION.md).
+ * :181-187 when the caller opts in.
  */
 int mkv_paged_attention_decode_append(
     int device, void *stream, const void *q, void *o, const void *k_new, const void *v_new,
