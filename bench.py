@@ -36,17 +36,17 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # BASELINE configs[2]: the configuration the tokens/s-at-1/2/4/8 metric is quoted on
+    # Llama-3-8B GQA, 256 sequences per GPU: the configuration the tokens/s-at-1/2/4/8-GPUs metric is quoted on
     "llama3-8b-gqa-decode": dict(cfg=3, B=256, Hq=32, Hkv=8, L=32, max_len=1536, free_frac=0.10),
-    # BASELINE configs[1]
+    # Llama-2-7B MHA, 64 sequences, contexts up to 768
     "llama2-7b-mha-decode": dict(cfg=2, B=64, Hq=32, Hkv=32, L=32, max_len=768, free_frac=0.30),
-    # BASELINE configs[4], sequence-sharded form
+    # CodeLlama-34B GQA, 512 sequences per GPU, sequence-sharded
     "codellama-34b-gqa-decode": dict(cfg=5, B=512, Hq=64, Hkv=8, L=48, max_len=1536, free_frac=0.05),
-    # BASELINE configs[4], head-sharded form: every rank holds Hkv/N KV heads (and their query heads) of ALL
+    # CodeLlama-34B GQA, head-sharded: every rank holds Hkv/N KV heads (and their query heads) of ALL
     # 512*N sequences; the attention outputs are all-gathered over NVLink (NCCL) after every layer
     "codellama-34b-gqa-decode-headshard": dict(cfg=5, B=512, Hq=64, Hkv=8, L=48, max_len=1536, free_frac=0.05,
                                                head_shard=True),
-    # BASELINE configs[3] pool shape: compaction of a 16384-block pool down to 10240 (copy + remap timing only)
+    # elastic-resize pool (Llama-3-8B shape): compaction of a 16384-block pool down to 10240 (copy + remap timing)
     "kv-resize": dict(cfg=4, resize=True, L=32, Hq=32, Hkv=8, B=128, max_len=1536, nb_org=8192, chunk=1024,
                       n_chunks=8, release=6),
     # the same with 4 layers (pool 4 GB) for profiler captures
@@ -67,9 +67,9 @@ WORKLOADS = {
 }
 D, BS = 128, 16
 FALLBACK_HBM_GBS = 6650.0
-# DRAM bytes (read + write) per attention launch divided by the algorithmic K/V bytes, from the ncu capture
-# summarised in profiles/attn_decode_f16_kernel__llama3-8b-gqa-decode-2layer.md (same batch and bytes per launch as
-# llama3-8b-gqa-decode; 863.6 MB moved for 851 MB of K/V).  Traffic grows with the units processed, so the
+# DRAM bytes (read + write) per attention launch divided by the algorithmic K/V bytes, from an ncu capture of the
+# llama3-8b-gqa-decode-2layer workload (same batch and bytes per launch as llama3-8b-gqa-decode; 863.6 MB moved for
+# 851 MB of K/V).  Traffic grows with the units processed, so the
 # ratio is applied to the live byte count of the timed launches.
 NCU_TRAFFIC_RATIO = {"llama3-8b-gqa-decode": 1.0148, "llama3-8b-gqa-decode-2layer": 1.0148}
 

@@ -74,7 +74,8 @@ def case_inputs_hash(c) -> str:
                      c["block_table"], c["seq_ids"], c["seq_lens"])
 
 
-# name -> kwargs of build_decode_case.  cfg1* is BASELINE config 1 verbatim.
+# name -> kwargs of build_decode_case.  cfg1* is the CPU-plumbing configuration: 4 sequences, 32 MHA heads,
+# head_dim 128, block 16, fp32, contexts uniform in [1,512], 256-block pool.
 DECODE_CASES = {
     "cfg1_mha_fp32": dict(seed=1000, B=4, Hq=32, Hkv=32, D=128, bs=16, L=1, layer=0,
                           num_blocks_org=256, dtype=np.float32, max_len=512),

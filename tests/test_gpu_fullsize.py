@@ -1,4 +1,4 @@
-"""Full-size runs of the BASELINE configurations on the GPU, checked through
+"""Full-size runs of the benchmark configurations on the GPU, checked through
 properties that do not need a CPU copy of a 27-32 GB pool:
 
 * appended K/V rows are read back bit-exact from the position the block table
@@ -110,7 +110,8 @@ def _block_checksums(pool):
 
 
 def test_elastic_resize_trace_full_size():
-    """BASELINE configs[3]: 8192 -> 16384 blocks, release 40 % by compaction, 100 decode steps of batch 128."""
+    """Elastic trace at full size (Llama-3-8B pool shape): 8192 -> 16384 blocks, release 40 % by compaction,
+    100 decode steps of batch 128."""
     from morphserve_b200 import BlockManager, paged_attention, store_kvcache
     from morphserve_b200.server import memory_utils as MU
     L, Hq, Hkv = 32, 32, 8
