@@ -54,6 +54,8 @@ WORKLOADS = {
                             n_chunks=8, release=6),
     # llama3-8b batch, 2 layers, every context exactly 768 tokens (no length spread): isolates scheduling effects
     "llama3-8b-gqa-decode-2layer-uniform": dict(cfg=3, B=256, Hq=32, Hkv=8, L=2, min_len=768, max_len=768, free_frac=0.10),
+    # prefill scatter of store_kvcache: 32 prompts of up to 2048 tokens into a fragmented pool, 4 layers
+    "kv-prefill": dict(cfg=3, prefill=True, L=4, Hq=32, Hkv=8, n_seqs=32, max_len=2048),
     # block swap between the pool and the host swap space (Llama-3-8B block = 2 x 1 MiB): 1024 blocks per direction
     "kv-swap": dict(cfg=3, swap=True, L=32, Hq=32, Hkv=8, nb=4096, n_swap=1024),
     # the same with the all-gather folded into the attention launch: every rank stores its output slice straight
@@ -459,6 +461,59 @@ def resize_bench(w, K, W, device):
 
 
 # ----------------------------------------------------------------------------
+# prefill scatter
+# ----------------------------------------------------------------------------
+def prefill_bench(w, K, W, device):
+    """store_kvcache for a prefill-only batch: every prompt token's K/V row goes to its block."""
+    from types import SimpleNamespace
+
+    import morphserve_b200 as mk
+    L, Hkv, n_seqs = w["L"], w["Hkv"], w["n_seqs"]
+    g = torch.Generator().manual_seed(1000 * w["cfg"] + 5)
+    lens = torch.randint(w["max_len"] // 2, w["max_len"] + 1, (n_seqs,), generator=g)
+    need = (lens + BS - 1) // BS
+    nb = int(need.sum()) * 2
+    perm = torch.randperm(nb, generator=g)
+    mbps = int(need.max()) + 1
+    table = torch.full((n_seqs, mbps), -1, dtype=torch.int32)
+    pos = 0
+    for i in range(n_seqs):
+        table[i, : int(need[i])] = perm[pos:pos + int(need[i])].to(torch.int32)
+        pos += int(need[i])
+    ntok = int(lens.sum())
+    k = torch.randn((ntok, Hkv, D), dtype=torch.float16, device=device)
+    v = torch.randn((ntok, Hkv, D), dtype=torch.float16, device=device)
+    k_cache = torch.zeros((nb, L, Hkv, BS, D), dtype=torch.float16, device=device)
+    v_cache = torch.zeros((nb, L, Hkv, BS, D), dtype=torch.float16, device=device)
+    z = torch.zeros(0, dtype=torch.int32, device=device)
+    lens_d = lens.to(torch.int32).to(device)
+    st = mk.LlamaInferState(
+        batch_size=n_seqs, num_tokens=ntok, seq_ids=torch.arange(n_seqs, dtype=torch.int32, device=device),
+        softmax_scale=D ** -0.5, num_prefill_seqs=n_seqs, num_prefill_tokens=ntok,
+        prefill_seq_start_locs=(torch.cumsum(lens_d, 0, dtype=torch.int32) - lens_d), prefill_seq_start_locs_with_end=z,
+        prefill_seq_lens=lens_d, max_prefill_len=int(lens.max()), num_decoding_seqs=0, decoding_seq_lens=z,
+        max_decoding_len=0, seq_block_size=512, num_seq_blocks=0, num_blocks_org=nb, kv_cache_new_block_size=0,
+        org_layer_param_size=0, position_cos=z, position_sin=z, ignore_kvcache=False)
+    mc = SimpleNamespace(num_layers=L, num_q_heads=w["Hq"], num_kv_heads=Hkv, head_dim=D)
+    ec = SimpleNamespace(block_size=BS, max_blocks_per_seq=mbps)
+    bt = table.to(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(W):
+        for layer in range(L):
+            mk.store_kvcache(k, v, k_cache, v_cache, [], [], bt, mc, ec, st, layer)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(K):
+        for layer in range(L):
+            mk.store_kvcache(k, v, k_cache, v_cache, [], [], bt, mc, ec, st, layer)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / (K * L)
+    nbytes = 2 * 2 * ntok * Hkv * D * 2          # K and V, read + write
+    return {"tokens": ntok, "ms_per_launch": ms, "bytes_per_launch": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9}
+
+
+# ----------------------------------------------------------------------------
 # block swap
 # ----------------------------------------------------------------------------
 def swap_bench(w, K, W, device):
@@ -525,6 +580,19 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     base = WORKLOADS[args.workload]
+    if base.get("prefill"):
+        assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+        torch.cuda.set_device(local_rank)
+        if rank == 0:
+            r = prefill_bench(base, max(K, 3), max(W, 3), torch.device("cuda", local_rank))
+            peak, peak_kind = measured_peak()
+            print(json.dumps({"metric": "prefill_scatter_gbs", "value": r["gbs"], "unit": "GB/s", "n_gpus": 1,
+                              "higher_is_better": True, "dtype": "u8", "data": "synthetic",
+                              "config": {"workload": args.workload},
+                              "roofline": {"kernel": "store_kv_prefill_kernel", "bound": "hbm", "achieved": r["gbs"],
+                                           "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                                           "frac": r["gbs"] / peak, "traffic": None}, "prefill": r}))
+        return
     if base.get("swap"):
         assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
         torch.cuda.set_device(local_rank)

@@ -121,6 +121,7 @@ def test_block_manager_trace_matches_reference_fixture():
 SWEEP = [
     (1, 8, 8, 1, 1, 0), (1, 4, 1, 4096, 1, 0), (3, 16, 1, 700, 2, 1), (5, 12, 4, 300, 2, 0),
     (17, 32, 8, 1536, 2, 1), (64, 32, 32, 768, 1, 0), (9, 2, 1, 2500, 1, 0), (33, 64, 8, 1536, 1, 0),
+    (2, 32, 8, 20000, 1, 0),        # long context, tiny batch: every sequence is cut into dozens of chunks
 ]
 
 
