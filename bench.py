@@ -234,8 +234,8 @@ class DecodeJob:
         """One decode step with every input already in HBM."""
         self.lens_host += 1
         self.lens_dev += 1
+        st = self.infer_state(self.seq_ids, self.lens_dev)      # host work first: the allocate below synchronises
         self.bm.allocate_blocks_for_seqs(self.seq_ids, self.lens_dev)
-        st = self.infer_state(self.seq_ids, self.lens_dev)
         self.layers(st, self.q, self.kn, self.vn, self.o)
 
     def make_host_buffers(self):
