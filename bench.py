@@ -66,6 +66,11 @@ WORKLOADS = {
     "small-gqa-decode": dict(cfg=9, B=64, Hq=32, Hkv=8, L=4, max_len=1536, free_frac=0.10),
     # the llama3-8b batch with 2 layers: same bytes per attention launch as the full workload, pool ~1.8 GB
     "llama3-8b-gqa-decode-2layer": dict(cfg=3, B=256, Hq=32, Hkv=8, L=2, max_len=1536, free_frac=0.10),
+    # one 32k-token sequence among 127 short ones, 2 layers: the case that needs split-KV to stay balanced
+    "skewed-gqa-decode": dict(cfg=10, B=128, Hq=32, Hkv=8, L=2, max_len=512, free_frac=0.10, n_long=1,
+                              long_len=32768),
+    # 8 long sequences (8k-32k tokens), 2 layers: fewer (sequence, head) pairs than worker warps
+    "longctx-gqa-decode": dict(cfg=11, B=8, Hq=32, Hkv=8, L=2, min_len=8192, max_len=32768, free_frac=0.10),
 }
 D, BS = 128, 16
 FALLBACK_HBM_GBS = 6650.0
@@ -129,12 +134,13 @@ def draw_lengths_and_tables(w, rank, growth_tokens):
     """Seeded lengths and a block table built from a shuffled free list."""
     g = torch.Generator().manual_seed(w.get("seed", 1000 * w["cfg"] + rank))
     lens = torch.randint(w.get("min_len", 1), w["max_len"] + 1, (w["B"],), generator=g, dtype=torch.int64)
+    lens[:w.get("n_long", 0)] = w.get("long_len", 0)
     need = (lens + BS - 1) // BS
     live = int(need.sum())
     growth = w["B"] * ((growth_tokens + BS - 1) // BS + 1)
     nb = int(np.ceil(live / (1.0 - w["free_frac"]))) + growth
     perm = torch.randperm(nb, generator=g)
-    mbps = (w["max_len"] + growth_tokens + BS - 1) // BS + 1
+    mbps = (max(w["max_len"], w.get("long_len", 0)) + growth_tokens + BS - 1) // BS + 1
     return lens, need, nb, perm, mbps, g
 
 
@@ -623,7 +629,8 @@ def main():
     head_shard = bool(base.get("head_shard"))
     config = {"workload": args.workload, "baseline_config": base["cfg"], "global_batch": w["B_global"],
               "batch_per_gpu": w["B"], "num_q_heads": base["Hq"], "num_kv_heads": base["Hkv"], "head_dim": D,
-              "block_size": BS, "num_layers": w["L"], "context_len": f"uniform[1,{w['max_len']}] + 1 per step",
+              "block_size": BS, "num_layers": w["L"], "context_len": f"uniform[{w.get('min_len', 1)},{w['max_len']}] + 1 per step"
+              + (f"; first {w['n_long']} at {w['long_len']}" if w.get("n_long") else ""),
               "sharding": ((f"kv heads x{world}, o pushed to all ranks from the attention epilogue" if base.get("push")
                             else f"kv heads x{world} + all-gather of o per layer") if head_shard
                            else f"sequence x{world}"),

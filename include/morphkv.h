@@ -158,8 +158,12 @@ int mkv_paged_attention_decode_push(
  * warps per SM and ring stages (values <= 0 keep the current ones) and the
  * number of work units planned per worker warp (<= 0 keeps).  Changing the item
  * factor changes mkv_attn_workspace_bytes: re-query it and plan again.
+ * `split_balance` (< 0 keeps; default 1.5): a sequence is only cut into chunks
+ * when it is longer than split_balance x the mean number of KV blocks per worker
+ * warp, since every cut costs fp32 partial rows and a merge; 0 cuts as finely as
+ * the item factor allows.
  */
-int mkv_attn_configure(int warps, int stages, double item_factor);
+int mkv_attn_configure(int warps, int stages, double item_factor, double split_balance);
 
 /*
  * Copies the device-side error word of a workspace to `*flags` (synchronises the

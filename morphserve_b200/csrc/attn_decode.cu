@@ -72,6 +72,21 @@ static double item_factor() {
     return g_item_factor;
 }
 
+// A sequence is only cut into chunks shorter than split_balance() x the mean number of blocks per worker warp:
+// a cut costs fp32 partial rows and a merge, and pays only when one unit would otherwise outlast the rest.
+static double g_split_balance = -1.0;
+static double split_balance() {
+    if (g_split_balance < 0.0) {
+        const char *e = getenv("MKV_ATTN_SPLIT_BALANCE");  // tuning knob; 0 = cut as fine as the item cap allows
+        g_split_balance = e ? atof(e) : 1.5;
+        if (g_split_balance < 0.0) g_split_balance = 0.0;
+    }
+    return g_split_balance;
+}
+static float plan_balance(int sm_count, int num_kv_heads) {
+    return (float)(split_balance() * (double)num_kv_heads / ((double)sm_count * 8.0));
+}
+
 static WsLayout make_layout(int sm_count, int batch, int num_q_heads, int num_kv_heads, int head_dim,
                             int max_blocks) {
     WsLayout L;
@@ -128,8 +143,10 @@ __device__ __forceinline__ int plan_scan(int v, int &total, int *warp_sums) {
 __global__ void __launch_bounds__(1024) attn_plan_kernel(WsHeader *hdr, int4 *items, int4 *items_tmp,
                                                        int *arrive, const int32_t *__restrict__ seq_lens,
                                                        const int32_t *__restrict__ seq_ids, int batch,
-                                                       int num_kv_heads, int block_size, int cap_items) {
+                                                       int num_kv_heads, int block_size, int cap_items,
+                                                       float balance) {
     __shared__ int cnt[kNumCand];
+    __shared__ int s_total_blocks;
     __shared__ int hist[kSortBins + 1];
     __shared__ int start[kSortBins + 1];
     __shared__ int warp_sums[33];
@@ -137,12 +154,14 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(WsHeader *hdr, int4 *it
     const int tid = threadIdx.x;
 
     for (int k = tid; k < kNumCand; k += blockDim.x) cnt[k] = 0;
+    if (tid == 0) s_total_blocks = 0;
     for (int k = tid; k <= kSortBins; k += blockDim.x) hist[k] = 0;
     __syncthreads();
     for (int b = tid; b < batch; b += blockDim.x) {
         int len = seq_lens[b];
         int nblk = len > 0 ? (len + block_size - 1) / block_size : 0;
         if (nblk > 0) {
+            atomicAdd(&s_total_blocks, nblk);
             for (int k = 0; k < kNumCand; ++k) {
                 int c = chunk_candidate(k);
                 atomicAdd(&cnt[k], (nblk + c - 1) / c);
@@ -153,6 +172,9 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(WsHeader *hdr, int4 *it
     if (tid == 0) {
         int k = 0;
         while (k < kNumCand - 1 && cnt[k] > cap_items) ++k;
+        // balance x total blocks = the longest chunk worth keeping whole (see split_balance())
+        const float keep_whole = balance * (float)s_total_blocks;
+        while (k < kNumCand - 1 && (float)chunk_candidate(k + 1) <= keep_whole) ++k;
         s_chunk = chunk_candidate(k);
     }
     __syncthreads();
@@ -167,7 +189,10 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(WsHeader *hdr, int4 *it
             row = seq_ids[b];
             nblk = len > 0 ? (len + block_size - 1) / block_size : 0;
         }
-        const int ns = (nblk + chunk - 1) / chunk;
+        // chunk-sized pieces; a remainder of up to a quarter chunk stays with the piece before it (a 97-block
+        // context cut at 96 is one unit, not 96 + 1).  Equal pieces measured faster than an even division.
+        int ns = (nblk + chunk - 1) / chunk;
+        if (ns > 1 && nblk - (ns - 1) * chunk <= chunk / 4) --ns;
         const int pr = ns > 1 ? ns : 0;
         int tot_i, tot_r;
         const int off_i = plan_scan(ns, tot_i, warp_sums);
@@ -175,7 +200,7 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(WsHeader *hdr, int4 *it
         if (b < batch) {
             for (int s = 0; s < ns; ++s) {
                 int pos = carry_items + off_i + s;
-                int n = min(chunk, nblk - s * chunk);
+                int n = (s == ns - 1) ? nblk - s * chunk : chunk;
                 if (pos < cap_items) {
                     // item = (batch index, first block, blocks, chunk index | len, chunks, partial row, table row)
                     items_tmp[2 * pos] = make_int4(b, s * chunk, n, s);
@@ -878,7 +903,8 @@ int mkv_attn_plan(int device, void *stream, void *workspace, size_t workspace_by
     char *ws = (char *)workspace;
     attn_plan_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(
         (WsHeader *)ws, (int4 *)(ws + L.items), (int4 *)(ws + L.items_tmp),
-        (int *)(ws + L.arrive), seq_lens, seq_ids, batch, num_kv_heads, block_size, L.cap_items);
+        (int *)(ws + L.arrive), seq_lens, seq_ids, batch, num_kv_heads, block_size, L.cap_items,
+        plan_balance(sms, num_kv_heads));
     MKV_LAUNCH_CHECK();
     return MKV_OK;
 }
@@ -1025,7 +1051,7 @@ int mkv_paged_attention_decode_push(int device, void *stream, const void *q, voi
                                  max_blocks_per_seq_in_batch, workspace, workspace_bytes);
 }
 
-int mkv_attn_configure(int warps, int stages, double item_factor_value) {
+int mkv_attn_configure(int warps, int stages, double item_factor_value, double split_balance_value) {
     AttnConfig &c = attn_config();
     if (warps > 0 && stages > 1) {
         c.warps = warps;
@@ -1035,6 +1061,7 @@ int mkv_attn_configure(int warps, int stages, double item_factor_value) {
         item_factor();
         g_item_factor = item_factor_value;
     }
+    if (split_balance_value >= 0.0) g_split_balance = split_balance_value;
     return MKV_OK;
 }
 
@@ -1139,7 +1166,8 @@ int mkv_paged_attention_decode_noalloc(int device, void *stream, const void *q, 
     // done counters, the arrival counters of every (sequence, kv head), the item list.
     attn_plan_kernel<<<1, 1024, 0, s>>>((WsHeader *)ws, (int4 *)(ws + L.items), (int4 *)(ws + L.items_tmp),
                                         (int *)(ws + L.arrive), seq_lens, seq_ids,
-                                        batch, pv.num_kv_heads, pv.block_size, L.cap_items);
+                                        batch, pv.num_kv_heads, pv.block_size, L.cap_items,
+                                        plan_balance(sms, pv.num_kv_heads));
     MKV_LAUNCH_CHECK();
     AttnParams p;
     p.pool = pv;

@@ -150,6 +150,37 @@ def test_decode_attention_sweep_against_oracle(B, Hq, Hkv, max_len, L, layer):
     assert read_attn_error_flags(0) == 0
 
 
+@pytest.mark.parametrize("balance", [0.0, 1.5, 1000.0])
+@pytest.mark.parametrize("shape", ["spread", "one_long"])
+def test_split_rule_extremes(balance, shape):
+    """The plan cuts a sequence only when it is long against the mean load of a worker warp.  Finest cut (0),
+    the default, and "never cut" (1000) must all give the oracle's result, on a batch with a spread of lengths
+    and on one long sequence among short ones."""
+    from morphserve_b200._lib import lib, check
+    rs = np.random.RandomState(314)
+    if shape == "spread":
+        B, Hq, Hkv = 48, 32, 8
+        lens = rs.randint(1, 1553, size=B)
+        lens[0] = 1552            # 97 blocks: one more than a power-of-two-times-three chunk
+    else:
+        B, Hq, Hkv = 24, 16, 4
+        lens = rs.randint(1, 200, size=B)
+        lens[5] = 9000
+    nb = int(((lens + 15) // 16).sum()) + 5
+    c = cases.build_decode_case(seed=2718, B=B, Hq=Hq, Hkv=Hkv, D=128, bs=16, L=1, layer=0, num_blocks_org=nb,
+                                dtype=np.float16, lens=lens)
+    check(lib.mkv_attn_configure(-1, -1, -1.0, balance), "mkv_attn_configure")
+    try:
+        o, kp, vp = H.run_decode_step(H.device_case(c))
+    finally:
+        check(lib.mkv_attn_configure(-1, -1, -1.0, 1.5), "mkv_attn_configure")
+    ex = O.paged_attention_exact(c["q"], kp, vp, c["block_table"], c["seq_ids"], c["seq_lens"], 0, c["scale"],
+                                 c["num_blocks_org"], 0)
+    _close(o, ex)
+    from morphserve_b200.worker.kernels._common import read_attn_error_flags
+    assert read_attn_error_flags(0) == 0
+
+
 def test_every_length_across_block_and_chunk_edges():
     """lens 1..160 in one batch: every len % 16, single- and multi-block sequences."""
     lens = np.arange(1, 161)
