@@ -75,10 +75,11 @@ WORKLOADS = {
 D, BS = 128, 16
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes (read + write) per attention launch divided by the algorithmic K/V bytes, from an ncu capture of the
-# llama3-8b-gqa-decode-2layer workload (same batch and bytes per launch as llama3-8b-gqa-decode; 863.6 MB moved for
-# 851 MB of K/V).  Traffic grows with the units processed, so the
-# ratio is applied to the live byte count of the timed launches.
-NCU_TRAFFIC_RATIO = {"llama3-8b-gqa-decode": 1.0148, "llama3-8b-gqa-decode-2layer": 1.0148}
+# llama3-8b-gqa-decode-2layer workload (same batch and bytes per launch as llama3-8b-gqa-decode): 852.1 and 849.3 MB
+# moved by the two captured launches of the fourth step, whose contexts hold 832.6 MB of K/V (840.6 MB counted in
+# whole 16-token blocks, which is what the kernel fetches).  Traffic grows with the units processed, so the ratio is
+# applied to the live byte count of the timed launches.
+NCU_TRAFFIC_RATIO = {"llama3-8b-gqa-decode": 1.0217, "llama3-8b-gqa-decode-2layer": 1.0217}
 
 
 def measured_peak():
