@@ -69,6 +69,9 @@ WORKLOADS = {
     # one 32k-token sequence among 127 short ones, 2 layers: the case that needs split-KV to stay balanced
     "skewed-gqa-decode": dict(cfg=10, B=128, Hq=32, Hkv=8, L=2, max_len=512, free_frac=0.10, n_long=1,
                               long_len=32768),
+    # the default workload with the rotary embedding of q and k in front of every layer's append (the step before the
+    # path in the reference's layer code); fused into the attention launch unless --no-fused-rope
+    "llama3-8b-gqa-decode-rope": dict(cfg=3, B=256, Hq=32, Hkv=8, L=32, max_len=1536, free_frac=0.10, rope=True),
     # 8 long sequences (8k-32k tokens), 2 layers: fewer (sequence, head) pairs than worker warps
     "longctx-gqa-decode": dict(cfg=11, B=8, Hq=32, Hkv=8, L=2, min_len=8192, max_len=32768, free_frac=0.10),
 }
@@ -191,6 +194,13 @@ class DecodeJob:
         self.o = torch.zeros((L, B, Hq * D), dtype=torch.float16, device=device)
         self.nb = nb
         self._z = torch.zeros(0, dtype=torch.int32, device=device)
+        self.cos_table = self.sin_table = None
+        if w.get("rope"):
+            # the reference's tables (fp32 angles rounded to fp16), long enough for the run
+            inv_freq = 1.0 / (10000.0 ** (torch.arange(0, D, 2, device=device, dtype=torch.float32) / D))
+            t = torch.arange(mbps * BS + 128, device=device, dtype=torch.float32)
+            freqs = torch.outer(t, inv_freq)
+            self.cos_table, self.sin_table = torch.cos(freqs).to(torch.float16), torch.sin(freqs).to(torch.float16)
         self.dist = None
         if w.get("head_shard"):
             import torch.distributed as dist
@@ -213,12 +223,16 @@ class DecodeJob:
         B, Hkv = self.w["B"], self.w["Hkv"]
         max_len = int(self.lens_host.max())
         sbs, nsb = self.mk.infer_state.seq_block_size_heuristic(Hkv, self.lens_host.tolist())
+        cos = sin = self._z
+        if self.cos_table is not None:      # rows of the newest token's position, gathered once per step
+            pos = (lens_dev - 1).long()
+            cos, sin = self.cos_table[pos], self.sin_table[pos]
         return self.mk.LlamaInferState(
             batch_size=B, num_tokens=B, seq_ids=seq_ids, softmax_scale=D ** -0.5, num_prefill_seqs=0,
             num_prefill_tokens=0, prefill_seq_start_locs=self._z, prefill_seq_start_locs_with_end=self._z,
             prefill_seq_lens=self._z, max_prefill_len=0, num_decoding_seqs=B, decoding_seq_lens=lens_dev,
             max_decoding_len=max_len, seq_block_size=sbs, num_seq_blocks=nsb, num_blocks_org=self.nb,
-            kv_cache_new_block_size=0, org_layer_param_size=0, position_cos=self._z, position_sin=self._z,
+            kv_cache_new_block_size=0, org_layer_param_size=0, position_cos=cos, position_sin=sin,
             ignore_kvcache=False)
 
     def layers(self, st, q, kn, vn, o):
@@ -232,6 +246,8 @@ class DecodeJob:
                 self.symm.barrier()        # every rank's slice of this layer has landed everywhere
             return
         for layer in range(self.w["L"]):
+            if self.cos_table is not None:
+                mk.rotary_embedding_inplace(q[layer], kn[layer], st)
             mk.store_kvcache(kn[layer], vn[layer], self.k_cache, self.v_cache, [], [], bt, mc, ec, st, layer)
             mk.paged_attention(q[layer], self.k_cache, self.v_cache, [], [], bt, mc, ec, st, layer, o[layer])
             if self.dist is not None:      # head sharding: one all-gather of the output shards per layer
@@ -286,6 +302,8 @@ class DecodeJob:
             if layer + 1 < L:
                 copy_in(layer + 1)                   # next layer's inputs travel while this layer computes
             main.wait_event(self.ev_in[layer])
+            if self.cos_table is not None:
+                mk.rotary_embedding_inplace(self.dq[layer], self.dk[layer], st)
             mk.store_kvcache(self.dk[layer], self.dv[layer], self.k_cache, self.v_cache, [], [], bt, mc, ec, st, layer)
             mk.paged_attention(self.dq[layer], self.k_cache, self.v_cache, [], [], bt, mc, ec, st, layer,
                                self.o[layer])
@@ -517,7 +535,26 @@ def prefill_bench(w, K, W, device):
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / (K * L)
     nbytes = 2 * 2 * ntok * Hkv * D * 2          # K and V, read + write
-    return {"tokens": ntok, "ms_per_launch": ms, "bytes_per_launch": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9}
+    out = {"tokens": ntok, "ms_per_launch": ms, "bytes_per_launch": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9}
+    # rotary embedding of the same prompt tokens (q and k in place), the launch in front of the scatter
+    q = torch.randn((ntok, w["Hq"], D), dtype=torch.float16, device=device)
+    pos = torch.cat([torch.arange(int(n)) for n in lens]).to(device)
+    inv_freq = 1.0 / (10000.0 ** (torch.arange(0, D, 2, device=device, dtype=torch.float32) / D))
+    freqs = torch.outer(pos.float(), inv_freq)
+    st.position_cos, st.position_sin = torch.cos(freqs).to(torch.float16), torch.sin(freqs).to(torch.float16)
+    for _ in range(W):
+        mk.rotary_embedding_inplace(q, k, st)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(K * L):
+        mk.rotary_embedding_inplace(q, k, st)
+    e1.record()
+    torch.cuda.synchronize()
+    rope_ms = e0.elapsed_time(e1) / (K * L)
+    rope_bytes = 2 * ntok * (w["Hq"] + Hkv) * D * 2 + 2 * ntok * (D // 2) * 2   # q, k read + write; cos, sin read
+    out["rope"] = {"ms_per_launch": rope_ms, "bytes_per_launch": rope_bytes,
+                   "gbs": rope_bytes / (rope_ms * 1e-3) / 1e9}
+    return out
 
 
 # ----------------------------------------------------------------------------
@@ -578,6 +615,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-fused-rope", action="store_true",
+                    help="workloads with rotary embedding: run it as its own launch per layer")
     ap.add_argument("--no-fused-append", action="store_true",
                     help="launch the decode KV append as its own kernel (the reference's two-call structure) "
                          "instead of fusing it into the attention launch")
@@ -670,6 +709,10 @@ def main():
     from morphserve_b200 import _lib
     morphserve_b200.set_fused_decode_append(not args.no_fused_append)
     config["decode_append"] = "own launch" if args.no_fused_append else "fused into the attention launch"
+    if w.get("rope"):
+        fused_rope = not (args.no_fused_rope or args.no_fused_append)
+        morphserve_b200.set_fused_decode_rope(fused_rope)
+        config["rotary_embedding"] = "fused into the attention launch" if fused_rope else "own launch"
     job = DecodeJob(w, rank, growth_tokens=2 * (K + W) + 16, device=device)
 
     # ---- leg 1: inputs resident in HBM ----------------------------------------
@@ -713,6 +756,18 @@ def main():
     a1.record()
     torch.cuda.synchronize()
     append_ms = a0.elapsed_time(a1) / (reps * w["L"])
+    rope_ms = None
+    if w.get("rope"):       # the stand-alone rotary kernel on one layer's decode rows
+        was_fused = mk.rotary_emb.FUSE_DECODE_ROPE
+        mk.set_fused_decode_rope(False)
+        a0.record()
+        for _ in range(reps):
+            for layer in range(w["L"]):
+                mk.rotary_embedding_inplace(job.q[layer], job.kn[layer], st)
+        a1.record()
+        torch.cuda.synchronize()
+        rope_ms = a0.elapsed_time(a1) / (reps * w["L"])
+        mk.set_fused_decode_rope(was_fused)
     peak, peak_kind = measured_peak()
     attn_bytes = job.kv_bytes_per_layer()
     achieved = attn_bytes / (attn_ms * 1e-3) / 1e9
@@ -751,7 +806,7 @@ def main():
                          "traffic": (NCU_TRAFFIC_RATIO[args.workload] * attn_bytes
                                      if args.workload in NCU_TRAFFIC_RATIO else None),
                          "algorithmic_bytes_per_launch": attn_bytes, "ms_per_launch": attn_ms,
-                         "append_ms_per_launch": append_ms},
+                         "append_ms_per_launch": append_ms, "rope_ms_per_launch": rope_ms},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks.summary(),
         }
         print(json.dumps(line))

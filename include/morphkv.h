@@ -154,6 +154,32 @@ int mkv_paged_attention_decode_push(
     void *workspace, size_t workspace_bytes);
 
 /*
+ * Rotary position embedding of q [num_tokens, Hq, D] and k [num_tokens, Hkv, D] in place
+ * (replaces rotary_embedding_inplace, worker/kernels/rotary_emb.py:43-58, the step in front
+ * of store_kvcache: worker/layers/transformer_layer.py:93-98).  cos_table / sin_table:
+ * fp16 [num_tokens, D/2], the rows of the reference's tables gathered for the tokens'
+ * positions (worker/model.py:240-241, 432-433).  Halves [0, D/2) and [D/2, D) of every head
+ * become (x0*cos - x1*sin, x0*sin + x1*cos); with fp16 data every product and sum is rounded
+ * to fp16 on its own, as in the reference kernel.  elem_bytes 2 (fp16) or 4 (fp32).
+ */
+int mkv_rotary_embedding(int device, void *stream, void *q, void *k, const void *cos_table, const void *sin_table,
+                         int64_t num_tokens, int num_q_heads, int num_kv_heads, int head_dim, int elem_bytes);
+
+/*
+ * mkv_rotary_embedding (decode rows) + mkv_store_kv_decode + mkv_paged_attention_decode of one
+ * layer in ONE launch: q is rotated as it is loaded, the k_new row is rotated before it is
+ * patched into the staged tile and written to the pool.  rope_cos / rope_sin: fp16
+ * [batch, D/2], 16-byte aligned.  On the fused path (fp16, head_dim 128, block 16) q and k_new
+ * are left untouched in memory; for other shapes they are rotated in place by the stand-alone
+ * kernel first - either way `o` and the pool hold the same values as the three separate calls.
+ */
+int mkv_paged_attention_decode_rope_append(
+    int device, void *stream, void *q, void *o, void *k_new, const void *v_new, const void *rope_cos,
+    const void *rope_sin, const mkv_pool *pool, const int32_t *block_table, int64_t table_stride,
+    const int32_t *seq_ids, const int32_t *seq_lens, int batch, int num_q_heads, int cur_layer, float softmax_scale,
+    int max_blocks_per_seq_in_batch, void *workspace, size_t workspace_bytes);
+
+/*
  * Tuning knobs of the decode kernel (process-wide; not needed for normal use):
  * warps per SM and ring stages (values <= 0 keep the current ones) and the
  * number of work units planned per worker warp (<= 0 keeps).  Changing the item

@@ -4,6 +4,7 @@ Drop-in replacements, behind the reference's own Python names, for
 
   swiftllm.worker.kernels.paged_attn.paged_attention      -> worker.kernels.paged_attn
   swiftllm.worker.kernels.kvcache_mgmt.store_kvcache      -> worker.kernels.kvcache_mgmt
+  swiftllm.worker.kernels.rotary_emb.rotary_embedding_inplace -> worker.kernels.rotary_emb
   swiftllm.worker.kernels.block_mgmt.*                    -> worker.kernels.block_mgmt
   swiftllm.worker.block_manager.BlockManager              -> worker.block_manager
   swiftllm.worker.infer_state.LlamaInferState             -> worker.infer_state
@@ -26,9 +27,10 @@ from .server import memory_utils
 from .worker import block_manager, infer_state
 from .worker.block_manager import BlockManager
 from .worker.infer_state import LlamaInferState
-from .worker.kernels import block_mgmt, kvcache_mgmt, paged_attn
+from .worker.kernels import block_mgmt, kvcache_mgmt, paged_attn, rotary_emb
 from .worker.kernels.kvcache_mgmt import set_fused_decode_append, store_kvcache
 from .worker.kernels.paged_attn import paged_attention, paged_attention_push
+from .worker.kernels.rotary_emb import rotary_embedding_inplace, set_fused_decode_rope
 
 __version__ = "0.1.0"
 
@@ -36,6 +38,7 @@ _ALIASES = {
     "swiftllm.worker.kernels.paged_attn": paged_attn,
     "swiftllm.worker.kernels.kvcache_mgmt": kvcache_mgmt,
     "swiftllm.worker.kernels.block_mgmt": block_mgmt,
+    "swiftllm.worker.kernels.rotary_emb": rotary_emb,
     "swiftllm.worker.block_manager": block_manager,
     "swiftllm.worker.infer_state": infer_state,
     "swiftllm_c": swiftllm_c,
@@ -75,5 +78,6 @@ def install_as_swiftllm(overwrite: bool = True) -> None:
                 setattr(sys.modules[parent], parts[-1], mod)
 
 
-__all__ = ["paged_attention", "paged_attention_push", "store_kvcache", "set_fused_decode_append", "BlockManager", "LlamaInferState",
+__all__ = ["paged_attention", "paged_attention_push", "store_kvcache", "set_fused_decode_append",
+           "rotary_embedding_inplace", "set_fused_decode_rope", "BlockManager", "LlamaInferState",
            "swiftllm_c", "memory_utils", "install_as_swiftllm"]

@@ -56,6 +56,9 @@ SIGNATURES = {
     "mkv_attn_read_error_flags": (_i, [_i, _vp, _vp, C.POINTER(_i)]),
     "mkv_paged_attention_decode_noalloc": (_i, [_i, _vp, _vp, _vp, _pool, _vp, _i64, _vp, _vp, _i, _i, _i, _f, _i]),
     "mkv_noalloc_scratch_bytes": (_sz, []),
+    "mkv_rotary_embedding": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i]),
+    "mkv_paged_attention_decode_rope_append": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _pool, _vp, _i64, _vp, _vp,
+                                                   _i, _i, _i, _f, _i, _vp, _sz]),
     "mkv_store_kv_decode": (_i, [_i, _vp, _vp, _vp, _pool, _vp, _i64, _vp, _vp, _i, _i]),
     "mkv_store_kv_prefill": (_i, [_i, _vp, _vp, _vp, _pool, _vp, _i64, _vp, _vp, _vp, _i, _i, _i]),
     "mkv_block_need": (_i, [_i, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp]),

@@ -23,7 +23,7 @@ INCLUDE = os.path.join(ROOT, "include")
 OBJ = os.path.join(PKG, "build")
 LIB = os.path.join(PKG, "libmorphkv.so")
 
-SOURCES = ["core.cu", "kv_store.cu", "block_table.cu", "elastic.cu", "attn_decode.cu"]
+SOURCES = ["core.cu", "kv_store.cu", "block_table.cu", "elastic.cu", "rope.cu", "attn_decode.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
          "-I", INCLUDE, "-I", CSRC]

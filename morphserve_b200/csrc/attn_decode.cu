@@ -28,6 +28,7 @@
 #include <stdlib.h>
 
 #include "common.cuh"
+#include "rope.cuh"
 
 namespace mkv {
 
@@ -297,6 +298,10 @@ struct AttnParams {
     int64_t out_col_off;
     const __half *k_new;  // fused append: [batch, Hkv, D] rows of the newest token, or nullptr
     const __half *v_new;
+    // fused rotary embedding: cos/sin rows [batch, 64] of the newest token's position, or nullptr.  q and the
+    // k_new row are then rotated on their way in (q in the A fragments, k_new before it is patched and stored).
+    const __half *rope_cos;
+    const __half *rope_sin;
     const int32_t *block_table;
     int64_t table_stride;
     const int32_t *seq_ids;
@@ -528,6 +533,23 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
                 qf[kk][2] = row0 ? __ldg(q0 + kk * 8 + 4) : 0u;
                 qf[kk][3] = row1 ? __ldg(q1 + kk * 8 + 4) : 0u;
             }
+            if (p.rope_cos != nullptr) {
+                // k-step kk < 4 holds dims [16kk, 16kk+16) of the low half, kk+4 their partners in the high half;
+                // this thread's columns are 16kk + 2t (+1) and 16kk + 8 + 2t (+1)
+                const uint32_t *cb = reinterpret_cast<const uint32_t *>(p.rope_cos + (int64_t)cur.b * (kD / 2)) + t;
+                const uint32_t *sb = reinterpret_cast<const uint32_t *>(p.rope_sin + (int64_t)cur.b * (kD / 2)) + t;
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const uint32_t c0 = __ldg(cb + kk * 8), c1 = __ldg(cb + kk * 8 + 4);
+                    const uint32_t s0 = __ldg(sb + kk * 8), s1 = __ldg(sb + kk * 8 + 4);
+                    rope_rotate2(qf[kk][0], qf[kk + 4][0], c0, s0);
+                    rope_rotate2(qf[kk][2], qf[kk + 4][2], c1, s1);
+                    if (HI) {
+                        rope_rotate2(qf[kk][1], qf[kk + 4][1], c0, s0);
+                        rope_rotate2(qf[kk][3], qf[kk + 4][3], c1, s1);
+                    }
+                }
+            }
         }
 
         // Fused append: the unit that holds the block of token len-1 also stores that token's new
@@ -540,6 +562,24 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
         if (has_new) {
             const __half *src = (lane < 16 ? p.k_new : p.v_new) + ((int64_t)cur.b * Hkv + cur.h) * kD + (lane & 15) * 8;
             new_row = __ldg(reinterpret_cast<const uint4 *>(src));
+        }
+        if (p.rope_cos != nullptr) {  // warp-uniform; has_new is uniform too
+            if (has_new) {
+                // K row: piece c (lanes 0-7) pairs with piece c+8 (lanes 8-15); V lanes only take part in the shuffles
+                uint4 other;
+                other.x = __shfl_xor_sync(0xffffffffu, new_row.x, 8);
+                other.y = __shfl_xor_sync(0xffffffffu, new_row.y, 8);
+                other.z = __shfl_xor_sync(0xffffffffu, new_row.z, 8);
+                other.w = __shfl_xor_sync(0xffffffffu, new_row.w, 8);
+                if (lane < 16) {
+                    const int64_t off = (int64_t)cur.b * (kD / 2) + (lane & 7) * 8;
+                    const uint4 c = __ldg(reinterpret_cast<const uint4 *>(p.rope_cos + off));
+                    const uint4 sn = __ldg(reinterpret_cast<const uint4 *>(p.rope_sin + off));
+                    uint4 lo = lane < 8 ? new_row : other, hi = lane < 8 ? other : new_row;
+                    rope_rotate8(lo, hi, c, sn);
+                    new_row = lane < 8 ? lo : hi;
+                }
+            }
         }
 
         // The next unit is claimed late (kClaimAhead tiles before this one ends, or now if it is
@@ -920,7 +960,8 @@ static int attention_decode_impl(int device, void *stream, const void *q, void *
                                  const int32_t *block_table,
                                  int64_t table_stride, const int32_t *seq_ids, const int32_t *seq_lens, int batch,
                                  int num_q_heads, int cur_layer, float softmax_scale,
-                                 int max_blocks_per_seq_in_batch, void *workspace, size_t workspace_bytes) {
+                                 int max_blocks_per_seq_in_batch, void *workspace, size_t workspace_bytes,
+                                 const void *rope_cos = nullptr, const void *rope_sin = nullptr) {
     PoolView pv;
     int st = validate_pool(pool, &pv);
     if (st) return st;
@@ -937,6 +978,15 @@ static int attention_decode_impl(int device, void *stream, const void *q, void *
     const float scale_log2 = softmax_scale * kLog2e;
 
     if ((k_new == nullptr) != (v_new == nullptr)) return MKV_ERR_NULL;
+    if ((rope_cos == nullptr) != (rope_sin == nullptr)) return MKV_ERR_NULL;
+    if (rope_cos && (!k_new || (((uintptr_t)k_new | (uintptr_t)v_new | (uintptr_t)rope_cos | (uintptr_t)rope_sin) % 16) != 0 ||
+                     !fast_path_ok(pv, num_q_heads, q, o))) {
+        // no fused rotation for this shape / alignment: rotate q and k_new in place with the stand-alone kernel
+        int rc = mkv_rotary_embedding(device, stream, const_cast<void *>(q), const_cast<void *>(k_new), rope_cos,
+                                      rope_sin, batch, num_q_heads, pv.num_kv_heads, pv.head_dim, pv.elem_bytes);
+        if (rc) return rc;
+        rope_cos = rope_sin = nullptr;
+    }
     if (k_new && (((uintptr_t)k_new | (uintptr_t)v_new) % 16 != 0 || !fast_path_ok(pv, num_q_heads, q, o))) {
         // no fused path for this shape / alignment: append with the copy kernel, then attend
         int rc = mkv_store_kv_decode(device, stream, k_new, v_new, pool, block_table, table_stride, seq_ids, seq_lens,
@@ -986,6 +1036,8 @@ static int attention_decode_impl(int device, void *stream, const void *q, void *
     }
     p.k_new = (const __half *)k_new;
     p.v_new = (const __half *)v_new;
+    p.rope_cos = (const __half *)rope_cos;
+    p.rope_sin = (const __half *)rope_sin;
     p.block_table = block_table;
     p.table_stride = table_stride;
     p.seq_ids = seq_ids;
@@ -1025,6 +1077,18 @@ int mkv_paged_attention_decode_append(int device, void *stream, const void *q, v
     return attention_decode_impl(device, stream, q, o, nullptr, k_new, v_new, pool, block_table, table_stride, seq_ids,
                                  seq_lens, batch, num_q_heads, cur_layer, softmax_scale,
                                  max_blocks_per_seq_in_batch, workspace, workspace_bytes);
+}
+
+int mkv_paged_attention_decode_rope_append(int device, void *stream, void *q, void *o, void *k_new, const void *v_new,
+                                           const void *rope_cos, const void *rope_sin, const mkv_pool *pool,
+                                           const int32_t *block_table, int64_t table_stride, const int32_t *seq_ids,
+                                           const int32_t *seq_lens, int batch, int num_q_heads, int cur_layer,
+                                           float softmax_scale, int max_blocks_per_seq_in_batch, void *workspace,
+                                           size_t workspace_bytes) {
+    if (batch > 0 && (!k_new || !v_new || !rope_cos || !rope_sin)) return MKV_ERR_NULL;
+    return attention_decode_impl(device, stream, q, o, nullptr, k_new, v_new, pool, block_table, table_stride, seq_ids,
+                                 seq_lens, batch, num_q_heads, cur_layer, softmax_scale,
+                                 max_blocks_per_seq_in_batch, workspace, workspace_bytes, rope_cos, rope_sin);
 }
 
 int mkv_paged_attention_decode_push(int device, void *stream, const void *q, void *const *out_ptrs, int n_out,
@@ -1178,6 +1242,8 @@ int mkv_paged_attention_decode_noalloc(int device, void *stream, const void *q, 
     p.out_col_off = 0;
     p.k_new = nullptr;
     p.v_new = nullptr;
+    p.rope_cos = nullptr;
+    p.rope_sin = nullptr;
     p.block_table = block_table;
     p.table_stride = table_stride;
     p.seq_ids = seq_ids;

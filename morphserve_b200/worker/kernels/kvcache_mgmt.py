@@ -32,6 +32,11 @@ def flush_pending_append(infer_state, pool, block_table, dev, stream) -> None:
     pending = state.pop("_mkv_pending_append", None) if state is not None else None
     if pending is None:
         return
+    rope = state.pop("_mkv_pending_rope", None)
+    if rope is not None:    # rows must be rotated before they reach the pool
+        check(lib.mkv_rotary_embedding(dev, stream, rope[0].data_ptr(), rope[1].data_ptr(), rope[2].data_ptr(),
+                                       rope[3].data_ptr(), rope[0].shape[0], rope[0].shape[1], rope[1].shape[1],
+                                       rope[1].shape[2], rope[0].element_size()), "mkv_rotary_embedding")
     layer, k_dec, v_dec = pending
     n_pre = infer_state.num_prefill_seqs
     check(lib.mkv_store_kv_decode(
@@ -82,6 +87,9 @@ def store_kvcache(
             flush_pending_append(infer_state, pool, block_table, dev, stream)
             state["_mkv_pending_append"] = (cur_layer, k_dec, v_dec)
             return
+        if state is not None and state.get("_mkv_pending_rope") is not None:
+            from .rotary_emb import flush_pending_rope      # no fused append for this call: rotate now
+            flush_pending_rope(infer_state, dev, stream)
         seq_ids = infer_state.seq_ids[n_pre:]
         check(lib.mkv_store_kv_decode(
             dev, stream, k_dec.data_ptr(), v_dec.data_ptr(), pool, block_table.data_ptr(), stride,

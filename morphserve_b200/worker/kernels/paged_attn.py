@@ -74,6 +74,21 @@ def paged_attention(
     _plan_for(infer_state, ws, dev, stream, lens, seq_ids, batch, hq, hkv, d, bs, max_blocks)
     state = getattr(infer_state, "__dict__", None)
     pending = state.get("_mkv_pending_append") if state is not None else None
+    rope = state.get("_mkv_pending_rope") if state is not None else None
+    if rope is not None and not (pending is not None and pending[0] == cur_layer
+                                 and rope[0].data_ptr() == q.data_ptr() and rope[1].data_ptr() == pending[1].data_ptr()):
+        from .rotary_emb import flush_pending_rope      # not this call's rows: rotate them in place now
+        flush_pending_rope(infer_state, dev, stream)
+        rope = None
+    if rope is not None:
+        # rotary_embedding_inplace and store_kvcache both left this layer's decode rows to this kernel
+        del state["_mkv_pending_rope"], state["_mkv_pending_append"]
+        check(lib.mkv_paged_attention_decode_rope_append(
+            dev, stream, q.data_ptr(), o.data_ptr(), pending[1].data_ptr(), pending[2].data_ptr(),
+            rope[2].data_ptr(), rope[3].data_ptr(), pool, block_table.data_ptr(), block_table.stride(0),
+            seq_ids.data_ptr(), lens.data_ptr(), batch, hq, cur_layer, float(infer_state.softmax_scale), max_blocks,
+            ws.tensor.data_ptr(), ws.nbytes), "mkv_paged_attention_decode_rope_append")
+        return
     if pending is not None and pending[0] == cur_layer:
         # store_kvcache left this layer's new rows to be appended inside the attention kernel
         del state["_mkv_pending_append"]

@@ -23,6 +23,25 @@ LOG2E = 1.442695040888963  # worker/kernels/paged_attn.py:837
 
 
 # --------------------------------------------------------------------------
+# rotary embedding (the step before the append: worker/layers/transformer_layer.py:93-98)
+# --------------------------------------------------------------------------
+def rotary_embedding(q: np.ndarray, k: np.ndarray, cos: np.ndarray, sin: np.ndarray):
+    """worker/kernels/rotary_emb.py:7-41: halves [0, D/2) and [D/2, D) of every head rotate as
+    (x0*cos - x1*sin, x0*sin + x1*cos) with the token's cos/sin row.  All operands are fp16 in the
+    reference (tables: worker/model.py:240-241), so every product and every sum rounds to fp16;
+    numpy's fp16 arithmetic rounds the same way.  Returns new arrays (the reference writes in place)."""
+    h = q.shape[-1] // 2
+    c = cos[:, None, :].astype(q.dtype)
+    s = sin[:, None, :].astype(q.dtype)
+
+    def rot(x):
+        x0, x1 = x[..., :h], x[..., h:]
+        return np.concatenate([x0 * c - x1 * s, x0 * s + x1 * c], axis=-1).astype(x.dtype)
+
+    return rot(q), rot(k)
+
+
+# --------------------------------------------------------------------------
 # addressing
 # --------------------------------------------------------------------------
 def locate_block(block_id: int, num_blocks_org: int, chunk_blocks: int) -> Tuple[int, int]:

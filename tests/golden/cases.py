@@ -140,6 +140,33 @@ PREFILL_CASES = {
 }
 
 
+def rope_tables(positions, D: int, theta: float = 10000.0, scaling: float = 1.0):
+    """cos/sin rows for the given token positions, built like the reference's table
+    (worker/model.py:229-241): fp32 angles, rounded to fp16."""
+    inv_freq = (1.0 / (np.float32(theta) ** (np.arange(0, D, 2, dtype=np.float32) / np.float32(D)))).astype(np.float32)
+    t = (np.asarray(positions, dtype=np.float32) / np.float32(scaling)).astype(np.float32)
+    freqs = np.outer(t, inv_freq).astype(np.float32)
+    return np.cos(freqs).astype(np.float16), np.sin(freqs).astype(np.float16)
+
+
+def build_rope_case(seed: int, T: int, Hq: int, Hkv: int, D: int, max_pos: int = 4096, dtype=np.float16):
+    """Draw order: positions -> q -> k."""
+    rs = np.random.RandomState(seed)
+    pos = rs.randint(0, max_pos, size=T)
+    q = rs.standard_normal((T, Hq, D)).astype(dtype)
+    k = rs.standard_normal((T, Hkv, D)).astype(dtype)
+    cos, sin = rope_tables(pos, D)
+    return dict(q=q, k=k, cos=cos, sin=sin, positions=pos.astype(np.int32), T=T, Hq=Hq, Hkv=Hkv, D=D)
+
+
+ROPE_CASES = {
+    "gqa4_fp16": dict(seed=6000, T=9, Hq=8, Hkv=2, D=128),
+    "mha_fp16": dict(seed=6001, T=5, Hq=4, Hkv=4, D=128),
+    "gqa8_d64_fp16": dict(seed=6002, T=3, Hq=8, Hkv=1, D=64),
+    "mha_fp32": dict(seed=6003, T=4, Hq=4, Hkv=4, D=128, dtype=np.float32),
+}
+
+
 def block_manager_trace(seed: int = 5000, num_blocks: int = 64, max_seqs: int = 12,
                         max_blocks_per_seq: int = 16, block_size: int = 16, steps: int = 40):
     """A seeded sequence of BlockManager operations: list of (op, seq_ids, lens)."""

@@ -168,6 +168,17 @@ def run_block_manager_trace():
     print("block manager trace:", len(tr["ops"]), "ops ok")
 
 
+def run_rope_case(name, kw):
+    from swiftllm.worker.kernels.rotary_emb import rotary_embedding_inplace
+    c = cases.build_rope_case(**kw)
+    q, k = to_t(c["q"]).clone(), to_t(c["k"]).clone()
+    st = Cfg(position_cos=to_t(c["cos"]), position_sin=to_t(c["sin"]))
+    rotary_embedding_inplace(q, k, st)
+    np.savez_compressed(os.path.join(HERE, f"rope_{name}.npz"), q=q.numpy(), k=k.numpy(),
+                        inputs_sha256=np.array(cases.sha256_of(c["q"], c["k"], c["cos"], c["sin"])))
+    print("rope", name, "ok")
+
+
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MORPHSERVE_REFERENCE", "")
     if not os.path.isdir(os.path.join(ref_root, "MorphServe")):
@@ -180,6 +191,9 @@ def main():
     for name, kw in cases.PREFILL_CASES.items():
         if not only or name in only:
             run_prefill_case(name, kw)
+    for name, kw in cases.ROPE_CASES.items():
+        if not only or "rope" in only:
+            run_rope_case(name, kw)
     if not only or "block_manager" in only:
         run_block_manager_trace()
 

@@ -95,3 +95,34 @@ def test_seq_block_size_heuristic_examples():
     assert O.seq_block_size_heuristic(32, [100, 200])[0] == 64
     assert O.seq_block_size_heuristic(8, [1536] * 256) == (512, 3)
     assert O.seq_block_size_heuristic(8, [1536] * 16) == (128, 12)
+
+
+@pytest.mark.parametrize("name", list(cases.ROPE_CASES))
+def test_rotary_embedding_matches_reference(name):
+    """worker/kernels/rotary_emb.py run in the interpreter vs the oracle: bit-exact (fp16 and fp32 rows)."""
+    c = cases.build_rope_case(**cases.ROPE_CASES[name])
+    gold = np.load(os.path.join(G, f"rope_{name}.npz"))
+    assert str(gold["inputs_sha256"]) == cases.sha256_of(c["q"], c["k"], c["cos"], c["sin"])
+    q, k = O.rotary_embedding(c["q"], c["k"], c["cos"], c["sin"])
+    assert q.dtype == c["q"].dtype and q.tobytes() == gold["q"].tobytes()
+    assert k.tobytes() == gold["k"].tobytes()
+
+
+def test_rotary_embedding_properties():
+    """Position 0 is the identity (cos 1, sin 0); a rotation keeps the norm of every (x0, x1) pair up to fp16
+    rounding; rotating by p and then by -p returns the input up to rounding."""
+    rs = np.random.RandomState(7)
+    q = rs.standard_normal((6, 4, 128)).astype(np.float16)
+    k = rs.standard_normal((6, 2, 128)).astype(np.float16)
+    cos0, sin0 = cases.rope_tables(np.zeros(6), 128)
+    q0, k0 = O.rotary_embedding(q, k, cos0, sin0)
+    assert q0.tobytes() == q.tobytes() and k0.tobytes() == k.tobytes()
+    pos = rs.randint(1, 5000, size=6)
+    cos, sin = cases.rope_tables(pos, 128)
+    q1, k1 = O.rotary_embedding(q, k, cos, sin)
+    n_in = np.hypot(q[..., :64].astype(np.float64), q[..., 64:].astype(np.float64))
+    n_out = np.hypot(q1[..., :64].astype(np.float64), q1[..., 64:].astype(np.float64))
+    np.testing.assert_allclose(n_out, n_in, rtol=0, atol=6e-3)
+    q2, k2 = O.rotary_embedding(q1, k1, cos, (-sin).astype(np.float16))
+    np.testing.assert_allclose(q2.astype(np.float64), q.astype(np.float64), rtol=0, atol=1e-2)
+    np.testing.assert_allclose(k2.astype(np.float64), k.astype(np.float64), rtol=0, atol=1e-2)
