@@ -72,6 +72,8 @@ WORKLOADS = {
     # the default workload with the rotary embedding of q and k in front of every layer's append (the step before the
     # path in the reference's layer code); fused into the attention launch unless --no-fused-rope
     "llama3-8b-gqa-decode-rope": dict(cfg=3, B=256, Hq=32, Hkv=8, L=32, max_len=1536, free_frac=0.10, rope=True),
+    # 8 sequences of up to 2k tokens, 32 layers: launches of ~10 us, where issuing the step costs more than running it
+    "small-batch-gqa-decode": dict(cfg=12, B=8, Hq=32, Hkv=8, L=32, max_len=2048, free_frac=0.10, rope=True),
     # 8 long sequences (8k-32k tokens), 2 layers: fewer (sequence, head) pairs than worker warps
     "longctx-gqa-decode": dict(cfg=11, B=8, Hq=32, Hkv=8, L=2, min_len=8192, max_len=32768, free_frac=0.10),
 }
@@ -219,9 +221,9 @@ class DecodeJob:
                     # gathered outputs, [rank, sequence, local heads * D]: the consumer reads the permuted view
                     self.o_full = torch.empty((L, n, B, Hq * D), dtype=torch.float16, device=device)
 
-    def infer_state(self, seq_ids, lens_dev):
+    def infer_state(self, seq_ids, lens_dev, max_len=None):
         B, Hkv = self.w["B"], self.w["Hkv"]
-        max_len = int(self.lens_host.max())
+        max_len = max_len or int(self.lens_host.max())
         sbs, nsb = self.mk.infer_state.seq_block_size_heuristic(Hkv, self.lens_host.tolist())
         cos = sin = self._z
         if self.cos_table is not None:      # rows of the newest token's position, gathered once per step
@@ -260,6 +262,37 @@ class DecodeJob:
         st = self.infer_state(self.seq_ids, self.lens_dev)      # host work first: the allocate below synchronises
         self.bm.allocate_blocks_for_seqs(self.seq_ids, self.lens_dev)
         self.layers(st, self.q, self.kn, self.vn, self.o)
+
+    def capture_step(self, max_steps):
+        """Capture one resident decode step in a CUDA graph: lengths + 1, the sync-free allocate, the plan and
+        all layers.  Everything the step reads lives at fixed device addresses, so a replay IS the next step.
+        `max_steps` bounds how far the contexts may grow (it sizes the plan's table window)."""
+        from morphserve_b200.worker.kernels._common import attn_workspace
+        w = self.w
+        self.bm.prepare_nosync(w["B"])
+        self.graph_max_len = min(int(self.lens_host.max()) + max_steps, self.bm.block_table.shape[1] * BS)
+        dev = self.dev.index or 0
+        max_blocks = min((self.graph_max_len + BS - 1) // BS, self.bm.block_table.shape[1])
+        ws = attn_workspace(dev, w["B"], w["Hq"], w["Hkv"], D, max_blocks)   # allocated before the capture
+        self.graph_ws_ptr = ws.tensor.data_ptr()
+        torch.cuda.synchronize()
+        from morphserve_b200 import _lib
+        calls0 = sum(_lib.CALLS.values())
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):   # other threads (NCCL) stay free
+            self.lens_dev += 1
+            st = self.infer_state(self.seq_ids, self.lens_dev, max_len=self.graph_max_len)
+            self.bm.allocate_blocks_for_seqs_nosync(self.seq_ids, self.lens_dev)
+            self.layers(st, self.q, self.kn, self.vn, self.o)
+        self.graph_launches = sum(_lib.CALLS.values()) - calls0      # library kernels per replay
+        assert attn_workspace(dev, w["B"], w["Hq"], w["Hkv"], D, max_blocks).tensor.data_ptr() == self.graph_ws_ptr
+
+    def step_graph(self):
+        """One decode step = one replay of the captured graph."""
+        self.lens_host += 1
+        assert int(self.lens_host.max()) <= self.graph_max_len, "captured step outgrown: capture again"
+        self.graph.replay()
+        self.bm.nosync_replayed()
 
     def make_host_buffers(self):
         self.hq = self.q.cpu().pin_memory()
@@ -615,6 +648,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-cuda-graph", action="store_true",
+                    help="resident leg: launch every call of the step from Python instead of capturing the step "
+                         "(sync-free allocate + plan + all layers) in a CUDA graph once and replaying it")
     ap.add_argument("--no-fused-rope", action="store_true",
                     help="workloads with rotary embedding: run it as its own launch per layer")
     ap.add_argument("--no-fused-append", action="store_true",
@@ -716,8 +752,16 @@ def main():
     job = DecodeJob(w, rank, growth_tokens=2 * (K + W) + 16, device=device)
 
     # ---- leg 1: inputs resident in HBM ----------------------------------------
+    step = job.step_resident
+    use_graph = not args.no_cuda_graph and not base.get("head_shard")   # the captured step has no collective in it
+    config["step_launch"] = "python calls"
+    if use_graph:
+        job.step_resident()                       # sizes the workspace, loads the kernels
+        job.capture_step(max_steps=K + max(W, 3) + 4)
+        step = job.step_graph
+        config["step_launch"] = "cuda graph replay"
     for _ in range(max(W, 3)):
-        job.step_resident()
+        step()
     barrier()
     calls0 = dict(_lib.CALLS)
     kv_bytes = 0
@@ -725,12 +769,14 @@ def main():
     with ClockSampler(list(range(world)) if rank == 0 else []) as clocks:
         e0.record()
         for _ in range(K):
-            job.step_resident()
+            step()
             kv_bytes += job.kv_bytes_per_layer() * w["L"]
         e1.record()
         barrier()
     ms = e0.elapsed_time(e1)
     launches = sum(v - calls0.get(k, 0) for k, v in _lib.CALLS.items())
+    if use_graph:
+        launches += K * job.graph_launches          # replays launch the captured kernels without library calls
     ms_max = max_over_ranks(ms, dist, device)
     value = w["tokens_per_step"] * K / (ms_max * 1e-3)
 
@@ -742,8 +788,18 @@ def main():
         mk.paged_attention(job.q[layer], job.k_cache, job.v_cache, [], [], bt, mc, ec, st, layer, job.o[layer])
     torch.cuda.synchronize()
     a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if use_graph:       # the L launches back to back as one graph, so that no launch waits for Python
+        attn_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(attn_graph, capture_error_mode="thread_local"):
+            for layer in range(w["L"]):
+                mk.paged_attention(job.q[layer], job.k_cache, job.v_cache, [], [], bt, mc, ec, st, layer, job.o[layer])
+        attn_graph.replay()
+        torch.cuda.synchronize()
     a0.record()
     for _ in range(reps):
+        if use_graph:
+            attn_graph.replay()
+            continue
         for layer in range(w["L"]):
             mk.paged_attention(job.q[layer], job.k_cache, job.v_cache, [], [], bt, mc, ec, st, layer, job.o[layer])
     a1.record()

@@ -264,6 +264,25 @@ int mkv_block_need(int device, void *stream, const int32_t *num_allocated, const
                    int32_t *need /* device [batch] */, int64_t *totals /* device [2] */);
 
 /*
+ * BlockManager.allocate_blocks_for_seqs (worker/block_manager.py:87-112) in one launch and without
+ * the reference's host round trips (:95, :100): need as in mkv_block_need, the first sum(need) free
+ * ids in ascending order as in mkv_bitmap_select (= torch.nonzero(is_block_free)[:n], :75), rows and
+ * counts as in mkv_block_table_set.  All or nothing: when the request cannot be served the tables
+ * stay as they are.  `status` (device, int64[4], zeroed by the caller once, then accumulated):
+ *   [0] blocks allocated so far, [1] sequences that owned more blocks than their target (the
+ *   reference's assertion, :95-98), [2] blocks that were missing (its RuntimeError, :69-70),
+ *   [3] sequences whose table row would overflow (or a request larger than ids_capacity).
+ * `need` [batch] and `ids` [ids_capacity] are caller-provided scratch; after the call they hold the
+ * per-sequence need and the new ids in batch order.  Contains no synchronisation and no
+ * allocation, so a whole decode step can be enqueued (or captured in a CUDA graph) ahead of time;
+ * the host reads `status` whenever it next needs the free-block count.
+ */
+int mkv_block_allocate(int device, void *stream, int32_t *num_allocated, int32_t *block_table, int64_t table_stride,
+                       const int32_t *seq_ids, const int32_t *target_lens, int batch, int block_size,
+                       uint8_t *bitmap /* is_block_free */, int64_t num_blocks, int32_t *need, int64_t *ids,
+                       int64_t ids_capacity, int64_t *status);
+
+/*
  * Ascending ids i in [lo, hi) with bitmap[i] == want, at most max_out of them,
  * written to out_ids; *out_count = min(matches, max_out) and *out_total = all
  * matches in the range.  If flip != 0 the selected entries are set to !want.

@@ -115,6 +115,98 @@ __global__ void __launch_bounds__(kThreads) bitmap_select_kernel(uint8_t *__rest
     }
 }
 
+// allocate_blocks_for_seqs (worker/block_manager.py:87-112) as ONE launch with no host round trip:
+// need per sequence -> first-fit ascending selection of sum(need) free ids (the order of
+// torch.nonzero(is_block_free)[:n], :75) -> rows and counts updated in batch order.  Nothing is changed
+// unless the whole request can be served.  status[0] += blocks allocated; status[1..3] are sticky error
+// counts (sequences that own more blocks than they need; blocks missing; sequences whose row is full).
+__global__ void __launch_bounds__(kThreads) block_allocate_kernel(
+    int32_t *__restrict__ num_allocated, int32_t *__restrict__ block_table, int64_t table_stride,
+    const int32_t *__restrict__ seq_ids, const int32_t *__restrict__ target_lens, int batch, int block_size,
+    uint8_t *__restrict__ bitmap, int64_t num_blocks, int32_t *__restrict__ need, int64_t *__restrict__ ids,
+    int64_t ids_capacity, int64_t *__restrict__ status) {
+    __shared__ int warp_sums[33];
+    __shared__ long long s_sum;
+    __shared__ int s_neg, s_full;
+    if (threadIdx.x == 0) {
+        s_sum = 0;
+        s_neg = 0;
+        s_full = 0;
+    }
+    __syncthreads();
+    long long sum = 0;
+    int neg = 0, full = 0;
+    for (int i = threadIdx.x; i < batch; i += blockDim.x) {
+        const int have = num_allocated[seq_ids[i]];
+        const int n = (target_lens[i] + (block_size - 1)) / block_size - have;
+        need[i] = n;
+        sum += n;
+        neg += (n < 0);
+        full += ((int64_t)have + n > table_stride);
+    }
+    for (int d = 16; d > 0; d >>= 1) {
+        sum += __shfl_down_sync(0xffffffffu, sum, d);
+        neg += __shfl_down_sync(0xffffffffu, neg, d);
+        full += __shfl_down_sync(0xffffffffu, full, d);
+    }
+    if ((threadIdx.x & 31) == 0) {
+        atomicAdd((unsigned long long *)&s_sum, (unsigned long long)sum);
+        atomicAdd(&s_neg, neg);
+        atomicAdd(&s_full, full);
+    }
+    __syncthreads();
+    const int64_t total = s_sum;
+    if (s_neg > 0 || s_full > 0 || total > ids_capacity) {
+        if (threadIdx.x == 0) {
+            status[1] += s_neg;
+            status[3] += s_full + (total > ids_capacity);
+        }
+        return;
+    }
+    if (total <= 0) return;
+
+    // first `total` free ids, ascending; the bitmap is not touched yet
+    int64_t carry = 0;
+    for (int64_t base = 0; base < num_blocks && carry < total; base += (int64_t)kThreads * kPerThread) {
+        const int64_t i0 = base + (int64_t)threadIdx.x * kPerThread;
+        unsigned mask = 0;
+#pragma unroll
+        for (int j = 0; j < kPerThread; ++j)
+            if (i0 + j < num_blocks && bitmap[i0 + j] != 0) mask |= 1u << j;
+        int found;
+        const int off = block_exclusive_scan(__popc(mask), found, warp_sums);
+        int64_t pos = carry + off;
+        while (mask) {
+            const int j = __ffs(mask) - 1;
+            mask &= mask - 1;
+            if (pos < total) ids[pos] = i0 + j;
+            ++pos;
+        }
+        carry += found;
+    }
+    if (carry < total) {
+        if (threadIdx.x == 0) status[2] += total - carry;
+        return;
+    }
+    __syncthreads();  // ids[] written by the whole block are visible to it
+    for (int64_t i = threadIdx.x; i < total; i += blockDim.x) bitmap[ids[i]] = 0;
+    int64_t taken = 0;
+    for (int base = 0; base < batch; base += kThreads) {
+        const int i = base + threadIdx.x;
+        const int n = (i < batch) ? need[i] : 0;
+        int chunk_total;
+        const int off = block_exclusive_scan(n, chunk_total, warp_sums);
+        if (i < batch && n > 0) {
+            const int64_t s = seq_ids[i];
+            const int have = num_allocated[s];
+            for (int j = 0; j < n; ++j) block_table[s * table_stride + have + j] = (int32_t)ids[taken + off + j];
+            num_allocated[s] = have + n;
+        }
+        taken += chunk_total;
+    }
+    if (threadIdx.x == 0) status[0] += total;
+}
+
 __global__ void bitmap_scatter_kernel(uint8_t *__restrict__ bitmap, int64_t bitmap_len,
                                       const int64_t *__restrict__ ids, int64_t n, int value) {
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
@@ -211,6 +303,24 @@ int mkv_block_need(int device, void *stream, const int32_t *num_allocated, const
     if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
     block_need_kernel<<<1, kThreads, 0, (cudaStream_t)stream>>>(num_allocated, seq_ids, target_lens, batch,
                                                                block_size, need, totals);
+    MKV_LAUNCH_CHECK();
+    return MKV_OK;
+}
+
+int mkv_block_allocate(int device, void *stream, int32_t *num_allocated, int32_t *block_table, int64_t table_stride,
+                       const int32_t *seq_ids, const int32_t *target_lens, int batch, int block_size,
+                       uint8_t *bitmap, int64_t num_blocks, int32_t *need, int64_t *ids, int64_t ids_capacity,
+                       int64_t *status) {
+    if (batch < 0 || block_size < 1 || table_stride < 1 || num_blocks < 0 || ids_capacity < 0) return MKV_ERR_SHAPE;
+    if (!status) return MKV_ERR_NULL;
+    if (batch == 0) return MKV_OK;
+    if (!num_allocated || !block_table || !seq_ids || !target_lens || !need) return MKV_ERR_NULL;
+    if ((num_blocks > 0 && !bitmap) || (ids_capacity > 0 && !ids)) return MKV_ERR_NULL;
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
+    block_allocate_kernel<<<1, kThreads, 0, (cudaStream_t)stream>>>(num_allocated, block_table, table_stride, seq_ids,
+                                                                   target_lens, batch, block_size, bitmap, num_blocks,
+                                                                   need, ids, ids_capacity, status);
     MKV_LAUNCH_CHECK();
     return MKV_OK;
 }

@@ -9,6 +9,11 @@ Allocation is first-fit in ascending block id like the reference's
 ``torch.nonzero(is_block_free)[:n]`` (:75), done by one CUDA kernel without the
 nonzero pass; an allocate costs one host synchronisation (the size of the
 returned tensor is data dependent) instead of the reference's three.
+
+``allocate_blocks_for_seqs_nosync`` is the same allocation as one launch with
+no host round trip at all (nothing is returned; errors and the free-block
+count reach the host the next time ``num_free_blocks`` is read), so that a
+whole decode step can be enqueued ahead of the GPU or captured in a CUDA graph.
 """
 from __future__ import annotations
 
@@ -52,6 +57,10 @@ class BlockManager:
         if not torch.cuda.is_available():
             raise RuntimeError("BlockManager keeps its tables on the GPU; no CUDA device is available")
         self.device_name = device_name
+        self._nosync_pending = False
+        self._alloc_status = None       # device int64[4], see mkv_block_allocate
+        self._alloc_seen = [0, 0, 0, 0]
+        self._alloc_need = self._alloc_ids = None
         self.num_free_blocks = BlockCount(num_blocks)
         self.num_blocks = num_blocks
         self.block_size = block_size
@@ -66,6 +75,70 @@ class BlockManager:
                                       dtype=torch.int32, device="cuda")
         # block_id |-> free?
         self.is_block_free = torch.ones((num_blocks,), dtype=torch.bool, device="cuda")
+
+    # ``num_free_blocks`` stays an attribute that outside code reads and assigns (the elastic resize does
+    # ``+= n`` / ``-= n``); reading it first folds in what sync-free allocations did on the GPU.
+    @property
+    def num_free_blocks(self):
+        if self._nosync_pending:
+            self.sync_counters()
+        return self._num_free_blocks
+
+    @num_free_blocks.setter
+    def num_free_blocks(self, value):
+        if self._nosync_pending:
+            self.sync_counters()
+        self._num_free_blocks = value if isinstance(value, BlockCount) else BlockCount(int(value))
+
+    def allocate_blocks_for_seqs_nosync(self, seq_ids: torch.Tensor, target_lens: torch.Tensor) -> None:
+        """``allocate_blocks_for_seqs`` without its return value and without any host synchronisation: one
+        kernel computes the need, takes the first free ids in ascending order and extends the rows, or changes
+        nothing if the pool is too small.  ``seq_ids`` / ``target_lens`` must be int32 CUDA tensors.  Errors
+        (the reference's AssertionError / RuntimeError) are raised by the next ``sync_counters()``, which every
+        read of ``num_free_blocks`` implies."""
+        assert seq_ids.dtype == torch.int32 and target_lens.dtype == torch.int32
+        assert seq_ids.is_contiguous() and target_lens.is_contiguous()
+        self.prepare_nosync(seq_ids.shape[0])
+        dev, stream = device_and_stream(self.block_table)
+        check(lib.mkv_block_allocate(
+            dev, stream, self.num_seq_allocated_blocks.data_ptr(), self.block_table.data_ptr(),
+            self.block_table.stride(0), seq_ids.data_ptr(), target_lens.data_ptr(), seq_ids.shape[0], self.block_size,
+            self.is_block_free.data_ptr(), self.is_block_free.shape[0], self._alloc_need.data_ptr(),
+            self._alloc_ids.data_ptr(), self._alloc_ids.shape[0], self._alloc_status.data_ptr()),
+            "mkv_block_allocate")
+        self._nosync_pending = True
+
+    def prepare_nosync(self, batch: int) -> None:
+        """Scratch of the sync-free allocate (status words, need per sequence, id list).  Called by it; call it
+        yourself before capturing a CUDA graph, since a capture must not allocate from the regular pool."""
+        dev = self.block_table.device
+        if self._alloc_status is None:
+            self._alloc_status = torch.zeros((4,), dtype=torch.int64, device=dev)
+        if self._alloc_need is None or self._alloc_need.shape[0] < batch:
+            self._alloc_need = torch.empty((max(batch, 64),), dtype=torch.int32, device=dev)
+        if self._alloc_ids is None or self._alloc_ids.shape[0] < self.is_block_free.shape[0]:
+            self._alloc_ids = torch.empty((self.is_block_free.shape[0],), dtype=torch.int64, device=dev)
+
+    def nosync_replayed(self) -> None:
+        """Tell the manager that a captured graph containing sync-free allocations was replayed."""
+        self._nosync_pending = True
+
+    def sync_counters(self) -> None:
+        """Fold the device-side record of the sync-free allocations into the host counters (one
+        synchronisation) and raise what the reference would have raised at allocation time."""
+        self._nosync_pending = False
+        if self._alloc_status is None:
+            return
+        st = self._alloc_status.tolist()
+        seen, self._alloc_seen = self._alloc_seen, st
+        self._num_free_blocks = BlockCount(self._num_free_blocks - (st[0] - seen[0]))
+        assert st[1] == seen[1], \
+            f"(On {self.device_name}) Logic error: Some sequences have more blocks already allocated than needed."
+        if st[2] != seen[2]:
+            raise RuntimeError(f"No enough free blocks available on {self.device_name} ({self.num_blocks} in total, "
+                               f"{st[2] - seen[2]} short)")
+        if st[3] != seen[3]:
+            raise RuntimeError(f"(On {self.device_name}) a sequence needs more blocks than a block-table row holds")
 
     def get_num_used_blocks(self) -> int:
         return self.num_blocks - self.num_free_blocks
