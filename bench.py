@@ -72,6 +72,9 @@ WORKLOADS = {
     # the default workload with the rotary embedding of q and k in front of every layer's append (the step before the
     # path in the reference's layer code); fused into the attention launch unless --no-fused-rope
     "llama3-8b-gqa-decode-rope": dict(cfg=3, B=256, Hq=32, Hkv=8, L=32, max_len=1536, free_frac=0.10, rope=True),
+    # layer slab replace (the producer of expand / release events): Llama-3-8B fp16 layer (436 MB) <-> its 4-bit
+    # image (~125 MB), host -> device from pinned memory
+    "layer-replace": dict(cfg=13, replace=True, org_bytes=436 << 20, quant_bytes=125 << 20),
     # 8 sequences of up to 2k tokens, 32 layers: launches of ~10 us, where issuing the step costs more than running it
     "small-batch-gqa-decode": dict(cfg=12, B=8, Hq=32, Hkv=8, L=32, max_len=2048, free_frac=0.10, rope=True),
     # 8 long sequences (8k-32k tokens), 2 layers: fewer (sequence, head) pairs than worker warps
@@ -591,6 +594,35 @@ def prefill_bench(w, K, W, device):
 
 
 # ----------------------------------------------------------------------------
+# layer slab replace
+# ----------------------------------------------------------------------------
+def replace_bench(w, K, W, device):
+    """replace_layer_org2quant / replace_layer_quant2org of one layer: a single host->device copy each."""
+    from morphserve_b200 import swiftllm_c as c
+    slab = torch.zeros(w["org_bytes"], dtype=torch.uint8, device=device)
+    org_host = torch.randint(0, 255, (w["org_bytes"],), dtype=torch.uint8).pin_memory()
+    q_host = torch.randint(0, 255, (w["quant_bytes"],), dtype=torch.uint8).pin_memory()
+    c.register_layer_memory_org_gpu(0, slab.data_ptr(), slab.numel())
+    c.register_layer_memory_org_cpu(0, org_host.data_ptr(), org_host.numel())
+    c.register_layer_memory_quant(0, q_host.data_ptr(), q_host.numel())
+    c.register_layer_memory_tensor_map_org(0, [{"w": dict(offset=0, shape=[w["org_bytes"]], dtype=torch.uint8, size=w["org_bytes"])}])
+    c.register_layer_memory_tensor_map_quant(0, [{"w": dict(offset=0, shape=[w["quant_bytes"]], dtype=torch.uint8, size=w["quant_bytes"])}])
+    out = {}
+    for name, fn, nbytes in (("org2quant", c.replace_layer_org2quant, w["quant_bytes"]),
+                             ("quant2org", c.replace_layer_quant2org, w["org_bytes"])):
+        for _ in range(W):
+            fn(0)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()        # the call returns when the copy is complete (it runs on its own stream)
+        for _ in range(K):
+            fn(0)
+        dt = (time.perf_counter() - t0) / K
+        out[name] = {"bytes": nbytes, "ms": dt * 1e3, "gbs": nbytes / dt / 1e9}
+    assert torch.equal(slab.cpu(), org_host)
+    return out
+
+
+# ----------------------------------------------------------------------------
 # block swap
 # ----------------------------------------------------------------------------
 def swap_bench(w, K, W, device):
@@ -674,6 +706,15 @@ def main():
                               "roofline": {"kernel": "store_kv_prefill_kernel", "bound": "hbm", "achieved": r["gbs"],
                                            "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                                            "frac": r["gbs"] / peak, "traffic": None}, "prefill": r}))
+        return
+    if base.get("replace"):
+        assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+        torch.cuda.set_device(local_rank)
+        if rank == 0:
+            r = replace_bench(base, max(K, 3) if K < 10 else 10, 2, torch.device("cuda", local_rank))
+            print(json.dumps({"metric": "layer_upload_gbs", "value": r["quant2org"]["gbs"], "unit": "GB/s",
+                              "n_gpus": 1, "higher_is_better": True, "dtype": "u8", "data": "synthetic",
+                              "config": {"workload": args.workload}, "replace": r}))
         return
     if base.get("swap"):
         assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"

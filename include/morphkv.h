@@ -385,6 +385,17 @@ int mkv_swap_blocks_pinned(int device, void *stream, const mkv_pool *pool, void 
                            const int64_t *src_ids /* device */, const int64_t *dst_ids /* device */, int64_t n,
                            int is_swap_in);
 
+/*
+ * Copies `bytes` of a layer image from host memory (pinned for full PCIe speed) to the start of
+ * the layer's slab on the GPU and returns when the copy is complete: the data movement of
+ * MemoryManager::replace_layer_org2quant / replace_layer_quant2org
+ * (csrc/src/memory_manager.cpp:179-231, :274-320).  MKV_ERR_NOSPACE if the image is larger than
+ * the slab (the reference's "Layer requires ... bytes" error, :195-200), nothing copied then.
+ * Runs on a copy stream of its own, like the reference; it is not ordered against the caller's
+ * compute streams.
+ */
+int mkv_slab_upload(int device, void *dst_device, size_t dst_capacity, const void *src_host, size_t bytes);
+
 #ifdef __cplusplus
 }
 #endif

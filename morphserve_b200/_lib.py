@@ -62,6 +62,7 @@ SIGNATURES = {
     "mkv_store_kv_decode": (_i, [_i, _vp, _vp, _vp, _pool, _vp, _i64, _vp, _vp, _i, _i]),
     "mkv_store_kv_prefill": (_i, [_i, _vp, _vp, _vp, _pool, _vp, _i64, _vp, _vp, _vp, _i, _i, _i]),
     "mkv_block_need": (_i, [_i, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp]),
+    "mkv_slab_upload": (_i, [_i, _vp, _sz, _vp, _sz]),
     "mkv_block_allocate": (_i, [_i, _vp, _vp, _vp, _i64, _vp, _vp, _i, _i, _vp, _i64, _vp, _vp, _i64, _vp]),
     "mkv_bitmap_select": (_i, [_i, _vp, _vp, _i64, _i64, _i, _i64, _i, _vp, _vp, _vp]),
     "mkv_bitmap_scatter": (_i, [_i, _vp, _vp, _i64, _vp, _i64, _i]),

@@ -161,4 +161,22 @@ int mkv_swap_blocks(int device, void *stream, const mkv_pool *pool, void *k_swap
     return MKV_OK;
 }
 
+// Layer slab upload: the quantised (or the original fp16) image of a transformer layer from host memory
+// into the layer's slab on the GPU, complete on return (csrc/src/memory_manager.cpp:179-231, :274-320).
+// The reference creates and destroys a stream per call; here one non-blocking copy stream per device is
+// kept, so the copy overlaps whatever runs on the compute streams and the call costs no stream set-up.
+int mkv_slab_upload(int device, void *dst_device, size_t dst_capacity, const void *src_host, size_t bytes) {
+    static cudaStream_t copy_streams[64];
+    if (device < 0 || device >= 64) return MKV_ERR_RANGE;
+    if (bytes > dst_capacity) return MKV_ERR_NOSPACE;
+    if (bytes == 0) return MKV_OK;
+    if (!dst_device || !src_host) return MKV_ERR_NULL;
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
+    if (!copy_streams[device]) MKV_CUDA_TRY(cudaStreamCreateWithFlags(&copy_streams[device], cudaStreamNonBlocking));
+    MKV_CUDA_TRY(cudaMemcpyAsync(dst_device, src_host, bytes, cudaMemcpyHostToDevice, copy_streams[device]));
+    MKV_CUDA_TRY(cudaStreamSynchronize(copy_streams[device]));
+    return MKV_OK;
+}
+
 }  // extern "C"

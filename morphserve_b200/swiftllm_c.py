@@ -15,7 +15,7 @@ import torch
 from ._lib import MKV_MAX_SEGMENTS, MkvPool, MorphKVError, check, lib
 from .worker.kernels._common import device_and_stream, make_pool
 
-_state = {"kv_info": None, "org_gpu": {}, "quant": {}}
+_state = {"kv_info": None, "org_gpu": {}, "org_cpu": {}, "quant": {}, "map_quant": {}, "map_org": {}}
 
 
 def _as_list(xs):
@@ -145,6 +145,93 @@ def acquire_new_kvcache(layer_id: int):
     return k, v
 
 
+def register_layer_memory_org_cpu(layer_id: int, start_addr: int, size: int) -> None:
+    """csrc/src/memory_manager.cpp:23-28: the host copy of the fp16 layer."""
+    _state["org_cpu"][int(layer_id)] = (int(start_addr), int(size))
+
+
+def register_layer_memory_tensor_map_quant(layer_id: int, tensor_map) -> None:
+    """csrc/src/memory_manager.cpp:37-45: list of ``{name: {offset, shape, dtype, size}}`` of the quantised layer."""
+    _state["map_quant"][int(layer_id)] = [dict(m) for m in tensor_map]
+
+
+def register_layer_memory_tensor_map_org(layer_id: int, tensor_map) -> None:
+    """csrc/src/memory_manager.cpp:47-55."""
+    _state["map_org"][int(layer_id)] = [dict(m) for m in tensor_map]
+
+
+# torch dtype -> (typestr of an equally wide type the CUDA array interface knows, dtype to view as afterwards)
+_TYPESTR = {torch.float16: ("<f2", None), torch.float32: ("<f4", None), torch.float64: ("<f8", None),
+            torch.int8: ("|i1", None), torch.uint8: ("|u1", None), torch.int16: ("<i2", None),
+            torch.int32: ("<i4", None), torch.int64: ("<i8", None), torch.bool: ("|u1", torch.bool),
+            torch.bfloat16: ("<i2", torch.bfloat16)}
+
+
+def _tensors_in_slab(base_addr: int, tensor_map):
+    """Non-owning tensors at ``base_addr + offset`` for every entry, in list order; inside one entry names
+    come in sorted order like the reference's std::map (csrc/src/memory_manager.cpp:235-268)."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    out = []
+    for entry in tensor_map:
+        for name in sorted(entry):
+            info = entry[name]
+            shape = tuple(int(x) for x in info["shape"])
+            typestr, view_as = _TYPESTR[info["dtype"]]
+            t = torch.as_tensor(_RawCudaMemory(base_addr + int(info["offset"]), shape, typestr), device=dev)
+            out.append(t.view(view_as) if view_as is not None else t)
+    return out
+
+
+def _upload(dst, src, what: str):
+    (dst_addr, dst_size), (src_addr, src_size) = dst, src
+    if src_size > dst_size:     # checked before any CUDA call, like csrc/src/memory_manager.cpp:195-200
+        raise RuntimeError(f"Layer requires {src_size} bytes, but only {dst_size} bytes available")
+    st = lib.mkv_slab_upload(torch.cuda.current_device(), dst_addr, dst_size, src_addr, src_size)
+    if st == -7:
+        raise RuntimeError(f"Layer requires {src_size} bytes, but only {dst_size} bytes available")
+    check(st, what)
+
+
+def replace_layer_org2quant(layer_id: int):
+    """Overwrite the start of layer ``layer_id``'s fp16 slab with its quantised image (host -> device,
+    complete on return) and return the quantised tensors as views into the slab, in registration order.
+    csrc/src/memory_manager.cpp:179-271."""
+    layer_id = int(layer_id)
+    if (layer_id not in _state["org_gpu"] or layer_id not in _state["quant"]
+            or layer_id not in _state["map_quant"]):
+        raise RuntimeError(f"Layer ID {layer_id} not registered in memory map")
+    _upload(_state["org_gpu"][layer_id], _state["quant"][layer_id], "mkv_slab_upload")
+    return _tensors_in_slab(_state["org_gpu"][layer_id][0], _state["map_quant"][layer_id])
+
+
+def replace_layer_quant2org(layer_id: int):
+    """Restore the fp16 layer from its host copy into the slab and return its tensors as views.
+    csrc/src/memory_manager.cpp:274-364.  Elastic KV chunks carved out of the slab must have been
+    released before (server/memory_utils.py:617-662 checks that)."""
+    layer_id = int(layer_id)
+    if (layer_id not in _state["org_gpu"] or layer_id not in _state["org_cpu"]
+            or layer_id not in _state["map_org"]):
+        raise RuntimeError(f"[MemoryManager C++] Layer ID {layer_id} not registered in original memory maps")
+    _upload(_state["org_gpu"][layer_id], _state["org_cpu"][layer_id], "mkv_slab_upload")
+    return _tensors_in_slab(_state["org_gpu"][layer_id][0], _state["map_org"][layer_id])
+
+
+def get_freed_memory_size(layer_id: int, used_size: int) -> int:
+    """csrc/src/memory_manager.cpp:367-374."""
+    if int(layer_id) not in _state["org_gpu"]:
+        return 0
+    return max(_state["org_gpu"][int(layer_id)][1] - int(used_size), 0)
+
+
+def verify_tensor_continuity(tensors) -> bool:
+    """True if the tensors, sorted by address, follow each other without a gap.
+    csrc/src/memory_manager.cpp:376-405."""
+    spans = sorted((t.data_ptr(), t.numel() * t.element_size()) for t in tensors)
+    return all(spans[i - 1][0] + spans[i - 1][1] == spans[i][0] for i in range(1, len(spans)))
+
+
 __all__ = ["swap_blocks", "swap_blocks_new_kv_combined", "register_kv_cache_info",
-           "register_layer_memory_org_gpu", "register_layer_memory_quant", "acquire_new_kvcache",
-           "MorphKVError"]
+           "register_layer_memory_org_gpu", "register_layer_memory_org_cpu", "register_layer_memory_quant",
+           "register_layer_memory_tensor_map_quant", "register_layer_memory_tensor_map_org",
+           "acquire_new_kvcache", "replace_layer_org2quant", "replace_layer_quant2org",
+           "get_freed_memory_size", "verify_tensor_continuity", "MorphKVError"]

@@ -132,3 +132,25 @@ def test_swap_run_coalescing_rule():
     assert O.coalesce_runs([3, 4, 5, 9], [0, 1, 2, 3]) == [(0, 3), (3, 1)]
     assert O.coalesce_runs([10, 11, 12, 13], [0, 1, 2, 3], num_blocks_org=12, chunk_blocks=4) == [(0, 2), (2, 2)]
     assert O.coalesce_runs([14, 15, 16, 17], [0, 1, 2, 3], num_blocks_org=12, chunk_blocks=4) == [(0, 2), (2, 2)]
+
+
+def test_layer_replace_bookkeeping_and_errors_need_no_gpu():
+    """Registration state, the two error messages raised before any copy (csrc/src/memory_manager.cpp:
+    180-186, :195-200, :275-282) and the pure-host helpers of the layer-replace entry points."""
+    import torch
+    from morphserve_b200 import swiftllm_c as c
+    with pytest.raises(RuntimeError, match="not registered in memory map"):
+        c.replace_layer_org2quant(901)
+    with pytest.raises(RuntimeError, match="not registered in original memory maps"):
+        c.replace_layer_quant2org(901)
+    c.register_layer_memory_org_gpu(901, 1 << 20, 100)
+    c.register_layer_memory_quant(901, 1 << 21, 200)
+    c.register_layer_memory_tensor_map_quant(901, [])
+    with pytest.raises(RuntimeError, match="Layer requires 200 bytes, but only 100 bytes available"):
+        c.replace_layer_org2quant(901)
+    assert c.get_freed_memory_size(901, 30) == 70 and c.get_freed_memory_size(901, 300) == 0
+    assert c.get_freed_memory_size(902, 1) == 0
+    x = torch.zeros(16)
+    assert c.verify_tensor_continuity([x[8:], x[:4], x[4:8]])
+    assert not c.verify_tensor_continuity([x[:4], x[8:]])
+    assert c.verify_tensor_continuity([])

@@ -279,3 +279,67 @@ def test_acquire_new_kvcache_carves_the_slab_like_the_reference():
     swiftllm_c.register_layer_memory_org_gpu(6, slab.data_ptr(), org_size)
     with pytest.raises(RuntimeError):
         swiftllm_c.acquire_new_kvcache(6)
+
+
+def test_layer_slab_replace_and_restore_round_trip():
+    """org -> quant -> (elastic chunk in the freed tail) -> org, as server/memory_utils.py:93-367 and :617-662
+    drive it: the slab holds the host images byte for byte, returned tensors are views into the slab with the
+    registered shapes and dtypes, bytes behind the quantised image stay as they were until the chunk is zeroed."""
+    from morphserve_b200 import swiftllm_c as c
+    layer = 700
+    rs = np.random.RandomState(12)
+    # "fp16 layer": three tensors back to back; "quantised layer": int32 / fp16 / int32 / bf16 tensors, smaller
+    org_np = {"a.weight": rs.standard_normal((256, 512)).astype(np.float16),
+              "b.weight": rs.standard_normal((512, 300)).astype(np.float16),
+              "norm.weight": rs.standard_normal((512,)).astype(np.float16)}
+    q_np = {"a.qweight": rs.randint(-2 ** 31, 2 ** 31 - 1, size=(256, 64)).astype(np.int32),
+            "a.scales": rs.standard_normal((4, 512)).astype(np.float16),
+            "a.qzeros": rs.randint(0, 2 ** 31 - 1, size=(4, 64)).astype(np.int32),
+            "norm.weight": rs.standard_normal((512,)).astype(np.float32),
+            "b.lowrank": rs.randint(-2 ** 15, 2 ** 15 - 1, size=(8, 300)).astype(np.int16)}    # stands for bf16 bits
+
+    def pack(d, torch_dtypes):
+        blob, maps, off = [], [], 0
+        for (name, a), dt in zip(d.items(), torch_dtypes):
+            maps.append({name: {"offset": off, "shape": list(a.shape), "dtype": dt, "size": a.nbytes, "is_param": False}})
+            blob.append(a.tobytes())
+            off += a.nbytes
+        return np.frombuffer(b"".join(blob), dtype=np.uint8).copy(), maps
+
+    org_blob, org_map = pack(org_np, [torch.float16] * 3)
+    q_blob, q_map = pack(q_np, [torch.int32, torch.float16, torch.int32, torch.float32, torch.bfloat16])
+    slab = torch.from_numpy(org_blob).cuda()                       # the layer as it sits on the GPU
+    org_host = torch.from_numpy(org_blob).pin_memory()
+    q_host = torch.from_numpy(q_blob).pin_memory()
+    c.register_layer_memory_org_gpu(layer, slab.data_ptr(), slab.numel())
+    c.register_layer_memory_org_cpu(layer, org_host.data_ptr(), org_host.numel())
+    c.register_layer_memory_tensor_map_org(layer, org_map)
+    c.register_layer_memory_quant(layer, q_host.data_ptr(), q_host.numel())
+    c.register_layer_memory_tensor_map_quant(layer, q_map)
+
+    got = c.replace_layer_org2quant(layer)
+    torch.cuda.synchronize()
+    after = slab.cpu().numpy()
+    assert after[: q_blob.size].tobytes() == q_blob.tobytes()
+    assert after[q_blob.size:].tobytes() == org_blob[q_blob.size:].tobytes()      # tail untouched
+    assert len(got) == 5 and got[4].dtype == torch.bfloat16 and got[0].dtype == torch.int32
+    for t, (name, a) in zip(got, q_np.items()):
+        assert tuple(t.shape) == a.shape and t.is_cuda
+        bits = t.view(torch.int16) if t.dtype == torch.bfloat16 else t
+        assert bits.cpu().numpy().tobytes() == a.tobytes(), name
+        assert slab.data_ptr() <= t.data_ptr() < slab.data_ptr() + slab.numel()      # a view, not a copy
+    assert c.verify_tensor_continuity(got)
+    assert c.get_freed_memory_size(layer, q_blob.size) == org_blob.size - q_blob.size
+
+    # the freed tail becomes an elastic KV chunk (csrc/src/memory_manager.cpp:69-176)
+    c.register_kv_cache_info(2, 2, 16, 128)
+    k, v = c.acquire_new_kvcache(layer)
+    assert k.shape[0] >= 1 and k.data_ptr() >= slab.data_ptr() + q_blob.size
+    torch.cuda.synchronize()
+    assert slab.cpu().numpy()[: q_blob.size].tobytes() == q_blob.tobytes()          # zeroing the chunk spared the layer
+
+    back = c.replace_layer_quant2org(layer)
+    torch.cuda.synchronize()
+    assert slab.cpu().numpy().tobytes() == org_blob.tobytes()
+    for t, (name, a) in zip(back, org_np.items()):
+        assert t.dtype == torch.float16 and t.cpu().numpy().tobytes() == a.tobytes(), name
