@@ -304,6 +304,8 @@ class DecodeJob:
         self.ho = torch.empty(self.o.shape, dtype=torch.float16).pin_memory()
         self.dq, self.dk, self.dv = torch.empty_like(self.q), torch.empty_like(self.kn), torch.empty_like(self.vn)
         L = self.w["L"]
+        self.h_meta = torch.empty((2, self.w["B"]), dtype=torch.int32).pin_memory()
+        self.d_meta = torch.empty((2, self.w["B"]), dtype=torch.int32, device=self.dev)
         self.s_in, self.s_out = torch.cuda.Stream(self.dev), torch.cuda.Stream(self.dev)
         self.ev_in = [torch.cuda.Event() for _ in range(L)]
         self.ev_out = [torch.cuda.Event() for _ in range(L)]
@@ -318,8 +320,11 @@ class DecodeJob:
         step ends when the last output byte is on the host."""
         main = torch.cuda.current_stream()
         self.lens_host += 1
-        seq_ids = torch.tensor(self.seq_ids_list, dtype=torch.int32, device=self.dev)
-        lens = torch.tensor(self.lens_host.tolist(), dtype=torch.int32, device=self.dev)
+        # sequence ids and lengths: Python lists -> one pinned staging buffer -> one asynchronous copy
+        self.h_meta[0].copy_(torch.tensor(self.seq_ids_list, dtype=torch.int32))
+        self.h_meta[1].copy_(torch.tensor(self.lens_host.tolist(), dtype=torch.int32))
+        self.d_meta.copy_(self.h_meta, non_blocking=True)
+        seq_ids, lens = self.d_meta[0], self.d_meta[1]
         self.lens_dev = lens
         L = self.w["L"]
 
@@ -331,7 +336,7 @@ class DecodeJob:
                 self.ev_in[layer].record(self.s_in)
 
         copy_in(0)
-        self.bm.allocate_blocks_for_seqs(seq_ids, lens)
+        self.bm.allocate_blocks_for_seqs_nosync(seq_ids, lens)      # no host round trip: the layers queue up behind it
         st = self.infer_state(seq_ids, lens)
         mk, mc, ec, bt = self.mk, self.model_config, self.engine_config, self.bm.block_table
         for layer in range(L):
@@ -349,6 +354,7 @@ class DecodeJob:
                 self.ho[layer].copy_(self.o[layer], non_blocking=True)
         self.s_out.synchronize()
         main.synchronize()
+        _ = self.bm.num_free_blocks     # folds the device-side allocation record into the host counters
 
     def kv_bytes_per_layer(self):
         return 2 * 2 * self.w["Hkv"] * D * int(self.lens_host.sum())

@@ -10,9 +10,12 @@
 //     sorts the (sequence, chunk) items longest first.
 //   decode kernel (once per layer): one persistent thread block per SM; every
 //     WARP is an independent worker that pulls (item, kv head) units from a
-//     global counter, streams the unit's K/V tiles through a private
-//     cp.async ring in shared memory (XOR-swizzled for ldmatrix), and keeps an
-//     fp32 online softmax in base 2.  The next unit is claimed in three
+//     global counter, streams the unit's K/V tiles through a private ring in
+//     shared memory - filled by TMA (cp.async.bulk.tensor, 128-byte swizzle, one
+//     mbarrier per stage; four 2 KiB boxes per tile issued by one lane) or, for
+//     pools of more than 8 segments, by 16-byte cp.async with the same kind of
+//     XOR swizzle - reads it with ldmatrix, and keeps an fp32 online softmax in
+//     base 2.  The next unit is claimed in three
 //     non-blocking steps a few tiles before the current one ends and its first
 //     tiles are fetched into the stages the current unit frees, so the ring
 //     stays full across unit boundaries.  A sequence cut into several chunks
@@ -22,10 +25,13 @@
 //     token's K/V row (fused store_kvcache).
 //   plain kernel: any dtype / head_dim / block size, one warp per (seq, q head).
 //
-// No kernel here waits on another thread block, so nothing can spin forever.
+// No kernel here waits on another thread block; the only wait is a warp's wait for its
+// own bulk copy (mbarrier), which gives up after about a second and reports it.
+#include <cuda.h>  // CUtensorMap and its enums (types only: the encoder is fetched from the driver at run time)
 #include <math.h>
 #include <stdio.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include "common.cuh"
 #include "rope.cuh"
@@ -256,6 +262,47 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
+// ---- TMA (cp.async.bulk.tensor) + mbarrier: the tile loader of the default path
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded: gives up after about a second of GPU clock and reports it, so a copy that never lands cannot hang the GPU.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000000ll)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+// One box of the 2-D tensor map (64 halfs x 16 rows = 2 KiB, 128-byte swizzle) into shared memory.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+        ::"r"(dst), "l"(tmap), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+}
+// Byte offset of the 16-byte piece c (0..15) of token row r inside a staged 4 KiB tile.
+//   cp.async path: rows of 256 B, piece index XOR (r & 7).
+//   TMA path: the tile arrives as two boxes (dims 0-63 and 64-127) of 16 rows x 128 B, each in the hardware's
+//   128-byte swizzle: piece (c & 7) XOR (r & 7) inside the row.  ldmatrix is bank-conflict free in both.
+template <bool TMA>
+__device__ __forceinline__ uint32_t tile_off(int r, int c) {
+    return TMA ? (uint32_t)((c >> 3) * 2048 + r * 128 + (((c & 7) ^ (r & 7)) << 4))
+               : (uint32_t)(r * 256 + ((c ^ (r & 7)) << 4));
+}
+
 __device__ __forceinline__ void ldmatrix_x4(uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3, uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
@@ -316,6 +363,15 @@ struct AttnParams {
     int *arrive;
     float *lse;
     float *part_o;
+};
+
+// Tensor maps of the pool segments for the TMA loader: segment s of K (and of V) as a 2-D fp16 tensor
+// [rows = blocks * L * Hkv * 16, 128], box 64 x 16, 128-byte swizzle.
+constexpr int kTmaMaxSegments = 8;
+constexpr int kDefaultLoader = 0;  // 0 = cp.async (measured 1-2 % faster), 1 = TMA
+struct TmaMaps {
+    CUtensorMap k[kTmaMaxSegments];
+    CUtensorMap v[kTmaMaxSegments];
 };
 
 // Merge of the split-KV partials of one (sequence, kv head): for each of the G query
@@ -398,18 +454,33 @@ struct WorkMeta {
 
 // HI: the GQA group has more than 8 query heads, so rows 8-15 of the tensor-core tile carry data.
 // For G <= 8 (every Llama shape) their softmax, rescale and write-out work is compiled out.
-template <int WARPS, int STAGES, bool HI>
-__global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __grid_constant__ AttnParams p) {
+template <int WARPS, int STAGES, bool HI, bool TMA>
+__global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __grid_constant__ AttnParams p,
+                                                                        const __grid_constant__ TmaMaps tm) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const uint32_t ring = smem_u32(smem) + warp * (STAGES * kStageBytes);
+    // TMA path: one mbarrier per ring stage of this warp, behind the rings
+    const uint32_t bars = smem_u32(smem) + WARPS * STAGES * kStageBytes + warp * (STAGES * 8);
 
     WsHeader *hdr = p.hdr;
     if (hdr->magic != kMagic || hdr->batch != p.batch) {  // no plan for this batch: refuse, touch nothing
         if (threadIdx.x == 0) atomicOr(&hdr->error_flags, 2);
         return;
+    }
+    if (TMA) {
+        if (smem_u32(smem) & 1023u) {  // the swizzle pattern repeats every 1 KiB: the rings must start on one
+            if (threadIdx.x == 0) atomicOr(&hdr->error_flags, 16);
+            return;
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int s = 0; s < STAGES; ++s) mbar_init(bars + s * 8, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        }
+        __syncwarp();
     }
     const int Hkv = p.pool.num_kv_heads;
     const int G = p.group;
@@ -461,7 +532,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
     const int v_half = lane >> 4;
 
     // One tile (K and V of one block for kv head `head_off`) into a ring stage.
-    auto issue_raw = [&](int64_t blk, int64_t head_off, uint32_t st) {
+    auto issue_raw = [&](int64_t blk, int64_t head_off, unsigned slot) {
+        const uint32_t st = ring + slot * kStageBytes;
         if (!block_in_pool(p.pool, blk)) {
             if (lane == 0) atomicOr(&hdr->error_flags, 1);
             blk = 0;
@@ -469,6 +541,19 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
         int seg;
         int64_t brow;
         locate_block(p.pool, blk, seg, brow);
+        if (TMA) {
+            if (lane == 0) {
+                // first row of the tile in the segment's [rows, 128] view: head_off counts bytes, a row is 256
+                const int row0 = (int)((brow * p.pool.block_bytes + head_off) >> 8);
+                const uint32_t bar = bars + slot * 8;
+                mbar_expect_tx(bar, kStageBytes);
+                tma_load_2d(st, &tm.k[seg], 0, row0, bar);
+                tma_load_2d(st + 2048, &tm.k[seg], 64, row0, bar);
+                tma_load_2d(st + kTileBytes, &tm.v[seg], 0, row0, bar);
+                tma_load_2d(st + kTileBytes + 2048, &tm.v[seg], 64, row0, bar);
+            }
+            return;
+        }
         const char *kt = p.pool.k_base[seg] + brow * p.pool.block_bytes + head_off;
         const char *vt = p.pool.v_base[seg] + brow * p.pool.block_bytes + head_off;
 #pragma unroll
@@ -486,12 +571,14 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
     // first tiles of the next unit (`pre` of them), so the ring never runs empty at a boundary.
     unsigned ring_pos = 0;
     int pre = 0;
+    bool failed = false;
 
     WorkMeta nxt;
     nxt.valid = false;
     while (fstage < 3) fetch_step(nxt);
     while (nxt.valid) {
         const WorkMeta cur = nxt;
+        nxt.valid = false;  // until the next claim lands, `nxt` is this unit: nothing may be prefetched from it
         const int pre_cur = pre;
         pre = 0;
         __syncwarp();  // the previous unit's ldmatrix reads are done before its stages are refilled
@@ -509,14 +596,14 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
                 ids_nxt = (nj < cur.nblk) ? __ldg(cur.table + nj) : 0;
             }
             const int64_t blk = __shfl_sync(0xffffffffu, ids_cur, j & 31);
-            issue_raw(blk, head_off, ring + ((ring_pos + (unsigned)j) % STAGES) * kStageBytes);
+            issue_raw(blk, head_off, (ring_pos + (unsigned)j) % STAGES);
         };
 
 #pragma unroll
         for (int s = 0; s < STAGES - 1; ++s) {
             if (s >= pre_cur) {  // tiles below pre_cur were issued during the previous unit's tail
                 if (s < cur.nblk) issue_tile(s);
-                cp_async_commit();
+                if (!TMA) cp_async_commit();
             }
         }
 
@@ -592,7 +679,20 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
         float m0 = kNegBig, m1 = kNegBig, l0 = 0.f, l1 = 0.f;
 
         for (int j = 0; j < cur.nblk; ++j) {
-            cp_async_wait<STAGES - 2>();
+            const bool patch_tile = has_new && cur.start + j == new_blk;
+            if (TMA) {
+                // tile number ring_pos + j of this warp lands in stage (ring_pos + j) % STAGES on that stage's
+                // ((ring_pos + j) / STAGES)-th use; ring_pos counts every tile since the kernel started
+                const unsigned n = ring_pos + (unsigned)j;
+                const bool landed = mbar_wait(bars + (n % STAGES) * 8, (n / STAGES) & 1u);
+                if (!__all_sync(0xffffffffu, landed)) {  // warp-uniform: the lanes leave together
+                    if (lane == 0) atomicOr(&hdr->error_flags, 8);
+                    failed = true;
+                    break;
+                }
+            } else {
+                cp_async_wait<STAGES - 2>();
+            }
             __syncwarp();
             if (j + STAGES - 1 < cur.nblk) {
                 issue_tile(j + STAGES - 1);
@@ -600,20 +700,22 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
                 // nothing left to fetch for this unit: start on the next one (pre <= j+STAGES-1-nblk < STAGES-1)
                 const int64_t blk = __shfl_sync(0xffffffffu, nxt.ids, pre);
                 issue_raw(blk, ((int64_t)p.cur_layer * Hkv + nxt.h) * kTileBytes,
-                          ring + ((ring_pos + (unsigned)(cur.nblk + pre)) % STAGES) * kStageBytes);
+                          (ring_pos + (unsigned)(cur.nblk + pre)) % STAGES);
                 ++pre;
             }
-            cp_async_commit();
+            if (!TMA) cp_async_commit();
             if (j == claim_at) fstage = 0;
             if (j >= claim_at && fstage < 3) fetch_step(nxt);
 
             const uint32_t st = ring + ((ring_pos + (unsigned)j) % STAGES) * kStageBytes;
-            if (has_new && cur.start + j == new_blk) {
+            if (patch_tile) {
                 const int slot = (cur.len - 1) & 15, c = lane & 15;
-                const uint32_t off = (lane < 16 ? 0 : kTileBytes) + slot * 256;
-                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(st + off + ((c ^ (slot & 7)) << 4)),
+                const uint32_t off = (lane < 16 ? 0 : kTileBytes) + tile_off<TMA>(slot, c);
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(st + off),
                              "r"(new_row.x), "r"(new_row.y), "r"(new_row.z), "r"(new_row.w)
                              : "memory");
+                // this stage is written again later by a bulk copy (async proxy): order the plain store before it
+                if (TMA) asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
                 // the same row into the pool, for the steps to come
                 const int64_t blk = __ldg(cur.table + j);
                 if (block_in_pool(p.pool, blk)) {
@@ -634,7 +736,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
             for (int kk = 0; kk < 8; ++kk) {
                 uint32_t b0, b1, b2, b3;
                 const int c = 2 * kk + k_half;
-                ldmatrix_x4(b0, b1, b2, b3, st + k_tok * 256 + ((c ^ (k_tok & 7)) << 4));
+                ldmatrix_x4(b0, b1, b2, b3, st + tile_off<TMA>(k_tok, c));
                 mma_16816(sc[0], qf[kk], b0, b1);
                 mma_16816(sc[1], qf[kk], b2, b3);
             }
@@ -701,12 +803,14 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
             for (int np = 0; np < 8; ++np) {
                 uint32_t b0, b1, b2, b3;
                 const int c = 2 * np + v_half;
-                ldmatrix_x4_trans(b0, b1, b2, b3, st + kTileBytes + v_tok * 256 + ((c ^ (v_tok & 7)) << 4));
+                ldmatrix_x4_trans(b0, b1, b2, b3, st + kTileBytes + tile_off<TMA>(v_tok, c));
                 mma_16816(oacc[2 * np], pa, b0, b1);
                 mma_16816(oacc[2 * np + 1], pa, b2, b3);
             }
         }
-        ring_pos = (ring_pos + (unsigned)cur.nblk) % STAGES;
+        if (failed) break;  // a copy did not land in time: reported in the error word, nothing more is done
+        ring_pos += (unsigned)cur.nblk;
+        if (!TMA) ring_pos %= STAGES;  // TMA: kept absolute, the stage's barrier phase is derived from it
         while (fstage < 3) fetch_step(nxt);  // short unit: finish the claim now
 
         // ---- epilogue ---------------------------------------------------------
@@ -759,7 +863,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
             }
         }
     }
-    cp_async_wait<0>();
+    if (!TMA) cp_async_wait<0>();
     // the last worker to run dry re-arms the counters for the next launch
     if (lane == 0) {
         const unsigned workers = gridDim.x * WARPS;
@@ -873,35 +977,93 @@ static AttnConfig &attn_config() {
     return c;
 }
 
-template <int WARPS, int STAGES, bool HI>
-static cudaError_t launch_decode_hi(const AttnParams &p, int sm_count, cudaStream_t s) {
-    const int smem = WARPS * STAGES * kStageBytes;
+template <int WARPS, int STAGES, bool HI, bool TMA>
+static cudaError_t launch_decode_one(const AttnParams &p, const TmaMaps &tm, int sm_count, cudaStream_t s) {
+    const int smem = WARPS * STAGES * kStageBytes + (TMA ? WARPS * STAGES * 8 : 0);
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_f16_kernel<WARPS, STAGES, HI>,
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_f16_kernel<WARPS, STAGES, HI, TMA>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
-    attn_decode_f16_kernel<WARPS, STAGES, HI><<<sm_count, WARPS * 32, smem, s>>>(p);
+    attn_decode_f16_kernel<WARPS, STAGES, HI, TMA><<<sm_count, WARPS * 32, smem, s>>>(p, tm);
     return cudaGetLastError();
 }
 
 template <int WARPS, int STAGES>
-static cudaError_t launch_decode(const AttnParams &p, int sm_count, cudaStream_t s) {
-    return p.group > 8 ? launch_decode_hi<WARPS, STAGES, true>(p, sm_count, s)
-                       : launch_decode_hi<WARPS, STAGES, false>(p, sm_count, s);
+static cudaError_t launch_decode(const AttnParams &p, const TmaMaps *tm, int sm_count, cudaStream_t s) {
+    static const TmaMaps no_maps = {};
+    if (tm)
+        return p.group > 8 ? launch_decode_one<WARPS, STAGES, true, true>(p, *tm, sm_count, s)
+                           : launch_decode_one<WARPS, STAGES, false, true>(p, *tm, sm_count, s);
+    return p.group > 8 ? launch_decode_one<WARPS, STAGES, true, false>(p, no_maps, sm_count, s)
+                       : launch_decode_one<WARPS, STAGES, false, false>(p, no_maps, sm_count, s);
 }
 
-static cudaError_t launch_decode_configured(const AttnParams &p, int sms, cudaStream_t s) {
+static cudaError_t launch_decode_configured(const AttnParams &p, const TmaMaps *tm, int sms, cudaStream_t s) {
     const AttnConfig &c = attn_config();
-    if (c.warps == 6 && c.stages == 4) return launch_decode<6, 4>(p, sms, s);
-    if (c.warps == 12 && c.stages == 2) return launch_decode<12, 2>(p, sms, s);
-    if (c.warps == 9 && c.stages == 3) return launch_decode<9, 3>(p, sms, s);
-    if (c.warps == 7 && c.stages == 4) return launch_decode<7, 4>(p, sms, s);
-    return launch_decode<8, 3>(p, sms, s);
+    if (c.warps == 6 && c.stages == 4) return launch_decode<6, 4>(p, tm, sms, s);
+    if (c.warps == 12 && c.stages == 2) return launch_decode<12, 2>(p, tm, sms, s);
+    if (c.warps == 9 && c.stages == 3) return launch_decode<9, 3>(p, tm, sms, s);
+    if (c.warps == 7 && c.stages == 4) return launch_decode<7, 4>(p, tm, sms, s);
+    return launch_decode<8, 3>(p, tm, sms, s);
+}
+
+// ---- tensor maps for the TMA loader ------------------------------------------------------------
+// cuTensorMapEncodeTiled is a driver function; it is looked up at run time so that the library has no link
+// dependency on the driver (it loads, and every host-side check works, on a machine without a GPU).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn tensor_map_encoder() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+        tried = true;
+    }
+    return fn;
+}
+
+static int g_loader = -1;
+static int loader_choice() {  // tuning knob MKV_ATTN_LOADER: "tma" (1) or "cpasync" (0)
+    if (g_loader < 0) {
+        const char *e = getenv("MKV_ATTN_LOADER");
+        g_loader = e ? (strcmp(e, "cpasync") == 0 ? 0 : 1) : kDefaultLoader;
+    }
+    return g_loader;
+}
+
+// Fills `tm` for the pool; false if the TMA loader cannot serve it (then the cp.async loader runs).
+static bool make_tma_maps(const PoolView &pv, TmaMaps *tm) {
+    if (!loader_choice() || pv.num_segments > kTmaMaxSegments) return false;
+    EncodeTiledFn encode = tensor_map_encoder();
+    if (!encode) return false;
+    const cuuint64_t rows_per_block = (cuuint64_t)pv.num_layers * pv.num_kv_heads * kBS;
+    for (int i = 0; i < pv.num_segments; ++i) {
+        const cuuint64_t blocks = i == 0 ? (cuuint64_t)pv.num_blocks_org : (cuuint64_t)pv.chunk_blocks;
+        const cuuint64_t dims[2] = {(cuuint64_t)kD, blocks * rows_per_block};
+        const cuuint64_t strides[1] = {(cuuint64_t)kD * 2};      // bytes between rows
+        const cuuint32_t box[2] = {64, (cuuint32_t)kBS};         // 128 B x 16 rows
+        const cuuint32_t elem_strides[2] = {1, 1};
+        if (dims[1] == 0 || dims[1] > 0x7fffffffull) return false;
+        for (int kv = 0; kv < 2; ++kv) {
+            void *base = kv ? pv.v_base[i] : pv.k_base[i];
+            CUresult r = encode(kv ? &tm->v[i] : &tm->k[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides,
+                                box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return false;
+        }
+    }
+    return true;
 }
 
 static bool fast_path_ok(const PoolView &pv, int num_q_heads, const void *q, const void *o) {
@@ -1053,7 +1215,9 @@ static int attention_decode_impl(int device, void *stream, const void *q, void *
     p.lse = (float *)(ws + L.lse);
     p.part_o = (float *)(ws + L.part_o);
 
-    cudaError_t e = launch_decode_configured(p, sms, s);
+    TmaMaps tm;
+    const bool use_tma = make_tma_maps(pv, &tm);
+    cudaError_t e = launch_decode_configured(p, use_tma ? &tm : nullptr, sms, s);
     if (e != cudaSuccess) return set_cuda_error(e);
     return MKV_OK;
 }
@@ -1115,7 +1279,7 @@ int mkv_paged_attention_decode_push(int device, void *stream, const void *q, voi
                                  max_blocks_per_seq_in_batch, workspace, workspace_bytes);
 }
 
-int mkv_attn_configure(int warps, int stages, double item_factor_value, double split_balance_value) {
+int mkv_attn_configure(int warps, int stages, double item_factor_value, double split_balance_value, int loader) {
     AttnConfig &c = attn_config();
     if (warps > 0 && stages > 1) {
         c.warps = warps;
@@ -1126,6 +1290,10 @@ int mkv_attn_configure(int warps, int stages, double item_factor_value, double s
         g_item_factor = item_factor_value;
     }
     if (split_balance_value >= 0.0) g_split_balance = split_balance_value;
+    if (loader == 0 || loader == 1) {
+        loader_choice();
+        g_loader = loader;
+    }
     return MKV_OK;
 }
 
@@ -1258,7 +1426,9 @@ int mkv_paged_attention_decode_noalloc(int device, void *stream, const void *q, 
     p.arrive = (int *)(ws + L.arrive);
     p.lse = (float *)(ws + L.lse);
     p.part_o = (float *)(ws + L.part_o);
-    cudaError_t e = launch_decode<8, 3>(p, sms, s);
+    TmaMaps tm;
+    const bool use_tma = make_tma_maps(pv, &tm);
+    cudaError_t e = launch_decode<8, 3>(p, use_tma ? &tm : nullptr, sms, s);
     if (e != cudaSuccess) return set_cuda_error(e);
     return MKV_OK;
 }

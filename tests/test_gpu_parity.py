@@ -15,6 +15,7 @@ from tests.golden import cases
 pytestmark = pytest.mark.gpu
 G = os.path.join(os.path.dirname(__file__), "golden")
 RTOL, ATOL = 2e-3, 1e-2
+DEFAULT_LOADER = 1 if os.environ.get("MKV_ATTN_LOADER") == "tma" else 0      # the library's default is cp.async
 
 
 @pytest.fixture(params=["separate", "fused_append"], autouse=True)
@@ -25,6 +26,15 @@ def append_mode(request):
     morphserve_b200.set_fused_decode_append(request.param == "fused_append")
     yield request.param
     morphserve_b200.set_fused_decode_append(False)
+
+
+@pytest.fixture(params=["tma", "cpasync"], autouse=True)
+def tile_loader(request):
+    """... and with both tile loaders of the decode kernel (TMA boxes / 16-byte cp.async)."""
+    from morphserve_b200._lib import lib, check
+    check(lib.mkv_attn_configure(-1, -1, -1.0, -1.0, 1 if request.param == "tma" else 0), "mkv_attn_configure")
+    yield request.param
+    check(lib.mkv_attn_configure(-1, -1, -1.0, -1.0, DEFAULT_LOADER), "mkv_attn_configure")
 
 
 def _close(a, b):
@@ -169,11 +179,31 @@ def test_split_rule_extremes(balance, shape):
     nb = int(((lens + 15) // 16).sum()) + 5
     c = cases.build_decode_case(seed=2718, B=B, Hq=Hq, Hkv=Hkv, D=128, bs=16, L=1, layer=0, num_blocks_org=nb,
                                 dtype=np.float16, lens=lens)
-    check(lib.mkv_attn_configure(-1, -1, -1.0, balance), "mkv_attn_configure")
+    check(lib.mkv_attn_configure(-1, -1, -1.0, balance, -1), "mkv_attn_configure")
     try:
         o, kp, vp = H.run_decode_step(H.device_case(c))
     finally:
-        check(lib.mkv_attn_configure(-1, -1, -1.0, 1.5), "mkv_attn_configure")
+        check(lib.mkv_attn_configure(-1, -1, -1.0, 1.5, -1), "mkv_attn_configure")
+    ex = O.paged_attention_exact(c["q"], kp, vp, c["block_table"], c["seq_ids"], c["seq_lens"], 0, c["scale"],
+                                 c["num_blocks_org"], 0)
+    _close(o, ex)
+    from morphserve_b200.worker.kernels._common import read_attn_error_flags
+    assert read_attn_error_flags(0) == 0
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(8, 2), (16, 16)])
+def test_many_short_sequences_per_worker(Hq, Hkv):
+    """More (sequence, kv head) units than worker warps, nearly all of one or two blocks, a few long ones in
+    between: every warp runs several short units back to back, so the hand-over between units (claim of the next
+    unit, prefetch of its first tiles into freed stages) is exercised where it has the least slack."""
+    rs = np.random.RandomState(Hq)
+    B = 1400
+    lens = rs.randint(1, 41, size=B)
+    lens[rs.permutation(B)[:40]] = rs.randint(41, 400, size=40)
+    nb = int(((lens + 15) // 16).sum()) + 7
+    c = cases.build_decode_case(seed=4242 + Hkv, B=B, Hq=Hq, Hkv=Hkv, D=128, bs=16, L=1, layer=0, num_blocks_org=nb,
+                                dtype=np.float16, lens=lens)
+    o, kp, vp = H.run_decode_step(H.device_case(c))
     ex = O.paged_attention_exact(c["q"], kp, vp, c["block_table"], c["seq_ids"], c["seq_lens"], 0, c["scale"],
                                  c["num_blocks_org"], 0)
     _close(o, ex)
