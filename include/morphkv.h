@@ -187,8 +187,10 @@ int mkv_paged_attention_decode_rope_append(
  * `split_balance` (< 0 keeps; default 1.5): a sequence is only cut into chunks
  * when it is longer than split_balance x the mean number of KV blocks per worker
  * warp, since every cut costs fp32 partial rows and a merge; 0 cuts as finely as
- * the item factor allows.  `loader` (other values keep): 1 = K/V tiles arrive by TMA
- * (cp.async.bulk.tensor, pools of up to 8 segments), 0 = by 16-byte cp.async.
+ * the item factor allows.  `loader` (other values keep): 0 = K/V tiles arrive by 16-byte
+ * cp.async (default), 1 = by TMA (cp.async.bulk.tensor, pools of up to 8 segments), 2 = the
+ * tensor-core kernel is not used at all: every shape goes through the plain kernel (one warp per
+ * query head, fp32 FMA) - an independent implementation for cross-checks at full size.
  */
 int mkv_attn_configure(int warps, int stages, double item_factor, double split_balance, int loader);
 

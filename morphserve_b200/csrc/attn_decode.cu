@@ -1034,7 +1034,7 @@ static EncodeTiledFn tensor_map_encoder() {
 }
 
 static int g_loader = -1;
-static int loader_choice() {  // tuning knob MKV_ATTN_LOADER: "tma" (1) or "cpasync" (0)
+static int loader_choice() {  // tuning knob MKV_ATTN_LOADER: "tma" (1) or "cpasync" (0); 2 = no fast path at all
     if (g_loader < 0) {
         const char *e = getenv("MKV_ATTN_LOADER");
         g_loader = e ? (strcmp(e, "cpasync") == 0 ? 0 : 1) : kDefaultLoader;
@@ -1044,7 +1044,7 @@ static int loader_choice() {  // tuning knob MKV_ATTN_LOADER: "tma" (1) or "cpas
 
 // Fills `tm` for the pool; false if the TMA loader cannot serve it (then the cp.async loader runs).
 static bool make_tma_maps(const PoolView &pv, TmaMaps *tm) {
-    if (!loader_choice() || pv.num_segments > kTmaMaxSegments) return false;
+    if (loader_choice() != 1 || pv.num_segments > kTmaMaxSegments) return false;
     EncodeTiledFn encode = tensor_map_encoder();
     if (!encode) return false;
     const cuuint64_t rows_per_block = (cuuint64_t)pv.num_layers * pv.num_kv_heads * kBS;
@@ -1067,6 +1067,7 @@ static bool make_tma_maps(const PoolView &pv, TmaMaps *tm) {
 }
 
 static bool fast_path_ok(const PoolView &pv, int num_q_heads, const void *q, const void *o) {
+    if (loader_choice() == 2) return false;  // testing knob: everything through the plain kernel
     if (pv.elem_bytes != 2 || pv.head_dim != kD || pv.block_size != kBS) return false;
     if (num_q_heads % pv.num_kv_heads != 0 || num_q_heads / pv.num_kv_heads > 16) return false;
     if ((((uintptr_t)q) | ((uintptr_t)o)) % 16 != 0) return false;
@@ -1290,7 +1291,7 @@ int mkv_attn_configure(int warps, int stages, double item_factor_value, double s
         g_item_factor = item_factor_value;
     }
     if (split_balance_value >= 0.0) g_split_balance = split_balance_value;
-    if (loader == 0 || loader == 1) {
+    if (loader >= 0 && loader <= 2) {
         loader_choice();
         g_loader = loader;
     }

@@ -105,6 +105,20 @@ def test_baseline_decode_config_full_size(name, balance):
             kk, vv = _gather_seq([job.k_cache], [job.v_cache], table[b], (n + BS - 1) // BS, layer, job.nb, 0)
             ex = _oracle_attention(job.q[layer, b].cpu().numpy(), kk, vv, n, D ** -0.5)
             np.testing.assert_allclose(o[b].cpu().numpy().astype(np.float64), ex, rtol=2e-3, atol=1e-2)
+    # attention, EVERY sequence and layer: against the library's plain kernel (one warp per query head, fp32 FMA,
+    # no plan, no split, no tensor cores - held to the oracle by the small-shape tests)
+    st = job.infer_state(job.seq_ids, job.lens_dev)
+    check(lib.mkv_attn_configure(-1, -1, -1.0, -1.0, 2), "mkv_attn_configure")
+    try:
+        plain = torch.empty_like(job.o)
+        for layer in range(w["L"]):
+            job.mk.paged_attention(job.q[layer], job.k_cache, job.v_cache, [], [], bm.block_table, job.model_config,
+                                   job.engine_config, st, layer, plain[layer])
+        torch.cuda.synchronize()
+    finally:
+        check(lib.mkv_attn_configure(-1, -1, -1.0, -1.0, 0), "mkv_attn_configure")
+    diff = (job.o.float() - plain.float()).abs()
+    assert bool((diff <= 1e-2 + 2e-3 * plain.float().abs()).all()), f"max difference {float(diff.max())}"
     from morphserve_b200.worker.kernels._common import read_attn_error_flags
     assert read_attn_error_flags(0) == 0
 

@@ -211,6 +211,76 @@ def test_many_short_sequences_per_worker(Hq, Hkv):
     assert read_attn_error_flags(0) == 0
 
 
+def _random_batch(rs):
+    """A batch shape drawn to stress the scheduler: batch size from a handful to thousands, group size 1-16,
+    lengths from one of several mixtures (all short, uniform, a few giants among short ones, all equal)."""
+    Hkv = int(rs.choice([1, 2, 4, 8, 16]))
+    G = int(rs.choice([1, 2, 4, 8, 16]))
+    kind = int(rs.randint(0, 4))
+    B = int(rs.choice([3, 40, 300, 1300, 2600])) if kind != 2 else int(rs.choice([40, 300, 1300]))
+    if kind == 0:
+        lens = rs.randint(1, 49, size=B)
+    elif kind == 1:
+        lens = rs.randint(1, 700, size=B) if B <= 300 else rs.randint(1, 120, size=B)
+    elif kind == 2:
+        lens = rs.randint(1, 60, size=B)
+        lens[rs.permutation(B)[: max(1, B // 100)]] = rs.randint(1500, 6000, size=max(1, B // 100))
+    else:
+        lens = np.full(B, int(rs.choice([16, 17, 64, 130])))
+    return B, Hkv * G, Hkv, lens
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_batches_fast_path_against_plain_kernel(seed):
+    """Seeded random batches, all sequences compared on the GPU: the tensor-core kernel (plan, dynamic schedule,
+    split-KV merge, fused append when the fixture says so) against the library's plain kernel, which shares none
+    of that machinery and is held to the oracle by the tests above."""
+    from morphserve_b200._lib import lib, check
+    rs = np.random.RandomState(1000 + seed)
+    B, Hq, Hkv, lens = _random_batch(rs)
+    nb = int(((lens + 15) // 16).sum()) + 3
+    L = 2
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    kc = torch.randn((nb, L, Hkv, 16, 128), generator=g, dtype=torch.float16, device="cuda")
+    vc = torch.randn((nb, L, Hkv, 16, 128), generator=g, dtype=torch.float16, device="cuda")
+    q = torch.randn((B, Hq, 128), generator=g, dtype=torch.float16, device="cuda")
+    kn = torch.randn((B, Hkv, 128), generator=g, dtype=torch.float16, device="cuda")
+    vn = torch.randn((B, Hkv, 128), generator=g, dtype=torch.float16, device="cuda")
+    need = (lens + 15) // 16
+    perm = rs.permutation(nb)
+    table = np.full((B, int(need.max()) + 1), -1, dtype=np.int32)
+    pos = 0
+    for b in range(B):
+        table[b, : need[b]] = perm[pos:pos + need[b]]
+        pos += need[b]
+    c = dict(L=L, Hq=Hq, Hkv=Hkv, D=128, bs=16, scale=128 ** -0.5, num_blocks_org=nb, chunk_blocks=0)
+    bt, ids, lens_t = H.to_dev(table), torch.arange(B, dtype=torch.int32, device="cuda"), H.to_dev(lens.astype(np.int32))
+    mc, ec = H.cfgs(c, bt.shape[1])
+    from morphserve_b200 import paged_attention, store_kvcache
+    outs = []
+    for force_plain in (False, True):
+        k2, v2 = kc.clone(), vc.clone()
+        if force_plain:
+            check(lib.mkv_attn_configure(-1, -1, -1.0, -1.0, 2), "mkv_attn_configure")
+        try:
+            st = H.decode_state(c, ids, lens_t)
+            o = torch.zeros((B, Hq * 128), dtype=torch.float16, device="cuda")
+            store_kvcache(kn, vn, k2, v2, [], [], bt, mc, ec, st, 1)
+            paged_attention(q, k2, v2, [], [], bt, mc, ec, st, 1, o)
+            torch.cuda.synchronize()
+        finally:
+            if force_plain:
+                check(lib.mkv_attn_configure(-1, -1, -1.0, -1.0, DEFAULT_LOADER), "mkv_attn_configure")
+        outs.append((o, k2, v2))
+    (o_fast, k_fast, v_fast), (o_plain, k_plain, v_plain) = outs
+    assert torch.equal(k_fast, k_plain) and torch.equal(v_fast, v_plain), "appended pools differ"
+    diff = (o_fast.float() - o_plain.float()).abs()
+    bad = diff > ATOL + RTOL * o_plain.float().abs()
+    assert not bool(bad.any()), f"B={B} Hq={Hq} Hkv={Hkv}: {int(bad.any(dim=1).sum())} sequences differ, max {float(diff.max())}"
+    from morphserve_b200.worker.kernels._common import read_attn_error_flags
+    assert read_attn_error_flags(0) == 0
+
+
 def test_every_length_across_block_and_chunk_edges():
     """lens 1..160 in one batch: every len % 16, single- and multi-block sequences."""
     lens = np.arange(1, 161)
