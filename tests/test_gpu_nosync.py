@@ -91,6 +91,92 @@ def test_nosync_allocate_large_batch_against_oracle():
         lens = (lens + rs.randint(0, 40, size=2500)).astype(np.int32)
 
 
+def test_block_manager_large_batches_against_oracle():
+    """allocate / free / gather with thousands of sequences per call (several passes of the one-block kernels'
+    scan loops) in lockstep with the oracle: tables, counts, bitmap, returned ids."""
+    from morphserve_b200 import BlockManager
+    rs = np.random.RandomState(8)
+    nb, max_seqs, cols, bs = 130000, 5000, 24, 16
+    bm = BlockManager("GPU", nb, max_seqs, cols, bs)
+    ob = O.BlockManagerOracle(nb, max_seqs, cols, bs)
+    lens = np.zeros(max_seqs, dtype=np.int64)
+    for step in range(6):
+        ids = rs.permutation(max_seqs)[: rs.randint(1500, 4000)].astype(np.int32)
+        new = np.minimum(lens[ids] + rs.randint(0, 120, size=len(ids)), cols * bs).astype(np.int32)
+        lens[ids] = new
+        got = bm.allocate_blocks_for_seqs(H.to_dev(ids), H.to_dev(new))
+        exp = ob.allocate_blocks_for_seqs(ids, new)
+        np.testing.assert_array_equal(got.cpu().numpy(), exp)
+        drop = rs.permutation(max_seqs)[: rs.randint(1100, 2500)].astype(np.int32)
+        if step % 2 == 0:
+            bm.free_blocks_for_seqs(H.to_dev(drop))
+            ob.free_blocks_for_seqs(drop)
+        else:
+            g = bm.gather_allocated_blocks_and_free(H.to_dev(drop))
+            np.testing.assert_array_equal(g.cpu().numpy(), ob.gather_allocated_blocks_and_free(drop))
+        lens[drop] = 0
+        np.testing.assert_array_equal(bm.num_seq_allocated_blocks.cpu().numpy(), ob.num_seq_allocated_blocks)
+        np.testing.assert_array_equal(bm.is_block_free.cpu().numpy(), ob.is_block_free)
+        assert int(bm.num_free_blocks) == int(ob.num_free_blocks)
+        live = ob.num_seq_allocated_blocks > 0          # rows of freed sequences keep stale ids on both sides
+        np.testing.assert_array_equal(bm.block_table.cpu().numpy()[live], ob.block_table[live])
+
+
+def test_prefill_scatter_mid_size_against_torch_indexing():
+    """48 prompts of up to 1500 tokens plus decode rows, elastic pool of three segments: the scatter kernels against
+    the same assignment written with torch advanced indexing (bit-exact)."""
+    from morphserve_b200 import store_kvcache
+    from morphserve_b200.worker.infer_state import LlamaInferState
+    rs = np.random.RandomState(21)
+    Hkv, D, L, layer, bs = 4, 128, 3, 2, 16
+    plens = rs.randint(1, 1500, size=48)
+    dlens = rs.randint(1, 900, size=30)
+    all_lens = np.concatenate([plens, dlens])
+    need = (all_lens + bs - 1) // bs
+    total = int(need.sum()) + 11
+    nb_org, chunk = total // 2, (total - total // 2 + 1) // 2
+    perm = rs.permutation(nb_org + 2 * chunk)
+    nseq = len(all_lens)
+    seq_ids = rs.permutation(nseq + 5)[:nseq].astype(np.int32)
+    table = np.full((nseq + 5, int(need.max()) + 1), -1, dtype=np.int32)
+    pos = 0
+    for i in range(nseq):
+        table[seq_ids[i], : need[i]] = perm[pos:pos + need[i]]
+        pos += need[i]
+    ntok = int(plens.sum()) + len(dlens)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    k = torch.randn((ntok, Hkv, D), generator=g, dtype=torch.float16, device="cuda")
+    v = torch.randn((ntok, Hkv, D), generator=g, dtype=torch.float16, device="cuda")
+    shapes = [(nb_org, L, Hkv, bs, D), (chunk, L, Hkv, bs, D), (chunk, L, Hkv, bs, D)]
+    kp = [torch.randn(sh, generator=g, dtype=torch.float16, device="cuda") for sh in shapes]
+    vp = [torch.randn(sh, generator=g, dtype=torch.float16, device="cuda") for sh in shapes]
+    ref_k, ref_v = [t.clone() for t in kp], [t.clone() for t in vp]
+    # reference: token -> (segment, row, slot) with numpy integer arithmetic, assignment with torch indexing
+    tok_seq = np.concatenate([np.repeat(np.arange(len(plens)), plens), len(plens) + np.arange(len(dlens))])
+    tok_pos = np.concatenate([np.concatenate([np.arange(n) for n in plens]), dlens - 1])
+    blk = table[seq_ids[tok_seq], tok_pos // bs].astype(np.int64)
+    seg = np.where(blk < nb_org, 0, 1 + (blk - nb_org) // chunk)
+    row = np.where(blk < nb_org, blk, (blk - nb_org) % chunk)
+    for s_i in range(3):
+        m = np.nonzero(seg == s_i)[0]
+        mi, ri, si = H.to_dev(m).long(), H.to_dev(row[m]).long(), H.to_dev(tok_pos[m] % bs).long()
+        ref_k[s_i][ri, layer, :, si, :] = k[mi]
+        ref_v[s_i][ri, layer, :, si, :] = v[mi]
+    z = torch.zeros(0, dtype=torch.int32, device="cuda")
+    st = LlamaInferState(
+        batch_size=nseq, num_tokens=ntok, seq_ids=H.to_dev(seq_ids), softmax_scale=1.0, num_prefill_seqs=len(plens),
+        num_prefill_tokens=int(plens.sum()), prefill_seq_start_locs=H.to_dev((np.cumsum(plens) - plens).astype(np.int32)),
+        prefill_seq_start_locs_with_end=z, prefill_seq_lens=H.to_dev(plens.astype(np.int32)),
+        max_prefill_len=int(plens.max()), num_decoding_seqs=len(dlens), decoding_seq_lens=H.to_dev(dlens.astype(np.int32)),
+        max_decoding_len=int(dlens.max()), seq_block_size=512, num_seq_blocks=2, num_blocks_org=nb_org,
+        kv_cache_new_block_size=chunk, org_layer_param_size=0, position_cos=z, position_sin=z, ignore_kvcache=False)
+    mc, ec = H.cfgs(dict(L=L, Hkv=Hkv, D=D, bs=bs), table.shape[1])
+    store_kvcache(k, v, kp[0], vp[0], kp[1:], vp[1:], H.to_dev(table), mc, ec, st, layer)
+    torch.cuda.synchronize()
+    for a, b in zip(kp + vp, ref_k + ref_v):
+        assert torch.equal(a, b)
+
+
 def _make_job(L=2, B=24):
     import bench
     w = dict(cfg=77, B=B, Hq=32, Hkv=8, L=L, max_len=700, free_frac=0.2, rope=True)

@@ -241,8 +241,12 @@ def test_random_batches_fast_path_against_plain_kernel(seed):
     nb = int(((lens + 15) // 16).sum()) + 3
     L = 2
     g = torch.Generator(device="cuda").manual_seed(seed)
-    kc = torch.randn((nb, L, Hkv, 16, 128), generator=g, dtype=torch.float16, device="cuda")
-    vc = torch.randn((nb, L, Hkv, 16, 128), generator=g, dtype=torch.float16, device="cuda")
+    # odd seeds: the pool is an original part plus two elastic chunks (three segments)
+    nb_org, chunk = (nb, 0) if seed % 2 == 0 else (nb // 3, (nb - nb // 3 + 1) // 2)
+    sizes = [nb_org] + ([chunk, chunk] if chunk else [])
+    nb = sum(sizes)
+    kseg = [torch.randn((n, L, Hkv, 16, 128), generator=g, dtype=torch.float16, device="cuda") for n in sizes]
+    vseg = [torch.randn((n, L, Hkv, 16, 128), generator=g, dtype=torch.float16, device="cuda") for n in sizes]
     q = torch.randn((B, Hq, 128), generator=g, dtype=torch.float16, device="cuda")
     kn = torch.randn((B, Hkv, 128), generator=g, dtype=torch.float16, device="cuda")
     vn = torch.randn((B, Hkv, 128), generator=g, dtype=torch.float16, device="cuda")
@@ -253,27 +257,28 @@ def test_random_batches_fast_path_against_plain_kernel(seed):
     for b in range(B):
         table[b, : need[b]] = perm[pos:pos + need[b]]
         pos += need[b]
-    c = dict(L=L, Hq=Hq, Hkv=Hkv, D=128, bs=16, scale=128 ** -0.5, num_blocks_org=nb, chunk_blocks=0)
+    c = dict(L=L, Hq=Hq, Hkv=Hkv, D=128, bs=16, scale=128 ** -0.5, num_blocks_org=nb_org, chunk_blocks=chunk)
     bt, ids, lens_t = H.to_dev(table), torch.arange(B, dtype=torch.int32, device="cuda"), H.to_dev(lens.astype(np.int32))
     mc, ec = H.cfgs(c, bt.shape[1])
     from morphserve_b200 import paged_attention, store_kvcache
     outs = []
     for force_plain in (False, True):
-        k2, v2 = kc.clone(), vc.clone()
+        k2, v2 = [t.clone() for t in kseg], [t.clone() for t in vseg]
         if force_plain:
             check(lib.mkv_attn_configure(-1, -1, -1.0, -1.0, 2), "mkv_attn_configure")
         try:
             st = H.decode_state(c, ids, lens_t)
             o = torch.zeros((B, Hq * 128), dtype=torch.float16, device="cuda")
-            store_kvcache(kn, vn, k2, v2, [], [], bt, mc, ec, st, 1)
-            paged_attention(q, k2, v2, [], [], bt, mc, ec, st, 1, o)
+            store_kvcache(kn, vn, k2[0], v2[0], k2[1:], v2[1:], bt, mc, ec, st, 1)
+            paged_attention(q, k2[0], v2[0], k2[1:], v2[1:], bt, mc, ec, st, 1, o)
             torch.cuda.synchronize()
         finally:
             if force_plain:
                 check(lib.mkv_attn_configure(-1, -1, -1.0, -1.0, DEFAULT_LOADER), "mkv_attn_configure")
         outs.append((o, k2, v2))
     (o_fast, k_fast, v_fast), (o_plain, k_plain, v_plain) = outs
-    assert torch.equal(k_fast, k_plain) and torch.equal(v_fast, v_plain), "appended pools differ"
+    for a, b in zip(k_fast + v_fast, k_plain + v_plain):
+        assert torch.equal(a, b), "appended pools differ"
     diff = (o_fast.float() - o_plain.float()).abs()
     bad = diff > ATOL + RTOL * o_plain.float().abs()
     assert not bool(bad.any()), f"B={B} Hq={Hq} Hkv={Hkv}: {int(bad.any(dim=1).sum())} sequences differ, max {float(diff.max())}"
