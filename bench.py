@@ -311,18 +311,19 @@ class DecodeJob:
         self.ev_out = [torch.cuda.Event() for _ in range(L)]
         return self.hq.nbytes + self.hk.nbytes + self.hv.nbytes + 8 * self.w["B"], self.ho.nbytes
 
-    def step_host(self):
-        """The same step as a caller with host data makes it: metadata from Python
-        lists (as the reference's LlamaModel.forward builds it), the q/k/v of each
-        layer copied from pinned memory, the attention output of each layer read
-        back.  Copies run on two side streams, layer by layer, so that layer l+1's
-        inputs arrive and layer l-1's output leaves while layer l computes; the
-        step ends when the last output byte is on the host."""
-        main = torch.cuda.current_stream()
+    def _stage_metadata(self):
+        """Sequence ids and lengths of the coming step: Python lists (as the reference's LlamaModel.forward
+        holds them) -> one pinned staging buffer."""
         self.lens_host += 1
-        # sequence ids and lengths: Python lists -> one pinned staging buffer -> one asynchronous copy
-        self.h_meta[0].copy_(torch.tensor(self.seq_ids_list, dtype=torch.int32))
-        self.h_meta[1].copy_(torch.tensor(self.lens_host.tolist(), dtype=torch.int32))
+        meta = self.h_meta.numpy()              # a view of the pinned buffer
+        meta[0] = self.seq_ids_list
+        meta[1] = self.lens_host
+
+    def _enqueue_host_step(self, main, max_len=None):
+        """Everything a step with host-side data puts on the GPU's queues, nothing that waits for it: the
+        metadata copy, the sync-free allocate, and per layer the q/k/v copies from pinned memory (side stream, one
+        layer ahead), rotary/append/attention, and the copy of the layer's output back to pinned memory (second
+        side stream)."""
         self.d_meta.copy_(self.h_meta, non_blocking=True)
         seq_ids, lens = self.d_meta[0], self.d_meta[1]
         self.lens_dev = lens
@@ -337,7 +338,7 @@ class DecodeJob:
 
         copy_in(0)
         self.bm.allocate_blocks_for_seqs_nosync(seq_ids, lens)      # no host round trip: the layers queue up behind it
-        st = self.infer_state(seq_ids, lens)
+        st = self.infer_state(seq_ids, lens, max_len=max_len)
         mk, mc, ec, bt = self.mk, self.model_config, self.engine_config, self.bm.block_table
         for layer in range(L):
             if layer + 1 < L:
@@ -352,9 +353,44 @@ class DecodeJob:
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(self.ev_out[layer])
                 self.ho[layer].copy_(self.o[layer], non_blocking=True)
+
+    def step_host(self):
+        """One step as a caller with host data makes it; it ends when the last output byte is on the host and
+        the host has the allocation result."""
+        main = torch.cuda.current_stream()
+        self._stage_metadata()
+        self._enqueue_host_step(main)
         self.s_out.synchronize()
         main.synchronize()
         _ = self.bm.num_free_blocks     # folds the device-side allocation record into the host counters
+
+    def capture_step_host(self, max_steps):
+        """The host-data step as ONE CUDA graph: copy nodes for the metadata, every layer's inputs and outputs
+        (pinned buffers at fixed addresses) on two forked branches, the kernels on the main branch."""
+        from morphserve_b200.worker.kernels._common import attn_workspace
+        w = self.w
+        self.bm.prepare_nosync(w["B"])
+        self.graph_max_len = min(int(self.lens_host.max()) + max_steps, self.bm.block_table.shape[1] * BS)
+        max_blocks = min((self.graph_max_len + BS - 1) // BS, self.bm.block_table.shape[1])
+        attn_workspace(self.dev.index or 0, w["B"], w["Hq"], w["Hkv"], D, max_blocks)    # allocated before the capture
+        torch.cuda.synchronize()
+        self.graph_host = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph_host, capture_error_mode="thread_local"):
+            main = torch.cuda.current_stream()
+            self.s_in.wait_stream(main)             # fork: the copy streams join the capture
+            self.s_out.wait_stream(main)
+            self._enqueue_host_step(main, max_len=self.graph_max_len)
+            main.wait_stream(self.s_in)             # join
+            main.wait_stream(self.s_out)
+
+    def step_host_graph(self):
+        """The host-data step as one graph launch: stage the metadata, replay, wait for the outputs."""
+        self._stage_metadata()
+        assert int(self.lens_host.max()) <= self.graph_max_len, "captured step outgrown: capture again"
+        self.graph_host.replay()
+        torch.cuda.current_stream().synchronize()
+        self.bm.nosync_replayed()
+        _ = self.bm.num_free_blocks
 
     def kv_bytes_per_layer(self):
         return 2 * 2 * self.w["Hkv"] * D * int(self.lens_host.sum())
@@ -879,13 +915,18 @@ def main():
     e2e = None
     if not args.no_e2e:
         h2d, d2h = job.make_host_buffers()
-        for _ in range(3):
-            job.step_host()
-        barrier()
+        host_step = job.step_host
         Ke = max(3, min(K, 20))
+        if use_graph:
+            job.step_host()
+            job.capture_step_host(max_steps=Ke + 8)
+            host_step = job.step_host_graph
+        for _ in range(3):
+            host_step()
+        barrier()
         e0.record()
         for _ in range(Ke):
-            job.step_host()
+            host_step()
         e1.record()
         barrier()
         e2e_ms = max_over_ranks(e0.elapsed_time(e1), dist, device)

@@ -214,3 +214,30 @@ def test_decode_step_captured_in_a_cuda_graph_equals_eager_steps():
     assert torch.equal(job.o, eager.o)
     from morphserve_b200.worker.kernels._common import read_attn_error_flags
     assert read_attn_error_flags(0) == 0
+
+
+def test_host_buffer_step_captured_with_its_copies_equals_eager_steps():
+    """The step with host-side inputs and outputs (pinned q/k/v in, attention output back) as one graph with copy
+    nodes on forked branches: outputs on the host, pool bytes and tables equal the same steps issued call by call."""
+    import morphserve_b200 as mk
+    steps = 6
+    mk.set_fused_decode_append(True)
+    mk.set_fused_decode_rope(True)
+    try:
+        eager = _make_job()
+        eager.make_host_buffers()
+        for _ in range(steps):
+            eager.step_host()
+        job = _make_job()
+        job.make_host_buffers()
+        job.capture_step_host(max_steps=steps + 2)
+        for _ in range(steps):
+            job.step_host_graph()
+        torch.cuda.synchronize()
+    finally:
+        mk.set_fused_decode_append(False)
+        mk.set_fused_decode_rope(False)
+    assert torch.equal(job.ho, eager.ho) and bool(job.ho.abs().sum() > 0)
+    assert torch.equal(job.bm.block_table, eager.bm.block_table)
+    assert int(job.bm.num_free_blocks) == int(eager.bm.num_free_blocks)
+    assert torch.equal(job.k_cache, eager.k_cache) and torch.equal(job.v_cache, eager.v_cache)
