@@ -75,23 +75,54 @@ __global__ void store_kv_prefill_kernel(const char *__restrict__ k, const char *
     const int total = ntok * per_tok * 2;
     const int64_t blk_base = row * pool.block_bytes +
                              (int64_t)cur_layer * pool.num_kv_heads * pool.block_size * (int64_t)row_bytes;
-    for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
-        int which = idx / (ntok * per_tok);
-        int r = idx - which * ntok * per_tok;
-        int t = r / per_tok;
-        int rem = r - t * per_tok;
-        int h = rem / pieces_per_row;
-        int piece = rem - h * pieces_per_row;
-        int64_t src_off = ((start + t0 + t) * pool.num_kv_heads + h) * (int64_t)row_bytes + (int64_t)piece * VEC;
-        int64_t dst_off = blk_base + ((int64_t)h * pool.block_size + t) * row_bytes + (int64_t)piece * VEC;
-        const char *src = (which ? v : k) + src_off;
-        char *dst = (which ? pool.v_base[seg] : pool.k_base[seg]) + dst_off;
-        if (VEC == 16)
-            *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(src);
-        else if (VEC == 4)
-            *reinterpret_cast<uint32_t *>(dst) = *reinterpret_cast<const uint32_t *>(src);
-        else
-            *reinterpret_cast<uint16_t *>(dst) = *reinterpret_cast<const uint16_t *>(src);
+    // U pieces per thread and pass: all loads are issued before the first store, so that a thread has U requests
+    // in flight instead of one (the kernel is latency bound otherwise: 59 % of DRAM peak with one).
+    constexpr int U = 4;
+    const int half = ntok * per_tok;
+    for (int base = threadIdx.x; base < total; base += U * blockDim.x) {
+        const char *src[U];
+        char *dst[U];
+        bool on[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int idx = base + u * blockDim.x;
+            on[u] = idx < total;
+            const int which = idx >= half;
+            const int r = idx - which * half;
+            const int t = r / per_tok;
+            const int rem = r - t * per_tok;
+            const int h = rem / pieces_per_row;
+            const int piece = rem - h * pieces_per_row;
+            const int64_t src_off = ((start + t0 + t) * pool.num_kv_heads + h) * (int64_t)row_bytes + (int64_t)piece * VEC;
+            const int64_t dst_off = blk_base + ((int64_t)h * pool.block_size + t) * row_bytes + (int64_t)piece * VEC;
+            src[u] = (which ? v : k) + src_off;
+            dst[u] = (which ? pool.v_base[seg] : pool.k_base[seg]) + dst_off;
+        }
+        if (VEC == 16) {
+            uint4 x[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (on[u]) x[u] = __ldcs(reinterpret_cast<const uint4 *>(src[u]));   // read once: streaming
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (on[u]) *reinterpret_cast<uint4 *>(dst[u]) = x[u];
+        } else if (VEC == 4) {
+            uint32_t x[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (on[u]) x[u] = *reinterpret_cast<const uint32_t *>(src[u]);
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (on[u]) *reinterpret_cast<uint32_t *>(dst[u]) = x[u];
+        } else {
+            uint16_t x[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (on[u]) x[u] = *reinterpret_cast<const uint16_t *>(src[u]);
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (on[u]) *reinterpret_cast<uint16_t *>(dst[u]) = x[u];
+        }
     }
 }
 
