@@ -4,6 +4,8 @@
 
 #include <vector>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace mkv {
@@ -167,12 +169,14 @@ int mkv_swap_blocks(int device, void *stream, const mkv_pool *pool, void *k_swap
 // kept, so the copy overlaps whatever runs on the compute streams and the call costs no stream set-up.
 int mkv_slab_upload(int device, void *dst_device, size_t dst_capacity, const void *src_host, size_t bytes) {
     static cudaStream_t copy_streams[64];
+    static std::mutex copy_streams_lock;  // callers may come from different host threads
     if (device < 0 || device >= 64) return MKV_ERR_RANGE;
     if (bytes > dst_capacity) return MKV_ERR_NOSPACE;
     if (bytes == 0) return MKV_OK;
     if (!dst_device || !src_host) return MKV_ERR_NULL;
     DeviceGuard guard(device);
     if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
+    std::lock_guard<std::mutex> hold(copy_streams_lock);  // one upload per process at a time: they share PCIe anyway
     if (!copy_streams[device]) MKV_CUDA_TRY(cudaStreamCreateWithFlags(&copy_streams[device], cudaStreamNonBlocking));
     MKV_CUDA_TRY(cudaMemcpyAsync(dst_device, src_host, bytes, cudaMemcpyHostToDevice, copy_streams[device]));
     MKV_CUDA_TRY(cudaStreamSynchronize(copy_streams[device]));
