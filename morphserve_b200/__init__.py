@@ -24,9 +24,10 @@ import types
 from . import _lib  # noqa: F401  (raises ImportError if libmorphkv.so is missing)
 from . import swiftllm_c
 from .server import memory_utils
-from .worker import block_manager, infer_state
+from .worker import block_manager, infer_state, kv_model
 from .worker.block_manager import BlockManager
 from .worker.infer_state import LlamaInferState
+from .worker.kv_model import KVCacheModelState
 from .worker.kernels import block_mgmt, kvcache_mgmt, paged_attn, rotary_emb
 from .worker.kernels.kvcache_mgmt import set_fused_decode_append, store_kvcache
 from .worker.kernels.paged_attn import paged_attention, paged_attention_push
@@ -80,4 +81,5 @@ def install_as_swiftllm(overwrite: bool = True) -> None:
 
 __all__ = ["paged_attention", "paged_attention_push", "store_kvcache", "set_fused_decode_append",
            "rotary_embedding_inplace", "set_fused_decode_rope", "BlockManager", "LlamaInferState",
+           "KVCacheModelState",
            "swiftllm_c", "memory_utils", "install_as_swiftllm"]

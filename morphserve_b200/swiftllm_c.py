@@ -95,6 +95,15 @@ def swap_blocks_new_kv_combined(source_block_ids, target_block_ids, is_swap_in, 
     _swap(source_block_ids, target_block_ids, is_swap_in, pool, k_cache, k_swap, v_swap)
 
 
+def swap_blocks_chunk_list(source_block_ids, target_block_ids, is_swap_in, num_blocks_org, kv_cache_new_block_size,
+                           k_cache, v_cache, k_swap, v_swap, k_cache_new: list, v_cache_new: list):
+    """The elastic swap for callers that hold the whole chunk LISTS (as the model does, worker/model.py:75-76)
+    rather than chunk 0 and a slab stride: chunks may sit anywhere, and with a pinned swap space the ids can
+    stay on the GPU (no ``.tolist()``, no scan for the highest id).  No counterpart in the reference."""
+    pool = make_pool(k_cache, v_cache, k_cache_new, v_cache_new, int(num_blocks_org), int(kv_cache_new_block_size))
+    _swap(source_block_ids, target_block_ids, is_swap_in, pool, k_cache, k_swap, v_swap)
+
+
 def register_kv_cache_info(num_layers: int, num_kv_heads: int, block_size: int, head_dim: int) -> None:
     """csrc/src/memory_manager.cpp:57-66."""
     _state["kv_info"] = (int(num_layers), int(num_kv_heads), int(block_size), int(head_dim))
@@ -230,7 +239,7 @@ def verify_tensor_continuity(tensors) -> bool:
     return all(spans[i - 1][0] + spans[i - 1][1] == spans[i][0] for i in range(1, len(spans)))
 
 
-__all__ = ["swap_blocks", "swap_blocks_new_kv_combined", "register_kv_cache_info",
+__all__ = ["swap_blocks", "swap_blocks_new_kv_combined", "swap_blocks_chunk_list", "register_kv_cache_info",
            "register_layer_memory_org_gpu", "register_layer_memory_org_cpu", "register_layer_memory_quant",
            "register_layer_memory_tensor_map_quant", "register_layer_memory_tensor_map_org",
            "acquire_new_kvcache", "replace_layer_org2quant", "replace_layer_quant2org",

@@ -343,3 +343,90 @@ def test_layer_slab_replace_and_restore_round_trip():
     assert slab.cpu().numpy().tobytes() == org_blob.tobytes()
     for t, (name, a) in zip(back, org_np.items()):
         assert t.dtype == torch.float16 and t.cpu().numpy().tobytes() == a.tobytes(), name
+
+
+@pytest.mark.parametrize("with_chunks", [False, True])
+def test_model_level_swap_out_and_in_against_oracle(with_chunks):
+    """KVCacheModelState (the KV half of the reference's LlamaModel: worker/model.py:176-227, :468-550): sequences
+    are swapped out, others admitted, the first swapped back in - block managers, pools and swap space in lockstep
+    with the oracle's managers and its swap rule."""
+    from types import SimpleNamespace
+    from morphserve_b200 import KVCacheModelState
+    rs = np.random.RandomState(5 + with_chunks)
+    L, Hkv, bs, D = 2, 2, 16, 128
+    nb, n_cpu, max_seqs, cols = 48, 40, 12, 12
+    chunk = 8 if with_chunks else 0
+    mc = SimpleNamespace(num_layers=L, num_q_heads=4, num_kv_heads=Hkv, head_dim=D)
+    ec = SimpleNamespace(block_size=bs, num_cpu_blocks=n_cpu, max_seqs_in_block_table=max_seqs, max_blocks_per_seq=cols)
+    m = KVCacheModelState(mc, ec)
+    m.init_kvcache_and_swap(nb)
+    assert m.k_swap.is_pinned() and float(m.k_cache.abs().sum()) == 0.0
+    g_or, c_or = O.BlockManagerOracle(nb, max_seqs, cols, bs), O.BlockManagerOracle(n_cpu, max_seqs, cols, bs)
+    shapes = [(nb, L, Hkv, bs, D)]
+    if with_chunks:         # two elastic chunks, attached the way server/memory_utils.py:389-420 does it
+        for _ in range(2):
+            m.k_cache_new.append(torch.zeros((chunk, L, Hkv, bs, D), dtype=torch.float16, device="cuda"))
+            m.v_cache_new.append(torch.zeros((chunk, L, Hkv, bs, D), dtype=torch.float16, device="cuda"))
+            m.gpu_block_manager.num_blocks += chunk
+            m.gpu_block_manager.num_free_blocks += chunk
+            m.gpu_block_manager.is_block_free = torch.cat(
+                [m.gpu_block_manager.is_block_free, torch.ones(chunk, dtype=torch.bool, device="cuda")])
+            O.expand(g_or, chunk)
+            shapes.append((chunk, L, Hkv, bs, D))
+        m.kv_cache_new_block_size = chunk
+    k_or = [rs.standard_normal(sh).astype(np.float16) for sh in shapes]
+    v_or = [rs.standard_normal(sh).astype(np.float16) for sh in shapes]
+    for t, a in zip([m.k_cache] + m.k_cache_new, k_or):
+        t.copy_(H.to_dev(a))
+    for t, a in zip([m.v_cache] + m.v_cache_new, v_or):
+        t.copy_(H.to_dev(a))
+    ks_or = np.zeros((n_cpu, L, Hkv, bs, D), dtype=np.float16)
+    vs_or = np.zeros_like(ks_or)
+
+    def both_allocate(ids, lens):
+        ids, lens = np.asarray(ids, dtype=np.int32), np.asarray(lens, dtype=np.int32)
+        m.gpu_block_manager.allocate_blocks_for_seqs(H.to_dev(ids), H.to_dev(lens))
+        g_or.allocate_blocks_for_seqs(ids, lens)
+
+    def oracle_swap(ids, is_in):
+        src, dst = (c_or, g_or) if is_in else (g_or, c_or)
+        ids = np.asarray(ids, dtype=np.int32)
+        lens = src.get_num_allocated_blocks(ids) * bs
+        s_ids = src.gather_allocated_blocks_and_free(ids)
+        d_ids = dst.allocate_blocks_for_seqs(ids, lens)
+        O.swap_blocks(s_ids, d_ids, is_in, k_or, v_or, ks_or, vs_or, nb, chunk)
+
+    def check_all():
+        torch.cuda.synchronize()
+        for bm, ob in ((m.gpu_block_manager, g_or), (m.cpu_block_manager, c_or)):
+            live = ob.num_seq_allocated_blocks > 0
+            np.testing.assert_array_equal(bm.num_seq_allocated_blocks.cpu().numpy(), ob.num_seq_allocated_blocks)
+            np.testing.assert_array_equal(bm.block_table.cpu().numpy()[live], ob.block_table[live])
+            np.testing.assert_array_equal(bm.is_block_free.cpu().numpy(), ob.is_block_free)
+            assert int(bm.num_free_blocks) == int(ob.num_free_blocks)
+        for t, a in zip([m.k_cache] + m.k_cache_new + [m.v_cache] + m.v_cache_new, k_or + v_or):
+            assert t.cpu().numpy().tobytes() == a.tobytes()
+        assert m.k_swap.numpy().tobytes() == ks_or.tobytes() and m.v_swap.numpy().tobytes() == vs_or.tobytes()
+
+    if with_chunks:     # three resident sequences fill most of the original pool: the rest spills into the chunks
+        both_allocate([9, 10, 11], [192, 192, 192])
+    both_allocate([0, 1, 2, 3, 4, 5], [100, 30, 64, 60, 17, 90] if with_chunks else [100, 30, 64, 120, 17, 90])
+    if with_chunks:
+        assert int(m.gpu_block_manager.block_table[:6].max()) >= nb, "the case must reach the elastic chunks"
+    check_all()
+    m.swap_out_seqs([1, 3, 4])
+    oracle_swap([1, 3, 4], False)
+    check_all()
+    both_allocate([6, 7], [70, 33])                       # takes some of the freed blocks
+    m.swap_out_seqs([0])
+    oracle_swap([0], False)
+    m.swap_in_seqs([3, 1])
+    oracle_swap([3, 1], True)
+    check_all()
+    m.free_seqs_resources([2, 4])
+    g_or.free_blocks_for_seqs(np.array([2, 4], dtype=np.int32))
+    c_or.free_blocks_for_seqs(np.array([2, 4], dtype=np.int32))
+    m.swap_in_seqs([0])
+    oracle_swap([0], True)
+    check_all()
+    assert m.block_swap == (28 if with_chunks else 36)
