@@ -376,10 +376,9 @@ def test_model_level_swap_out_and_in_against_oracle(with_chunks):
         m.kv_cache_new_block_size = chunk
     k_or = [rs.standard_normal(sh).astype(np.float16) for sh in shapes]
     v_or = [rs.standard_normal(sh).astype(np.float16) for sh in shapes]
-    for t, a in zip([m.k_cache] + m.k_cache_new, k_or):
-        t.copy_(H.to_dev(a))
-    for t, a in zip([m.v_cache] + m.v_cache_new, v_or):
-        t.copy_(H.to_dev(a))
+    with torch.inference_mode():    # the pools are inference tensors, like the reference's (worker/model.py:176)
+        for t, a in zip([m.k_cache] + m.k_cache_new + [m.v_cache] + m.v_cache_new, k_or + v_or):
+            t.copy_(H.to_dev(a))
     ks_or = np.zeros((n_cpu, L, Hkv, bs, D), dtype=np.float16)
     vs_or = np.zeros_like(ks_or)
 
