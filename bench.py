@@ -400,11 +400,13 @@ class DecodeJob:
 # clocks
 # ----------------------------------------------------------------------------
 class ClockSampler:
-    """Samples SM clock and throttle reasons of the GPUs in use while the timed
-    region runs: a separate read-only `nvidia-smi --query-gpu ... -lms` process,
-    so that sampling does not compete with the launching thread."""
+    """Samples SM clock and throttle reasons of the GPUs in use: a separate read-only
+    `nvidia-smi --query-gpu ... -lms` process, so that sampling does not compete with the launching
+    thread.  It is started before the warm-up (the tool needs up to a few seconds to come up, longer
+    with eight GPUs) and its time-stamped samples are cut to the timed region afterwards; if the
+    region was too short to hold one, the samples of the warm-up (same load) are reported and marked."""
 
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+    FIELDS = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
     NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
@@ -413,9 +415,10 @@ class ClockSampler:
         self.indices = set(indices)
         self.proc = None
         self.text = ""
+        self.t_begin = self.t_end = None
 
-    def __enter__(self):
-        if self.indices:
+    def start(self):
+        if self.indices and self.proc is None:
             import subprocess
             try:
                 self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}",
@@ -425,7 +428,13 @@ class ClockSampler:
                 self.proc = None
         return self
 
+    def __enter__(self):            # the timed region
+        self.start()
+        self.t_begin = time.time()
+        return self
+
     def __exit__(self, *a):
+        self.t_end = time.time()
         if self.proc is not None:
             self.proc.terminate()
             try:
@@ -434,24 +443,32 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self):
-        mhz, mx, power, reasons = [], None, [], set()
+        import datetime
+        rows = []
         for ln in self.text.splitlines():
             f = [x.strip() for x in ln.split(",")]
-            if len(f) < 8 or not f[0].isdigit() or int(f[0]) not in self.indices:
+            if len(f) < 9 or not f[1].isdigit() or int(f[1]) not in self.indices:
                 continue
             try:
-                mhz.append(float(f[1]))
-                mx = float(f[2])
-                power.append(float(f[3]))
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((ts, float(f[2]), float(f[3]), float(f[4]), f[5:9]))
             except ValueError:
                 continue
-            for nm, val in zip(self.NAMES, f[4:8]):
+        inside = [r for r in rows if self.t_begin is not None and self.t_begin <= r[0] <= self.t_end]
+        window = "timed region"
+        if not inside and rows:     # region shorter than the tool's period or start-up: warm-up samples, same load
+            inside = [r for r in rows if r[0] <= (self.t_end or r[0])][-8 * max(1, len(self.indices)):]
+            window = "warm-up before the timed region (region too short for a sample)"
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        reasons = set()
+        for r in inside:
+            for nm, val in zip(self.NAMES, r[4]):
                 if val.lower().startswith("active"):
                     reasons.add(nm)
-        if not mhz:
-            return {"sm_mhz": None, "sm_max_mhz": mx, "reasons": ["unavailable"]}
-        return {"sm_mhz": statistics.median(mhz), "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(mhz), "power_w_max": max(power) if power else None}
+        return {"sm_mhz": statistics.median(r[1] for r in inside), "sm_max_mhz": inside[-1][2],
+                "reasons": sorted(reasons), "samples": len(inside), "power_w_max": max(r[3] for r in inside),
+                "window": window}
 
 
 # ----------------------------------------------------------------------------
@@ -835,6 +852,7 @@ def main():
     job = DecodeJob(w, rank, growth_tokens=2 * (K + W) + 16, device=device)
 
     # ---- leg 1: inputs resident in HBM ----------------------------------------
+    clocks = ClockSampler(list(range(world)) if rank == 0 else []).start()     # comes up during the warm-up
     step = job.step_resident
     use_graph = not args.no_cuda_graph and not base.get("head_shard")   # the captured step has no collective in it
     config["step_launch"] = "python calls"
@@ -849,7 +867,7 @@ def main():
     calls0 = dict(_lib.CALLS)
     kv_bytes = 0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(list(range(world)) if rank == 0 else []) as clocks:
+    with clocks:
         e0.record()
         for _ in range(K):
             step()
