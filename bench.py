@@ -127,6 +127,31 @@ def shard_workload(w, rank, world):
     return w
 
 
+def bind_to_gpu_numa_node(local_rank):
+    """Pin this rank to the CPUs of the NUMA node its GPU hangs off, so that the pinned host buffers it allocates
+    afterwards (first touch) and the threads that fill them are local to the GPU's PCIe root: with eight ranks
+    copying at once, buffers on the far socket are what the host-buffer leg is limited by.  Returns
+    (node, previous affinity) or (None, None) when the topology cannot be read or the CPUs are not ours to use."""
+    try:
+        p = torch.cuda.get_device_properties(local_rank)
+        bdf = f"{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+        node = int(open(f"/sys/bus/pci/devices/{bdf}/numa_node").read())
+        if node < 0:
+            return None, None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        before = os.sched_getaffinity(0)
+        cpus &= before
+        if not cpus:
+            return None, None
+        os.sched_setaffinity(0, cpus)
+        return node, before
+    except Exception:
+        return None, None
+
+
 def max_over_ranks(value, dist, device):
     """Slowest rank's time (dist is torch.distributed or None)."""
     if dist is None:
@@ -829,6 +854,8 @@ def main():
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    numa_node, cpu_affinity_before = bind_to_gpu_numa_node(local_rank)
+    config["host_numa_node"] = numa_node
     dist = None
     if world > 1:
         import torch.distributed as dist
@@ -951,6 +978,8 @@ def main():
         e2e = {"value": w["tokens_per_step"] * Ke / (e2e_ms * 1e-3), "unit": "tokens/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": Ke}
 
+    if cpu_affinity_before is not None:
+        os.sched_setaffinity(0, cpu_affinity_before)        # the CPU leg below uses every host core
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         v, info = cpu_reference_sample(base, steps=3, warmup=1)
