@@ -317,12 +317,13 @@ int mkv_block_table_set(int device, void *stream, int32_t *num_allocated, int32_
  * (worker/kernels/block_mgmt.py:49-80).  If gathered != NULL the ids are also
  * written there in batch order (int32), which replaces
  * gather_allocated_blocks_and_unset (:83-125); gathered_capacity guards it.
- * total_out (device, may be NULL) receives the number of blocks freed.
+ * total_out (device, may be NULL) receives the number of blocks freed, or, with
+ * accumulate != 0, is increased by it (a running count the host reads later).
  */
 int mkv_block_table_unset(int device, void *stream, int32_t *num_allocated, const int32_t *block_table,
                           int64_t table_stride, const int32_t *seq_ids, int batch, uint8_t *is_block_free,
                           int64_t num_blocks, int32_t *gathered, int64_t gathered_capacity,
-                          int64_t *total_out);
+                          int64_t *total_out, int accumulate);
 
 /* sum over the batch of num_allocated[seq_ids[i]] -> *total_out (device). */
 int mkv_block_table_count(int device, void *stream, const int32_t *num_allocated, const int32_t *seq_ids,

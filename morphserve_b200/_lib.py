@@ -67,7 +67,7 @@ SIGNATURES = {
     "mkv_bitmap_select": (_i, [_i, _vp, _vp, _i64, _i64, _i, _i64, _i, _vp, _vp, _vp]),
     "mkv_bitmap_scatter": (_i, [_i, _vp, _vp, _i64, _vp, _i64, _i]),
     "mkv_block_table_set": (_i, [_i, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _i]),
-    "mkv_block_table_unset": (_i, [_i, _vp, _vp, _vp, _i64, _vp, _i, _vp, _i64, _vp, _i64, _vp]),
+    "mkv_block_table_unset": (_i, [_i, _vp, _vp, _vp, _i64, _vp, _i, _vp, _i64, _vp, _i64, _vp, _i]),
     "mkv_block_table_count": (_i, [_i, _vp, _vp, _vp, _i, _vp]),
     "mkv_chunk_layout": (_i, [C.c_uint64, C.c_uint64, C.c_uint64, _i, _i, _i, _i, _i,
                               C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(_i64)]),

@@ -247,7 +247,7 @@ __global__ void __launch_bounds__(kThreads) block_table_unset_kernel(int32_t *__
                                                                    uint8_t *__restrict__ is_block_free,
                                                                    int64_t num_blocks, int32_t *__restrict__ gathered,
                                                                    int64_t gathered_capacity,
-                                                                   int64_t *__restrict__ total_out) {
+                                                                   int64_t *__restrict__ total_out, int accumulate) {
     __shared__ int warp_sums[33];
     int64_t carry = 0;
     for (int base = 0; base < batch; base += kThreads) {
@@ -271,7 +271,7 @@ __global__ void __launch_bounds__(kThreads) block_table_unset_kernel(int32_t *__
     }
     __syncthreads();  // every count was read before any is cleared (duplicate ids in a batch)
     for (int i = threadIdx.x; i < batch; i += blockDim.x) num_allocated[seq_ids[i]] = 0;
-    if (threadIdx.x == 0 && total_out) *total_out = carry;
+    if (threadIdx.x == 0 && total_out) *total_out = accumulate ? *total_out + carry : carry;
 }
 
 __global__ void __launch_bounds__(kThreads) block_table_count_kernel(const int32_t *__restrict__ num_allocated,
@@ -367,7 +367,8 @@ int mkv_block_table_set(int device, void *stream, int32_t *num_allocated, int32_
 
 int mkv_block_table_unset(int device, void *stream, int32_t *num_allocated, const int32_t *block_table,
                           int64_t table_stride, const int32_t *seq_ids, int batch, uint8_t *is_block_free,
-                          int64_t num_blocks, int32_t *gathered, int64_t gathered_capacity, int64_t *total_out) {
+                          int64_t num_blocks, int32_t *gathered, int64_t gathered_capacity, int64_t *total_out,
+                          int accumulate) {
     if (batch < 0 || table_stride < 1 || num_blocks < 0 || gathered_capacity < 0) return MKV_ERR_SHAPE;
     if (batch == 0) return MKV_OK;
     if (!num_allocated || !block_table || !seq_ids || !is_block_free) return MKV_ERR_NULL;
@@ -375,7 +376,8 @@ int mkv_block_table_unset(int device, void *stream, int32_t *num_allocated, cons
     if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
     block_table_unset_kernel<<<1, kThreads, 0, (cudaStream_t)stream>>>(num_allocated, block_table, table_stride,
                                                                       seq_ids, batch, is_block_free, num_blocks,
-                                                                      gathered, gathered_capacity, total_out);
+                                                                      gathered, gathered_capacity, total_out,
+                                                                      accumulate);
     MKV_LAUNCH_CHECK();
     return MKV_OK;
 }

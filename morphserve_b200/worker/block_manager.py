@@ -58,8 +58,8 @@ class BlockManager:
             raise RuntimeError("BlockManager keeps its tables on the GPU; no CUDA device is available")
         self.device_name = device_name
         self._nosync_pending = False
-        self._alloc_status = None       # device int64[4], see mkv_block_allocate
-        self._alloc_seen = [0, 0, 0, 0]
+        self._alloc_status = None       # device int64[5]: [0..3] see mkv_block_allocate, [4] blocks freed without sync
+        self._alloc_seen = [0, 0, 0, 0, 0]
         self._alloc_need = self._alloc_ids = None
         self.num_free_blocks = BlockCount(num_blocks)
         self.num_blocks = num_blocks
@@ -108,12 +108,26 @@ class BlockManager:
             "mkv_block_allocate")
         self._nosync_pending = True
 
+    def free_blocks_for_seqs_nosync(self, seq_ids: torch.Tensor) -> None:
+        """``free_blocks_for_seqs`` without the host round trip for the number of blocks freed
+        (worker/block_manager.py:114-119 reads it with a sum on the device and ends up with a tensor-valued
+        counter): the count is accumulated on the device and folded in by the next ``sync_counters()``."""
+        assert seq_ids.dtype == torch.int32 and seq_ids.is_contiguous()
+        self.prepare_nosync(seq_ids.shape[0])
+        dev, stream = device_and_stream(self.block_table)
+        check(lib.mkv_block_table_unset(dev, stream, self.num_seq_allocated_blocks.data_ptr(),
+                                        self.block_table.data_ptr(), self.block_table.stride(0),
+                                        seq_ids.data_ptr(), seq_ids.shape[0], self.is_block_free.data_ptr(),
+                                        self.is_block_free.shape[0], None, 0,
+                                        self._alloc_status.data_ptr() + 4 * 8, 1), "mkv_block_table_unset")
+        self._nosync_pending = True
+
     def prepare_nosync(self, batch: int) -> None:
         """Scratch of the sync-free allocate (status words, need per sequence, id list).  Called by it; call it
         yourself before capturing a CUDA graph, since a capture must not allocate from the regular pool."""
         dev = self.block_table.device
         if self._alloc_status is None:
-            self._alloc_status = torch.zeros((4,), dtype=torch.int64, device=dev)
+            self._alloc_status = torch.zeros((5,), dtype=torch.int64, device=dev)
         if self._alloc_need is None or self._alloc_need.shape[0] < batch:
             self._alloc_need = torch.empty((max(batch, 64),), dtype=torch.int32, device=dev)
         if self._alloc_ids is None or self._alloc_ids.shape[0] < self.is_block_free.shape[0]:
@@ -131,7 +145,7 @@ class BlockManager:
             return
         st = self._alloc_status.tolist()
         seen, self._alloc_seen = self._alloc_seen, st
-        self._num_free_blocks = BlockCount(self._num_free_blocks - (st[0] - seen[0]))
+        self._num_free_blocks = BlockCount(self._num_free_blocks - (st[0] - seen[0]) + (st[4] - seen[4]))
         assert st[1] == seen[1], \
             f"(On {self.device_name}) Logic error: Some sequences have more blocks already allocated than needed."
         if st[2] != seen[2]:
@@ -195,7 +209,7 @@ class BlockManager:
         check(lib.mkv_block_table_unset(dev, stream, self.num_seq_allocated_blocks.data_ptr(),
                                         self.block_table.data_ptr(), self.block_table.stride(0),
                                         seq_ids.data_ptr(), seq_ids.shape[0], self.is_block_free.data_ptr(),
-                                        self.is_block_free.shape[0], None, 0, total.data_ptr()),
+                                        self.is_block_free.shape[0], None, 0, total.data_ptr(), 0),
               "mkv_block_table_unset")
         self.num_free_blocks = BlockCount(self.num_free_blocks + int(total.item()))
 

@@ -39,7 +39,7 @@ def unset_block_table_and_num_seq_alloc_blocks(
     dev, stream = device_and_stream(block_table)
     check(lib.mkv_block_table_unset(dev, stream, num_seq_allocated_blocks.data_ptr(), block_table.data_ptr(),
                                     block_table.stride(0), seq_ids.data_ptr(), seq_ids.shape[0],
-                                    is_block_free.data_ptr(), is_block_free.shape[0], None, 0, None),
+                                    is_block_free.data_ptr(), is_block_free.shape[0], None, 0, None, 0),
           "mkv_block_table_unset")
 
 
@@ -60,5 +60,5 @@ def gather_allocated_blocks_and_unset(
     check(lib.mkv_block_table_unset(dev, stream, num_seq_allocated_blocks.data_ptr(), block_table.data_ptr(),
                                     block_table.stride(0), seq_ids.data_ptr(), seq_ids.shape[0],
                                     is_block_free.data_ptr(), is_block_free.shape[0],
-                                    gathered.data_ptr(), n, None), "mkv_block_table_unset")
+                                    gathered.data_ptr(), n, None, 0), "mkv_block_table_unset")
     return gathered

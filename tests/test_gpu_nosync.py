@@ -15,8 +15,8 @@ G = os.path.join(os.path.dirname(__file__), "golden")
 
 
 def test_nosync_allocate_follows_the_reference_trace():
-    """The 38-operation trace recorded from the reference class: every allocate goes through the sync-free
-    kernel; tables, counts, bitmap, free count and the new ids (left in the scratch list) must match."""
+    """The 38-operation trace recorded from the reference class: every allocate and every free goes through the
+    sync-free kernels; tables, counts, bitmap, free count and the new ids (left in the scratch list) must match."""
     from morphserve_b200 import BlockManager
     tr = cases.block_manager_trace()
     gold = np.load(os.path.join(G, "block_manager_trace.npz"))
@@ -27,7 +27,7 @@ def test_nosync_allocate_follows_the_reference_trace():
             n_new = len(gold[f"ret_{i}"])
             np.testing.assert_array_equal(bm._alloc_ids[:n_new].cpu().numpy(), gold[f"ret_{i}"])
         elif op == "free":
-            bm.free_blocks_for_seqs(H.to_dev(ids))
+            assert bm.free_blocks_for_seqs_nosync(H.to_dev(ids)) is None
         else:
             r = bm.gather_allocated_blocks_and_free(H.to_dev(ids))
             np.testing.assert_array_equal(r.cpu().numpy().astype(np.int64), gold[f"ret_{i}"])
