@@ -323,18 +323,24 @@ class DecodeJob:
         self.bm.nosync_replayed()
 
     def make_host_buffers(self):
-        self.hq = self.q.cpu().pin_memory()
-        self.hk = self.kn.cpu().pin_memory()
-        self.hv = self.vn.cpu().pin_memory()
+        # per layer one contiguous host record [q | k | v] and its device twin: one copy per layer brings all three
+        L, B, Hq, Hkv = self.w["L"], self.w["B"], self.w["Hq"], self.w["Hkv"]
+        nq, nk = B * Hq * D, B * Hkv * D
+        self.hqkv = torch.empty((L, nq + 2 * nk), dtype=torch.float16).pin_memory()
+        self.hqkv[:, :nq].copy_(self.q.view(L, nq))
+        self.hqkv[:, nq:nq + nk].copy_(self.kn.view(L, nk))
+        self.hqkv[:, nq + nk:].copy_(self.vn.view(L, nk))
+        self.dqkv = torch.empty((L, nq + 2 * nk), dtype=torch.float16, device=self.dev)
+        self.dq = [self.dqkv[l, :nq].view(B, Hq, D) for l in range(L)]
+        self.dk = [self.dqkv[l, nq:nq + nk].view(B, Hkv, D) for l in range(L)]
+        self.dv = [self.dqkv[l, nq + nk:].view(B, Hkv, D) for l in range(L)]
         self.ho = torch.empty(self.o.shape, dtype=torch.float16).pin_memory()
-        self.dq, self.dk, self.dv = torch.empty_like(self.q), torch.empty_like(self.kn), torch.empty_like(self.vn)
-        L = self.w["L"]
         self.h_meta = torch.empty((2, self.w["B"]), dtype=torch.int32).pin_memory()
         self.d_meta = torch.empty((2, self.w["B"]), dtype=torch.int32, device=self.dev)
         self.s_in, self.s_out = torch.cuda.Stream(self.dev), torch.cuda.Stream(self.dev)
         self.ev_in = [torch.cuda.Event() for _ in range(L)]
         self.ev_out = [torch.cuda.Event() for _ in range(L)]
-        return self.hq.nbytes + self.hk.nbytes + self.hv.nbytes + 8 * self.w["B"], self.ho.nbytes
+        return self.hqkv.nbytes + 8 * self.w["B"], self.ho.nbytes
 
     def _stage_metadata(self):
         """Sequence ids and lengths of the coming step: Python lists (as the reference's LlamaModel.forward
@@ -356,9 +362,7 @@ class DecodeJob:
 
         def copy_in(layer):
             with torch.cuda.stream(self.s_in):
-                self.dq[layer].copy_(self.hq[layer], non_blocking=True)
-                self.dk[layer].copy_(self.hk[layer], non_blocking=True)
-                self.dv[layer].copy_(self.hv[layer], non_blocking=True)
+                self.dqkv[layer].copy_(self.hqkv[layer], non_blocking=True)
                 self.ev_in[layer].record(self.s_in)
 
         copy_in(0)
@@ -378,6 +382,7 @@ class DecodeJob:
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(self.ev_out[layer])
                 self.ho[layer].copy_(self.o[layer], non_blocking=True)
+        self.bm.readback_counters_async()       # the allocation record travels to pinned memory with the step
 
     def step_host(self):
         """One step as a caller with host data makes it; it ends when the last output byte is on the host and
@@ -414,7 +419,7 @@ class DecodeJob:
         assert int(self.lens_host.max()) <= self.graph_max_len, "captured step outgrown: capture again"
         self.graph_host.replay()
         torch.cuda.current_stream().synchronize()
-        self.bm.nosync_replayed()
+        self.bm.nosync_replayed(with_readback=True)
         _ = self.bm.num_free_blocks
 
     def kv_bytes_per_layer(self):

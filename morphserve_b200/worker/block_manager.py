@@ -58,6 +58,7 @@ class BlockManager:
             raise RuntimeError("BlockManager keeps its tables on the GPU; no CUDA device is available")
         self.device_name = device_name
         self._nosync_pending = False
+        self._readback_enqueued = False
         self._alloc_status = None       # device int64[5]: [0..3] see mkv_block_allocate, [4] blocks freed without sync
         self._alloc_seen = [0, 0, 0, 0, 0]
         self._alloc_need = self._alloc_ids = None
@@ -128,22 +129,44 @@ class BlockManager:
         dev = self.block_table.device
         if self._alloc_status is None:
             self._alloc_status = torch.zeros((5,), dtype=torch.int64, device=dev)
+            self._status_host = torch.zeros((5,), dtype=torch.int64).pin_memory()
+            self._status_event = torch.cuda.Event()
+            self._readback_enqueued = False
         if self._alloc_need is None or self._alloc_need.shape[0] < batch:
             self._alloc_need = torch.empty((max(batch, 64),), dtype=torch.int32, device=dev)
         if self._alloc_ids is None or self._alloc_ids.shape[0] < self.is_block_free.shape[0]:
             self._alloc_ids = torch.empty((self.is_block_free.shape[0],), dtype=torch.int64, device=dev)
 
-    def nosync_replayed(self) -> None:
-        """Tell the manager that a captured graph containing sync-free allocations was replayed."""
+    def nosync_replayed(self, with_readback: bool = False) -> None:
+        """Tell the manager that a captured graph containing sync-free allocations was replayed (and whether the
+        graph also holds ``readback_counters_async()``, in which case the caller synchronises with the stream
+        before it reads ``num_free_blocks``)."""
         self._nosync_pending = True
+        self._readback_enqueued = with_readback
+
+    def readback_counters_async(self) -> None:
+        """Enqueue, on the current stream, the copy of the device-side record into pinned host memory.  A caller
+        that synchronises with the stream anyway (end of a step) then gets ``sync_counters()`` without another
+        round trip to the GPU; the copy can be captured in a CUDA graph."""
+        self.prepare_nosync(1)
+        self._status_host.copy_(self._alloc_status, non_blocking=True)
+        if not torch.cuda.is_current_stream_capturing():
+            self._status_event.record()
+        self._readback_enqueued = True
 
     def sync_counters(self) -> None:
-        """Fold the device-side record of the sync-free allocations into the host counters (one
-        synchronisation) and raise what the reference would have raised at allocation time."""
+        """Fold the device-side record of the sync-free allocations and frees into the host counters and raise
+        what the reference would have raised at allocation time.  One wait for the GPU - none if
+        ``readback_counters_async()`` ran after the last sync-free call and the stream has been synchronised."""
         self._nosync_pending = False
         if self._alloc_status is None:
             return
-        st = self._alloc_status.tolist()
+        if not self._readback_enqueued:
+            self._status_host.copy_(self._alloc_status, non_blocking=True)
+            self._status_event.record()
+        self._status_event.synchronize()    # returns at once when the stream was synchronised after the copy
+        self._readback_enqueued = False
+        st = self._status_host.tolist()
         seen, self._alloc_seen = self._alloc_seen, st
         self._num_free_blocks = BlockCount(self._num_free_blocks - (st[0] - seen[0]) + (st[4] - seen[4]))
         assert st[1] == seen[1], \
