@@ -61,3 +61,27 @@ def run_decode_step(d):
     torch.cuda.synchronize()
     return (o.cpu().numpy().reshape(d["B"], d["Hq"], d["D"]),
             [p.cpu().numpy() for p in d["k_pools_t"]], [p.cpu().numpy() for p in d["v_pools_t"]])
+
+
+def plan_rule(lens, num_kv_heads, batch_cap_items, sm_count, split_balance=1.5, block_size=16):
+    """What the decode plan kernel must decide for a batch (restated on the host for the tests): chunk size in
+    blocks, number of (sequence, chunk) items, number of partial rows.  Candidates 4,6,8,12,...; the smallest one
+    whose item count fits the cap, raised to the largest one not above split_balance x the mean number of blocks per
+    worker warp; a remainder of up to a quarter chunk stays with the piece before it."""
+    nblk = [(int(n) + block_size - 1) // block_size for n in lens if n > 0]
+    cand = [(6 << (k >> 1)) if k & 1 else (4 << (k >> 1)) for k in range(40)]
+    k = 0
+    while k < 39 and sum(-(-n // cand[k]) for n in nblk) > batch_cap_items:
+        k += 1
+    keep_whole = np.float32(np.float32(split_balance * num_kv_heads / (sm_count * 8.0)) * np.float32(sum(nblk)))
+    while k < 39 and np.float32(cand[k + 1]) <= keep_whole:
+        k += 1
+    chunk = cand[k]
+    items = rows = 0
+    for n in nblk:
+        ns = -(-n // chunk)
+        if ns > 1 and n - (ns - 1) * chunk <= chunk // 4:
+            ns -= 1
+        items += ns
+        rows += ns if ns > 1 else 0
+    return chunk, items, rows

@@ -358,3 +358,36 @@ def test_push_variant_writes_the_column_slice_of_every_destination():
     for o in outs:
         assert torch.equal(o[:, first_head * 128:(first_head + 8) * 128], ref)
         assert (o[:, : first_head * 128] == 7.0).all() and (o[:, (first_head + 8) * 128:] == 7.0).all()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_plan_kernel_follows_the_stated_rule(seed):
+    """Chunk size, item count and partial-row count in the workspace header against the rule restated on the host
+    (tests/helpers.py::plan_rule), for batches from 1 to 3000 sequences and several split_balance settings."""
+    from morphserve_b200._lib import lib, check
+    from morphserve_b200.worker.kernels._common import attn_workspace
+    rs = np.random.RandomState(77 + seed)
+    B = int(rs.choice([1, 7, 64, 256, 900, 3000]))
+    Hkv = int(rs.choice([1, 2, 8, 32]))
+    Hq = Hkv * int(rs.choice([1, 4, 8]))
+    max_len = int(rs.choice([40, 700, 1536, 30000])) if B <= 256 else int(rs.choice([40, 700]))
+    lens = rs.randint(1, max_len + 1, size=B).astype(np.int32)
+    balance = float(rs.choice([0.0, 1.0, 1.5, 4.0]))
+    max_blocks = (int(lens.max()) + 15) // 16
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    check(lib.mkv_attn_configure(-1, -1, -1.0, balance, -1), "mkv_attn_configure")
+    try:
+        ws = attn_workspace(0, B, Hq, Hkv, 128, max_blocks)
+        lens_t, ids_t = H.to_dev(lens), torch.arange(B, dtype=torch.int32, device="cuda")
+        stream = torch.cuda.current_stream().cuda_stream
+        check(lib.mkv_attn_plan(0, stream, ws.tensor.data_ptr(), ws.nbytes, lens_t.data_ptr(), ids_t.data_ptr(), B,
+                                Hq, Hkv, 128, 16, max_blocks), "mkv_attn_plan")
+        ws.generation += 1
+        torch.cuda.synchronize()
+        hdr = ws.tensor[:64].cpu().numpy().view(np.int32)
+    finally:
+        check(lib.mkv_attn_configure(-1, -1, -1.0, 1.5, -1), "mkv_attn_configure")
+    magic, batch, n_items, chunk, _, _, flags, n_rows, cap = [int(x) for x in hdr[:9]]
+    assert magic == 0x4d4b5631 and batch == B and flags == 0
+    exp_chunk, exp_items, exp_rows = H.plan_rule(lens, Hkv, cap, sms, balance)
+    assert (chunk, n_items, n_rows) == (exp_chunk, exp_items, exp_rows)
