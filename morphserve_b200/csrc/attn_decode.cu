@@ -751,6 +751,17 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
                     sc[jj][e] = (tok < valid) ? v : kNegBig;
                 }
             }
+            if (valid < kBS) {  // warp-uniform: the last tile of the sequence
+                // Slots behind the sequence's end may hold anything (a pool that was never zeroed, a recycled
+                // block).  Their P is exactly 0, but 0 x NaN would still poison the accumulators - the reference
+                // zero-fills its pools for that reason (worker/model.py:187-188) - so the staged V rows are cleared.
+                for (int i = lane; i < (kBS - valid) * 16; i += 32) {
+                    const uint32_t at = st + kTileBytes + tile_off<TMA>(valid + (i >> 4), i & 15);
+                    asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};\n" ::"r"(at), "r"(0u) : "memory");
+                }
+                if (TMA) asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                __syncwarp();
+            }
             float mx0 = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
             float mx1 = HI ? fmaxf(fmaxf(sc[0][2], sc[0][3]), fmaxf(sc[1][2], sc[1][3])) : kNegBig;
             mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));

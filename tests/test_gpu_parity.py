@@ -286,6 +286,28 @@ def test_random_batches_fast_path_against_plain_kernel(seed):
     assert read_attn_error_flags(0) == 0
 
 
+def test_slots_behind_the_sequence_end_may_hold_nan():
+    """A pool that was never zeroed (or recycled blocks): every slot that no sequence owns holds NaN.  The reference
+    zero-fills its pools to survive this (worker/model.py:187-188); here the result must not depend on those slots."""
+    rs = np.random.RandomState(12)
+    lens = np.array([1, 5, 16, 17, 31, 100, 333, 1000, 47])
+    nb = int(((lens + 15) // 16).sum()) + 9
+    c = cases.build_decode_case(seed=31, B=len(lens), Hq=8, Hkv=2, D=128, bs=16, L=2, layer=1, num_blocks_org=nb,
+                                dtype=np.float16, lens=lens)
+    owned = np.zeros((nb, 16), dtype=bool)
+    for b, n in enumerate(lens):
+        row = c["block_table"][c["seq_ids"][b]]
+        for t in range(n):
+            owned[row[t // 16], t % 16] = True
+    for pool in (c["k_pools"][0], c["v_pools"][0]):
+        pool[~owned[:, None, None, :].repeat(2, 1).repeat(2, 2)] = np.nan      # [nb, L, Hkv, 16, D]
+    o, kp, vp = H.run_decode_step(H.device_case(c))
+    assert np.isfinite(o).all()
+    ex = O.paged_attention_exact(c["q"], kp, vp, c["block_table"], c["seq_ids"], c["seq_lens"], 1, c["scale"],
+                                 c["num_blocks_org"], 0)
+    _close(o, ex)
+
+
 def test_every_length_across_block_and_chunk_edges():
     """lens 1..160 in one batch: every len % 16, single- and multi-block sequences."""
     lens = np.arange(1, 161)
