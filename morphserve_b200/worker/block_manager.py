@@ -127,6 +127,13 @@ class BlockManager:
         """Scratch of the sync-free allocate (status words, need per sequence, id list).  Called by it; call it
         yourself before capturing a CUDA graph, since a capture must not allocate from the regular pool."""
         dev = self.block_table.device
+        if (self._alloc_status is not None and self._alloc_need is not None and self._alloc_need.shape[0] >= batch
+                and self._alloc_ids is not None and self._alloc_ids.shape[0] >= self.is_block_free.shape[0]):
+            return
+        with torch.inference_mode(False):   # plain tensors: they are updated from inside and outside inference mode
+            self._prepare_nosync_buffers(batch, dev)
+
+    def _prepare_nosync_buffers(self, batch, dev) -> None:
         if self._alloc_status is None:
             self._alloc_status = torch.zeros((5,), dtype=torch.int64, device=dev)
             self._status_host = torch.zeros((5,), dtype=torch.int64).pin_memory()

@@ -12,8 +12,11 @@ from __future__ import annotations
 
 import torch
 
+import numpy as np
+
 from .. import swiftllm_c
 from .block_manager import BlockManager
+from .infer_state import LlamaInferState, seq_block_size_heuristic
 
 
 class KVCacheModelState:
@@ -28,6 +31,94 @@ class KVCacheModelState:
         self.kv_cache_new_block_size = 0
         self.block_swap = 0                              # blocks swapped so far (worker/model.py:479)
         self.gpu_block_manager = self.cpu_block_manager = None
+        self._cos_cached = self._sin_cached = None
+        self._staging = [None, None]                     # pinned int32 buffers for the per-step metadata
+        self._staging_done = [None, None]
+        self._staging_turn = 0
+
+    @torch.inference_mode()
+    def _init_to_get_rotary(self):
+        """cos / sin tables, fp32 angles rounded to fp16 (worker/model.py:229-241)."""
+        mc = self.model_config
+        scaling = getattr(mc, "rope_scaling", 1) or 1
+        base = getattr(mc, "rope_theta", 10000.0)
+        max_seq_len = getattr(mc, "max_position_embeddings", 4096) * scaling
+        inv_freq = 1.0 / (base ** (torch.arange(0, mc.head_dim, 2, device="cuda", dtype=torch.float32) / mc.head_dim))
+        t = torch.arange(max_seq_len + 128, device="cuda", dtype=torch.float32) / scaling
+        freqs = torch.outer(t, inv_freq)
+        self._cos_cached = torch.cos(freqs).to(torch.float16)
+        self._sin_cached = torch.sin(freqs).to(torch.float16)
+
+    def _stage(self, n: int):
+        """A pinned int32 buffer of at least n entries whose previous upload has finished (two take turns)."""
+        i = self._staging_turn = self._staging_turn ^ 1
+        if self._staging[i] is None or self._staging[i].shape[0] < n:
+            self._staging[i] = torch.empty((max(n, 4096),), dtype=torch.int32).pin_memory()
+            self._staging_done[i] = torch.cuda.Event()
+        else:
+            self._staging_done[i].synchronize()
+        return self._staging[i], self._staging_done[i]
+
+    @torch.inference_mode()
+    def prepare_step(self, input_ids_list, seq_ids_list, decoding_seq_lens_list, ignore_kvcache: bool = False,
+                     sync_free: bool = False) -> LlamaInferState:
+        """The part of the reference's ``forward`` that turns its Python lists into the step's metadata and block
+        allocation (worker/model.py:318-436): prefill sequences come first in ``input_ids_list``, decoding ones
+        after them with one token each.  Returns the LlamaInferState the kernels of this package take.
+
+        Underneath, all integer metadata (sequence ids, lengths, prompt start offsets, token positions) is laid out
+        in ONE pinned buffer on the host and uploaded with ONE asynchronous copy; the reference builds six small
+        tensors from lists and derives the rest with cumsum / arange / cat kernels.  ``sync_free`` takes the
+        allocation path without a host round trip (errors then surface with the next ``num_free_blocks`` read)."""
+        mc = self.model_config
+        n_dec = len(decoding_seq_lens_list)
+        n_pre = len(input_ids_list) - n_dec
+        prompt_lens = [len(x) for x in input_ids_list[:n_pre]]
+        batch = n_pre + n_dec
+        n_pre_tok = sum(prompt_lens)
+        n_tok = n_pre_tok + n_dec
+        # [ seq_ids | seq_lengths | prompt starts + end | token positions ]
+        total = 2 * batch + (n_pre + 1) + n_tok
+        host, done = self._stage(total)
+        h = host.numpy()
+        h[:batch] = seq_ids_list
+        h[batch:batch + n_pre] = prompt_lens
+        h[batch + n_pre:2 * batch] = decoding_seq_lens_list
+        o_start = 2 * batch
+        if n_pre:
+            h[o_start:o_start + n_pre] = np.cumsum(prompt_lens) - np.asarray(prompt_lens)
+        h[o_start + n_pre] = n_tok
+        o_pos = o_start + n_pre + 1
+        p = o_pos
+        for n in prompt_lens:
+            h[p:p + n] = np.arange(n, dtype=np.int32)
+            p += n
+        h[p:p + n_dec] = np.asarray(decoding_seq_lens_list, dtype=np.int32) - 1
+        dev = torch.empty((total,), dtype=torch.int32, device="cuda")
+        dev.copy_(host[:total], non_blocking=True)
+        done.record()
+        seq_ids, seq_lengths = dev[:batch], dev[batch:2 * batch]
+        starts_with_end = dev[o_start:o_start + n_pre + 1]
+        positions = dev[o_pos:o_pos + n_tok]
+        if not ignore_kvcache:
+            if sync_free:
+                self.gpu_block_manager.allocate_blocks_for_seqs_nosync(seq_ids, seq_lengths)
+            else:
+                self.gpu_block_manager.allocate_blocks_for_seqs(seq_ids, seq_lengths)
+        if self._cos_cached is None:
+            self._init_to_get_rotary()
+        seq_block_size, num_seq_blocks = seq_block_size_heuristic(mc.num_kv_heads, decoding_seq_lens_list)
+        return LlamaInferState(
+            batch_size=batch, num_tokens=n_tok, seq_ids=seq_ids, softmax_scale=mc.head_dim ** -0.5,
+            num_prefill_seqs=n_pre, num_prefill_tokens=n_pre_tok, prefill_seq_start_locs=starts_with_end[:n_pre],
+            prefill_seq_start_locs_with_end=starts_with_end, prefill_seq_lens=seq_lengths[:n_pre],
+            max_prefill_len=max(prompt_lens, default=0), num_decoding_seqs=n_dec, decoding_seq_lens=seq_lengths[n_pre:],
+            max_decoding_len=max(decoding_seq_lens_list, default=0), seq_block_size=seq_block_size,
+            num_seq_blocks=num_seq_blocks,
+            num_blocks_org=self.gpu_block_manager.num_blocks_org if self.gpu_block_manager else None,
+            kv_cache_new_block_size=self.kv_cache_new_block_size, org_layer_param_size=self.org_layer_param_size,
+            position_cos=self._cos_cached[positions], position_sin=self._sin_cached[positions],
+            ignore_kvcache=ignore_kvcache)
 
     @torch.inference_mode()
     def init_kvcache_and_swap(self, num_blocks: int):

@@ -23,6 +23,31 @@ LOG2E = 1.442695040888963  # worker/kernels/paged_attn.py:837
 
 
 # --------------------------------------------------------------------------
+# per-step metadata (worker/model.py:318-436)
+# --------------------------------------------------------------------------
+def infer_state_fields(prompt_lens: Sequence[int], decoding_seq_lens: Sequence[int], num_kv_heads: int,
+                       head_dim: int) -> dict:
+    """The integer fields the reference's forward() derives from its Python lists before it builds the
+    LlamaInferState: prefill sequences first, decoding sequences after them (worker/model.py:318-352), token
+    positions 0..len-1 for prompts and len-1 for decoding sequences (:354-372), the split size (:397-402, :426)."""
+    prompt_lens = [int(x) for x in prompt_lens]
+    dec = [int(x) for x in decoding_seq_lens]
+    num_tokens = sum(prompt_lens) + len(dec)
+    starts = np.cumsum(prompt_lens) - np.asarray(prompt_lens) if prompt_lens else np.zeros(0)
+    positions = np.concatenate([np.arange(n) for n in prompt_lens] + [np.asarray(dec, dtype=np.int64) - 1]) \
+        if (prompt_lens or dec) else np.zeros(0, dtype=np.int64)
+    sbs, nsb = seq_block_size_heuristic(num_kv_heads, dec)
+    return dict(batch_size=len(prompt_lens) + len(dec), num_tokens=num_tokens, num_prefill_seqs=len(prompt_lens),
+                num_prefill_tokens=sum(prompt_lens), prefill_seq_start_locs=starts.astype(np.int32),
+                prefill_seq_start_locs_with_end=np.concatenate([starts, [num_tokens]]).astype(np.int32),
+                prefill_seq_lens=np.asarray(prompt_lens, dtype=np.int32), max_prefill_len=max(prompt_lens, default=0),
+                num_decoding_seqs=len(dec), decoding_seq_lens=np.asarray(dec, dtype=np.int32),
+                max_decoding_len=max(dec, default=0), seq_block_size=sbs, num_seq_blocks=nsb,
+                seq_lengths=np.asarray(prompt_lens + dec, dtype=np.int32), position_indices=positions.astype(np.int64),
+                softmax_scale=float(head_dim) ** -0.5)
+
+
+# --------------------------------------------------------------------------
 # rotary embedding (the step before the append: worker/layers/transformer_layer.py:93-98)
 # --------------------------------------------------------------------------
 def rotary_embedding(q: np.ndarray, k: np.ndarray, cos: np.ndarray, sin: np.ndarray):

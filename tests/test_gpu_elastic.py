@@ -9,6 +9,7 @@ import torch
 
 from oracle import kv_oracle as O
 from tests import helpers as H
+from tests.golden import cases
 
 pytestmark = pytest.mark.gpu
 
@@ -429,3 +430,74 @@ def test_model_level_swap_out_and_in_against_oracle(with_chunks):
     oracle_swap([0], True)
     check_all()
     assert m.block_swap == (28 if with_chunks else 36)
+
+
+@pytest.mark.parametrize("sync_free", [False, True])
+def test_prepare_step_builds_the_reference_metadata(sync_free):
+    """KVCacheModelState.prepare_step against the restated list-to-tensor logic of the reference's forward()
+    (worker/model.py:318-436): every field of the infer state, the cos/sin rows, and the block allocation, over a
+    prefill-only step, a mixed step and decode-only steps."""
+    from types import SimpleNamespace
+    from morphserve_b200 import KVCacheModelState
+    rs = np.random.RandomState(9)
+    mc = SimpleNamespace(num_layers=2, num_q_heads=8, num_kv_heads=2, head_dim=128, rope_theta=10000.0,
+                         rope_scaling=1, max_position_embeddings=2048)
+    ec = SimpleNamespace(block_size=16, num_cpu_blocks=8, max_seqs_in_block_table=16, max_blocks_per_seq=40)
+    m = KVCacheModelState(mc, ec)
+    m.init_kvcache_and_swap(400)
+    ob = O.BlockManagerOracle(400, 16, 40, 16)
+    cos_tab, sin_tab = cases.rope_tables(np.arange(2048 + 128), 128)
+    lens = {}
+
+    def step(prompts, dec_ids):
+        """prompts: {seq id: prompt length}; dec_ids: running sequences that generate one more token."""
+        for s, n in prompts.items():
+            lens[s] = n
+        for s in dec_ids:
+            lens[s] += 1
+        input_ids = [list(rs.randint(0, 1000, size=n)) for n in prompts.values()] + [[7] for _ in dec_ids]
+        seq_ids = list(prompts) + list(dec_ids)
+        dec_lens = [lens[s] for s in dec_ids]
+        st = m.prepare_step(input_ids, seq_ids, dec_lens, sync_free=sync_free)
+        f = O.infer_state_fields(list(prompts.values()), dec_lens, mc.num_kv_heads, mc.head_dim)
+        ob.allocate_blocks_for_seqs(np.asarray(seq_ids, dtype=np.int32), f["seq_lengths"])
+        torch.cuda.synchronize()
+        for name in ("batch_size", "num_tokens", "num_prefill_seqs", "num_prefill_tokens", "max_prefill_len",
+                     "num_decoding_seqs", "max_decoding_len", "seq_block_size", "num_seq_blocks", "softmax_scale"):
+            assert getattr(st, name) == f[name], name
+        for name in ("prefill_seq_start_locs", "prefill_seq_start_locs_with_end", "prefill_seq_lens", "decoding_seq_lens"):
+            got = getattr(st, name)
+            assert got.dtype == torch.int32 and got.is_cuda
+            np.testing.assert_array_equal(got.cpu().numpy(), f[name], err_msg=name)
+        np.testing.assert_array_equal(st.seq_ids.cpu().numpy(), np.asarray(seq_ids, dtype=np.int32))
+        # the rows are those of the model's tables at the tokens' positions; the tables are the reference's formula
+        # (fp32 angles -> fp16), equal to a numpy evaluation up to the last bit of the angle
+        for got, table, want in ((st.position_cos, m._cos_cached, cos_tab), (st.position_sin, m._sin_cached, sin_tab)):
+            assert got.cpu().numpy().tobytes() == table.cpu().numpy()[f["position_indices"]].tobytes()
+            np.testing.assert_allclose(table.cpu().numpy().astype(np.float64), want.astype(np.float64), atol=2e-3)
+        assert st.num_blocks_org == 400 and st.ignore_kvcache is False
+        bm = m.gpu_block_manager
+        assert int(bm.num_free_blocks) == int(ob.num_free_blocks)
+        np.testing.assert_array_equal(bm.block_table.cpu().numpy(), ob.block_table)
+        np.testing.assert_array_equal(bm.num_seq_allocated_blocks.cpu().numpy(), ob.num_seq_allocated_blocks)
+        np.testing.assert_array_equal(bm.is_block_free.cpu().numpy(), ob.is_block_free)
+        return st
+
+    step({3: 70, 5: 16, 0: 1}, [])                       # prefill only
+    step({9: 33}, [3, 5, 0])                             # mixed
+    for _ in range(3):
+        step({}, [3, 5, 0, 9])                           # decode only
+    st = step({11: 200, 2: 15}, [9, 3])
+    # the state drives the kernels: rotary -> store -> attention of the mixed step run without error
+    import morphserve_b200 as mk
+    T = st.num_tokens
+    q = torch.randn((T, 8, 128), dtype=torch.float16, device="cuda")
+    k = torch.randn((T, 2, 128), dtype=torch.float16, device="cuda")
+    v = torch.randn((T, 2, 128), dtype=torch.float16, device="cuda")
+    mk.rotary_embedding_inplace(q, k, st)
+    mk.store_kvcache(k, v, m.k_cache, m.v_cache, [], [], m.gpu_block_manager.block_table, mc, ec, st, 1)
+    o = torch.zeros((st.num_decoding_seqs, 8 * 128), dtype=torch.float16, device="cuda")
+    mk.paged_attention(q[st.num_prefill_tokens:], m.k_cache, m.v_cache, [], [], m.gpu_block_manager.block_table, mc, ec,
+                       st, 1, o)
+    torch.cuda.synchronize()
+    assert bool(torch.isfinite(o).all())
