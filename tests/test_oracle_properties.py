@@ -115,3 +115,17 @@ def test_first_fit_allocation_is_ascending_and_lowest(seed):
         assert np.array_equal(new, free_before[: want - have])
         assert np.array_equal(bm.block_table[s, have:want], new.astype(np.int32))
     assert int(bm.is_block_free.sum()) == bm.num_free_blocks
+
+
+def test_infer_state_fields_known_answer():
+    """worker/model.py:318-436 on a hand-made step: prompts of 3 and 2 tokens, one decoding sequence at length 5."""
+    f = O.infer_state_fields([3, 2], [5], num_kv_heads=8, head_dim=128)
+    assert (f["batch_size"], f["num_tokens"], f["num_prefill_seqs"], f["num_prefill_tokens"]) == (3, 6, 2, 5)
+    assert f["prefill_seq_start_locs"].tolist() == [0, 3]
+    assert f["prefill_seq_start_locs_with_end"].tolist() == [0, 3, 6]
+    assert f["position_indices"].tolist() == [0, 1, 2, 0, 1, 4]
+    assert f["seq_lengths"].tolist() == [3, 2, 5] and f["max_prefill_len"] == 3 and f["max_decoding_len"] == 5
+    assert (f["seq_block_size"], f["num_seq_blocks"]) == (64, 1) and f["softmax_scale"] == 128 ** -0.5
+    g = O.infer_state_fields([], [700, 20], num_kv_heads=8, head_dim=128)
+    assert g["prefill_seq_start_locs_with_end"].tolist() == [2] and g["position_indices"].tolist() == [699, 19]
+    assert g["num_prefill_tokens"] == 0 and g["max_prefill_len"] == 0
