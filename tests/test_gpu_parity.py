@@ -413,3 +413,45 @@ def test_plan_kernel_follows_the_stated_rule(seed):
     assert magic == 0x4d4b5631 and batch == B and flags == 0
     exp_chunk, exp_items, exp_rows = H.plan_rule(lens, Hkv, cap, sms, balance)
     assert (chunk, n_items, n_rows) == (exp_chunk, exp_items, exp_rows)
+
+
+def test_launch_without_a_matching_plan_touches_nothing():
+    """The decode kernel checks the workspace header before anything else: a plan made for another batch size
+    (or none at all) makes it set bit 1 of the error word and return; `o` and the pool stay as they were.  A later
+    call with a fresh plan works."""
+    from morphserve_b200._lib import lib, check
+    from morphserve_b200.worker.kernels._common import attn_workspace, make_pool, read_attn_error_flags
+    lens = np.array([40, 17, 300, 5])
+    c = cases.build_decode_case(seed=8, B=4, Hq=8, Hkv=2, D=128, bs=16, L=1, layer=0, num_blocks_org=40,
+                                dtype=np.float16, lens=lens)
+    d = H.device_case(c)
+    bt = d["block_table_t"]
+    pool = make_pool(d["k_pools_t"][0], d["v_pools_t"][0], [], [], 40, 0)
+    ws = attn_workspace(0, 4, 8, 2, 128, bt.shape[1])
+    stream = torch.cuda.current_stream().cuda_stream
+    # a plan for the first three sequences only
+    check(lib.mkv_attn_plan(0, stream, ws.tensor.data_ptr(), ws.nbytes, d["seq_lens_t"].data_ptr(),
+                            d["seq_ids_t"].data_ptr(), 3, 8, 2, 128, 16, bt.shape[1]), "mkv_attn_plan")
+    ws.generation += 1
+    o = torch.full((4, 8 * 128), 7.0, dtype=torch.float16, device="cuda")
+    k_before = d["k_pools_t"][0].clone()
+
+    def attend():
+        check(lib.mkv_paged_attention_decode_append(
+            0, stream, d["q_t"].data_ptr(), o.data_ptr(), d["k_new_t"].data_ptr(), d["v_new_t"].data_ptr(), pool,
+            bt.data_ptr(), bt.stride(0), d["seq_ids_t"].data_ptr(), d["seq_lens_t"].data_ptr(), 4, 8, 0,
+            float(c["scale"]), bt.shape[1], ws.tensor.data_ptr(), ws.nbytes), "mkv_paged_attention_decode_append")
+        torch.cuda.synchronize()
+
+    attend()
+    assert read_attn_error_flags(0) & 2
+    assert bool((o == 7.0).all()) and torch.equal(d["k_pools_t"][0], k_before)
+    check(lib.mkv_attn_plan(0, stream, ws.tensor.data_ptr(), ws.nbytes, d["seq_lens_t"].data_ptr(),
+                            d["seq_ids_t"].data_ptr(), 4, 8, 2, 128, 16, bt.shape[1]), "mkv_attn_plan")
+    ws.generation += 1
+    attend()
+    assert read_attn_error_flags(0) == 0
+    kpo, vpo = [p.copy() for p in c["k_pools"]], [p.copy() for p in c["v_pools"]]
+    O.store_kvcache_decode(c["k_new"], c["v_new"], kpo, vpo, c["block_table"], c["seq_ids"], c["seq_lens"], 0, 40, 0)
+    ex = O.paged_attention_exact(c["q"], kpo, vpo, c["block_table"], c["seq_ids"], c["seq_lens"], 0, c["scale"], 40, 0)
+    _close(o.cpu().numpy().reshape(ex.shape), ex)
