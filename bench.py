@@ -313,12 +313,16 @@ class DecodeJob:
             self.bm.allocate_blocks_for_seqs_nosync(self.seq_ids, self.lens_dev)
             self.layers(st, self.q, self.kn, self.vn, self.o)
         self.graph_launches = sum(_lib.CALLS.values()) - calls0      # library kernels per replay
+        self.graph_generation = self.bm.resize_generation
         assert attn_workspace(dev, w["B"], w["Hq"], w["Hkv"], D, max_blocks).tensor.data_ptr() == self.graph_ws_ptr
 
     def step_graph(self):
         """One decode step = one replay of the captured graph."""
         self.lens_host += 1
         assert int(self.lens_host.max()) <= self.graph_max_len, "captured step outgrown: capture again"
+        # an elastic expand / release moves the free bitmap and changes the pool's segments: the graph holds the
+        # old addresses and must be captured again
+        assert self.bm.resize_generation == self.graph_generation, "pool resized since the capture: capture again"
         self.graph.replay()
         self.bm.nosync_replayed()
 
@@ -412,11 +416,13 @@ class DecodeJob:
             self._enqueue_host_step(main, max_len=self.graph_max_len)
             main.wait_stream(self.s_in)             # join
             main.wait_stream(self.s_out)
+        self.graph_generation = self.bm.resize_generation
 
     def step_host_graph(self):
         """The host-data step as one graph launch: stage the metadata, replay, wait for the outputs."""
         self._stage_metadata()
         assert int(self.lens_host.max()) <= self.graph_max_len, "captured step outgrown: capture again"
+        assert self.bm.resize_generation == self.graph_generation, "pool resized since the capture: capture again"
         self.graph_host.replay()
         torch.cuda.current_stream().synchronize()
         self.bm.nosync_replayed(with_readback=True)

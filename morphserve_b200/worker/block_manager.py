@@ -7,8 +7,8 @@ Same constructor, methods, exceptions and public mutable attributes
 resize code replaces ``is_block_free`` and bumps the counters from outside).
 Allocation is first-fit in ascending block id like the reference's
 ``torch.nonzero(is_block_free)[:n]`` (:75), done by one CUDA kernel without the
-nonzero pass; an allocate costs one host synchronisation (the size of the
-returned tensor is data dependent) instead of the reference's three.
+nonzero pass; an allocate is one launch and one host synchronisation (the size
+of the returned tensor is data dependent) instead of the reference's three.
 
 ``allocate_blocks_for_seqs_nosync`` is the same allocation as one launch with
 no host round trip at all (nothing is returned; errors and the free-block
@@ -21,8 +21,7 @@ import torch
 
 from .._lib import check, lib
 from .kernels._common import device_and_stream
-from .kernels.block_mgmt import (gather_allocated_blocks_and_unset,
-                                 set_block_table_and_num_seq_alloc_blocks)
+from .kernels.block_mgmt import gather_allocated_blocks_and_unset
 
 
 class BlockCount(int):
@@ -57,6 +56,7 @@ class BlockManager:
         if not torch.cuda.is_available():
             raise RuntimeError("BlockManager keeps its tables on the GPU; no CUDA device is available")
         self.device_name = device_name
+        self.resize_generation = 0      # bumped whenever ``is_block_free`` is replaced (elastic expand / release)
         self._nosync_pending = False
         self._readback_enqueued = False
         self._alloc_status = None       # device int64[5]: [0..3] see mkv_block_allocate, [4] blocks freed without sync
@@ -76,6 +76,19 @@ class BlockManager:
                                       dtype=torch.int32, device="cuda")
         # block_id |-> free?
         self.is_block_free = torch.ones((num_blocks,), dtype=torch.bool, device="cuda")
+
+    # ``is_block_free`` stays an attribute that outside code REPLACES: the elastic resize assigns a longer or a
+    # shorter tensor (server/memory_utils.py:416-417, :650).  Every replacement moves the bitmap to a new address
+    # and changes the pool's size, which is what anything that baked the old address in - a captured CUDA graph of
+    # the decode step - has to notice: it compares ``resize_generation`` with the value it saw at capture.
+    @property
+    def is_block_free(self):
+        return self._is_block_free
+
+    @is_block_free.setter
+    def is_block_free(self, value):
+        self._is_block_free = value
+        self.resize_generation += 1
 
     # ``num_free_blocks`` stays an attribute that outside code reads and assigns (the elastic resize does
     # ``+= n`` / ``-= n``); reading it first folds in what sync-free allocations did on the GPU.
@@ -108,6 +121,7 @@ class BlockManager:
             self._alloc_ids.data_ptr(), self._alloc_ids.shape[0], self._alloc_status.data_ptr()),
             "mkv_block_allocate")
         self._nosync_pending = True
+        self._readback_enqueued = False     # a snapshot taken before this call no longer covers it
 
     def free_blocks_for_seqs_nosync(self, seq_ids: torch.Tensor) -> None:
         """``free_blocks_for_seqs`` without the host round trip for the number of blocks freed
@@ -122,6 +136,7 @@ class BlockManager:
                                         self.is_block_free.shape[0], None, 0,
                                         self._alloc_status.data_ptr() + 4 * 8, 1), "mkv_block_table_unset")
         self._nosync_pending = True
+        self._readback_enqueued = False
 
     def prepare_nosync(self, batch: int) -> None:
         """Scratch of the sync-free allocate (status words, need per sequence, id list).  Called by it; call it
@@ -176,13 +191,21 @@ class BlockManager:
         st = self._status_host.tolist()
         seen, self._alloc_seen = self._alloc_seen, st
         self._num_free_blocks = BlockCount(self._num_free_blocks - (st[0] - seen[0]) + (st[4] - seen[4]))
-        assert st[1] == seen[1], \
-            f"(On {self.device_name}) Logic error: Some sequences have more blocks already allocated than needed."
+        # every condition recorded since the last look is reported, not only the first one
+        problems = []
         if st[2] != seen[2]:
-            raise RuntimeError(f"No enough free blocks available on {self.device_name} ({self.num_blocks} in total, "
-                               f"{st[2] - seen[2]} short)")
+            problems.append(f"No enough free blocks available on {self.device_name} ({self.num_blocks} in total, "
+                            f"{st[2] - seen[2]} short)")
         if st[3] != seen[3]:
-            raise RuntimeError(f"(On {self.device_name}) a sequence needs more blocks than a block-table row holds")
+            problems.append(f"(On {self.device_name}) a sequence needs more blocks than a block-table row holds")
+        if st[1] != seen[1]:
+            shrink = (f"(On {self.device_name}) Logic error: Some sequences have more blocks already allocated "
+                      f"than needed.")
+            if problems:
+                raise RuntimeError("; ".join(problems + [shrink]))
+            raise AssertionError(shrink)
+        if problems:
+            raise RuntimeError("; ".join(problems))
 
     def get_num_used_blocks(self) -> int:
         return self.num_blocks - self.num_free_blocks
@@ -195,11 +218,16 @@ class BlockManager:
                                f"{self.num_free_blocks} free, {num_blocks} requested)")
         free = self.is_block_free
         dev, stream = device_and_stream(free)
-        selected = torch.empty((num_blocks,), dtype=torch.int64, device=free.device)
+        selected = torch.empty((num_blocks + 1,), dtype=torch.int64, device=free.device)   # ids, then the count found
         check(lib.mkv_bitmap_select(dev, stream, free.data_ptr(), 0, free.shape[0], 1, num_blocks, 1,
-                                    selected.data_ptr(), None, None), "mkv_bitmap_select")
-        self.num_free_blocks = BlockCount(self.num_free_blocks - num_blocks)
-        return selected
+                                    selected.data_ptr(), selected[num_blocks:].data_ptr(), None), "mkv_bitmap_select")
+        found = int(selected[num_blocks].item())
+        self.num_free_blocks = BlockCount(self.num_free_blocks - found)
+        if found < num_blocks:      # the host count was ahead of the bitmap: never hand out unwritten ids
+            self._free_blocks(selected[:found])
+            raise RuntimeError(f"No enough free blocks available on {self.device_name}: the bitmap holds {found} "
+                               f"free blocks, {num_blocks} requested")
+        return selected[:num_blocks]
 
     def _free_blocks(self, block_ids: torch.Tensor):
         self.num_free_blocks = BlockCount(self.num_free_blocks + len(block_ids))
@@ -211,26 +239,24 @@ class BlockManager:
 
     def allocate_blocks_for_seqs(self, seq_ids: torch.Tensor, target_lens: torch.Tensor) -> torch.Tensor:
         """Make sure sequence i owns ceil(target_lens[i] / block_size) blocks.
-        Returns the newly allocated ids (int64), assigned in batch order."""
+        Returns the newly allocated ids (int64), assigned in batch order.
+
+        One launch (the kernel of the sync-free form: need, first-fit ids, rows and counts, all or nothing)
+        and one read of its record, which sizes the returned tensor and carries what the reference raises:
+        AssertionError when a sequence already owns more blocks than its target (:95-98), RuntimeError when the
+        pool is too small (:69-70) - decided against the bitmap itself, so a host-side count that went stale
+        cannot let an allocation through - or when a row of the block table is full."""
         seq_ids = _as_i32(seq_ids)
         target_lens = _as_i32(target_lens)
-        batch = seq_ids.shape[0]
-        dev, stream = device_and_stream(self.block_table)
-        need = torch.empty((batch,), dtype=torch.int32, device=self.block_table.device)
-        totals = torch.empty((2,), dtype=torch.int64, device=self.block_table.device)
-        check(lib.mkv_block_need(dev, stream, self.num_seq_allocated_blocks.data_ptr(), seq_ids.data_ptr(),
-                                 target_lens.data_ptr(), batch, self.block_size, need.data_ptr(),
-                                 totals.data_ptr()), "mkv_block_need")
-        n_needed, n_negative = totals.tolist()
-        assert n_negative == 0, \
-            f"""(On {self.device_name}) Logic error: Some sequences have more blocks already allocated than needed.
-                seq_ids: {seq_ids}, target_lens: {target_lens}, block_needed: {need}"""
-        if n_needed == 0:
+        if self._nosync_pending:
+            self.sync_counters()            # earlier sync-free calls: their outcome belongs to them
+        before = self._alloc_seen[0]
+        self.allocate_blocks_for_seqs_nosync(seq_ids, target_lens)
+        self.sync_counters()
+        n_new = self._alloc_seen[0] - before
+        if n_new == 0:
             return torch.empty(0, device=self.block_table.device, dtype=torch.int64)
-        new_blocks = self._allocate_blocks(n_needed)
-        set_block_table_and_num_seq_alloc_blocks(self.num_seq_allocated_blocks, self.block_table, new_blocks,
-                                                 seq_ids, need)
-        return new_blocks
+        return self._alloc_ids[:n_new].clone()
 
     def free_blocks_for_seqs(self, seq_ids: torch.Tensor):
         seq_ids = _as_i32(seq_ids)

@@ -241,3 +241,51 @@ def test_host_buffer_step_captured_with_its_copies_equals_eager_steps():
     assert torch.equal(job.bm.block_table, eager.bm.block_table)
     assert int(job.bm.num_free_blocks) == int(eager.bm.num_free_blocks)
     assert torch.equal(job.k_cache, eager.k_cache) and torch.equal(job.v_cache, eager.v_cache)
+
+
+def test_counter_snapshot_taken_before_a_nosync_call_is_not_trusted():
+    """readback_counters_async() -> another sync-free allocate / free -> num_free_blocks: the snapshot was taken
+    before the later call, so the read must fetch a fresh one (a stale count would let a later allocate pass its
+    capacity check and hand out ids the bitmap does not have)."""
+    from morphserve_b200 import BlockManager
+    bm = BlockManager("GPU", 10, 4, 6, 16)
+    a = H.to_dev(np.array([0], dtype=np.int32))
+    b = H.to_dev(np.array([1], dtype=np.int32))
+    bm.allocate_blocks_for_seqs_nosync(a, H.to_dev(np.array([48], dtype=np.int32)))      # 3 blocks
+    bm.readback_counters_async()
+    bm.allocate_blocks_for_seqs_nosync(b, H.to_dev(np.array([64], dtype=np.int32)))      # 4 more, after the snapshot
+    torch.cuda.synchronize()
+    assert int(bm.num_free_blocks) == 3
+    bm.readback_counters_async()
+    bm.free_blocks_for_seqs_nosync(a)
+    torch.cuda.synchronize()
+    assert int(bm.num_free_blocks) == 6
+    assert int(bm.is_block_free.sum()) == 6
+    # a request for more than the bitmap holds is refused by the synchronous form too, tables untouched
+    table = bm.block_table.clone()
+    with pytest.raises(RuntimeError):
+        bm.allocate_blocks_for_seqs(H.to_dev(np.array([2, 3], dtype=np.int32)),
+                                    H.to_dev(np.array([64, 64], dtype=np.int32)))
+    assert torch.equal(bm.block_table, table) and int(bm.num_free_blocks) == 6
+    # several conditions recorded since the last look are all reported
+    bm.allocate_blocks_for_seqs_nosync(b, H.to_dev(np.array([1], dtype=np.int32)))       # shrinking target
+    bm.allocate_blocks_for_seqs_nosync(a, H.to_dev(np.array([16 * 8], dtype=np.int32)))  # 8 blocks > 6-column row
+    with pytest.raises(RuntimeError) as e:
+        bm.sync_counters()
+    assert "row" in str(e.value) and "Logic error" in str(e.value)
+
+
+def test_replacing_the_bitmap_bumps_the_resize_generation():
+    """Elastic expand and release assign a new tensor to ``is_block_free`` (server/memory_utils.py:416-417, :650);
+    whatever captured the old address (a CUDA graph of the step) checks ``resize_generation``."""
+    import types
+    from morphserve_b200 import BlockManager, memory_utils
+    bm = BlockManager("GPU", 32, 4, 8, 16)
+    g0 = bm.resize_generation
+    model = types.SimpleNamespace(k_cache_new=[], v_cache_new=[], kv_cache_new_block_size=0, gpu_block_manager=bm)
+    eng = types.SimpleNamespace(model=model, scheduler=None)
+    chunk = torch.zeros((8, 1, 1, 16, 128), dtype=torch.float16, device="cuda")
+    memory_utils.attach_kvcache_chunk(eng, chunk, chunk.clone())
+    assert bm.resize_generation == g0 + 1 and bm.is_block_free.shape[0] == 40 and int(bm.num_free_blocks) == 40
+    assert memory_utils.release_last_kvcache_chunk(eng)
+    assert bm.resize_generation == g0 + 2 and bm.is_block_free.shape[0] == 32
