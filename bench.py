@@ -301,20 +301,25 @@ class DecodeJob:
         self.graph_max_len = min(int(self.lens_host.max()) + max_steps, self.bm.block_table.shape[1] * BS)
         dev = self.dev.index or 0
         max_blocks = min((self.graph_max_len + BS - 1) // BS, self.bm.block_table.shape[1])
-        ws = attn_workspace(dev, w["B"], w["Hq"], w["Hkv"], D, max_blocks)   # allocated before the capture
+        # the attention scratch belongs to the stream the launches run on: allocate it for the capture stream, before
+        # the capture
+        self.capture_stream = torch.cuda.Stream(self.dev)
+        cs = self.capture_stream.cuda_stream
+        ws = attn_workspace(dev, w["B"], w["Hq"], w["Hkv"], D, max_blocks, cs)
         self.graph_ws_ptr = ws.tensor.data_ptr()
         torch.cuda.synchronize()
         from morphserve_b200 import _lib
         calls0 = sum(_lib.CALLS.values())
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):   # other threads (NCCL) stay free
+        with torch.cuda.graph(self.graph, stream=self.capture_stream,
+                              capture_error_mode="thread_local"):   # other threads (NCCL) stay free
             self.lens_dev += 1
             st = self.infer_state(self.seq_ids, self.lens_dev, max_len=self.graph_max_len)
             self.bm.allocate_blocks_for_seqs_nosync(self.seq_ids, self.lens_dev)
             self.layers(st, self.q, self.kn, self.vn, self.o)
         self.graph_launches = sum(_lib.CALLS.values()) - calls0      # library kernels per replay
         self.graph_generation = self.bm.resize_generation
-        assert attn_workspace(dev, w["B"], w["Hq"], w["Hkv"], D, max_blocks).tensor.data_ptr() == self.graph_ws_ptr
+        assert attn_workspace(dev, w["B"], w["Hq"], w["Hkv"], D, max_blocks, cs).tensor.data_ptr() == self.graph_ws_ptr
 
     def step_graph(self):
         """One decode step = one replay of the captured graph."""
@@ -406,10 +411,12 @@ class DecodeJob:
         self.bm.prepare_nosync(w["B"])
         self.graph_max_len = min(int(self.lens_host.max()) + max_steps, self.bm.block_table.shape[1] * BS)
         max_blocks = min((self.graph_max_len + BS - 1) // BS, self.bm.block_table.shape[1])
-        attn_workspace(self.dev.index or 0, w["B"], w["Hq"], w["Hkv"], D, max_blocks)    # allocated before the capture
+        self.capture_stream_host = torch.cuda.Stream(self.dev)
+        attn_workspace(self.dev.index or 0, w["B"], w["Hq"], w["Hkv"], D, max_blocks,
+                       self.capture_stream_host.cuda_stream)                              # allocated before the capture
         torch.cuda.synchronize()
         self.graph_host = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph_host, capture_error_mode="thread_local"):
+        with torch.cuda.graph(self.graph_host, stream=self.capture_stream_host, capture_error_mode="thread_local"):
             main = torch.cuda.current_stream()
             self.s_in.wait_stream(main)             # fork: the copy streams join the capture
             self.s_out.wait_stream(main)
@@ -430,6 +437,27 @@ class DecodeJob:
 
     def kv_bytes_per_layer(self):
         return 2 * 2 * self.w["Hkv"] * D * int(self.lens_host.sum())
+
+    def snapshot(self):
+        """Lengths and block-manager state, so that every timed block starts from the same contexts."""
+        torch.cuda.synchronize()
+        bm = self.bm
+        return dict(lens_host=self.lens_host.copy(), lens_dev=self.lens_dev.clone(), table=bm.block_table.clone(),
+                    counts=bm.num_seq_allocated_blocks.clone(), free=bm.is_block_free.clone(),
+                    n_free=int(bm.num_free_blocks))
+
+    def restore(self, snap):
+        """Back to a snapshot, in place: every tensor keeps its address, so captured graphs stay valid."""
+        torch.cuda.synchronize()
+        bm = self.bm
+        _ = bm.num_free_blocks                  # folds pending sync-free allocations in before the reset
+        self.lens_host[:] = snap["lens_host"]
+        self.lens_dev.copy_(snap["lens_dev"])
+        bm.block_table.copy_(snap["table"])
+        bm.num_seq_allocated_blocks.copy_(snap["counts"])
+        bm.is_block_free.copy_(snap["free"])
+        bm.num_free_blocks = snap["n_free"]
+        torch.cuda.synchronize()
 
 
 # ----------------------------------------------------------------------------
@@ -555,7 +583,7 @@ def cpu_reference_sample(w, steps, warmup, layers_sampled=2, seqs_sampled=None):
     dt = (time.perf_counter() - t0) / max(steps, 1)
     full_step = dt * (w["B"] / B) * (w["L"] / Ls)
     return w["B"] / full_step, dict(
-        cores=os.cpu_count() or 1, kind="port",
+        cores=os.cpu_count() or 1, kind="port", sample_ms_per_step=dt * 1e3,
         sample=f"{B} of {w['B']} sequences x {Ls} of {w['L']} layers per step, {steps} steps, scaled to the full step")
 
 
@@ -766,6 +794,277 @@ def swap_bench(w, K, W, device):
 
 
 # ----------------------------------------------------------------------------
+# one decode workload: resident leg, per-kernel roofline, host-buffer leg
+# ----------------------------------------------------------------------------
+class RunContext:
+    def __init__(self, rank, world, dist, device):
+        self.rank, self.world, self.dist, self.device = rank, world, dist, device
+
+    def barrier(self):
+        if self.dist is not None:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+
+def workload_config(name, base, w, world):
+    head_shard = bool(base.get("head_shard"))
+    return {"workload": name, "baseline_config": base["cfg"], "global_batch": w["B_global"],
+            "batch_per_gpu": w["B"], "num_q_heads": base["Hq"], "num_kv_heads": base["Hkv"], "head_dim": D,
+            "block_size": BS, "num_layers": w["L"],
+            "context_len": f"uniform[{w.get('min_len', 1)},{w['max_len']}] + 1 per step"
+            + (f"; first {w['n_long']} at {w['long_len']}" if w.get("n_long") else ""),
+            "sharding": ((f"kv heads x{world}, o pushed to all ranks from the attention epilogue" if base.get("push")
+                          else f"kv heads x{world} + all-gather of o per layer") if head_shard
+                         else f"sequence x{world}"),
+            "l2": "inputs_exceed_l2"}
+
+
+def run_decode(ctx, w, name, K, W, use_graph, min_seconds, clocks=None, with_e2e=False, with_roofline=True,
+               job=None, keep_job=False):
+    """Times one decode workload on this rank's GPU.  A timed BLOCK is exactly K steps between two CUDA events,
+    bracketed by barriers; blocks are repeated from the same starting state (lengths and block tables restored in
+    place) until `min_seconds` of blocks have been measured, and the MEDIAN block is reported."""
+    from morphserve_b200 import _lib
+    rank, world, dist, device = ctx.rank, ctx.world, ctx.dist, ctx.device
+    W = max(W, 3)
+    if job is None:
+        job = DecodeJob(w, rank, growth_tokens=2 * (K + W) + 24, device=device)
+    step = job.step_resident
+    if use_graph:
+        job.step_resident()                       # sizes the workspace, loads the kernels
+        job.capture_step(max_steps=K + W + 8)
+        step = job.step_graph
+    for _ in range(W):
+        step()
+    snap = job.snapshot()
+    ctx.barrier()
+    blocks, kv_block, launches = [], 0, 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    own_clocks = clocks is None
+    if own_clocks:
+        clocks = ClockSampler([])
+    t_span = time.perf_counter()
+    with clocks:
+        while True:
+            calls0 = dict(_lib.CALLS)
+            kv_block = 0
+            ctx.barrier()
+            e0.record()
+            for _ in range(K):
+                step()
+                kv_block += job.kv_bytes_per_layer() * w["L"]
+            e1.record()
+            ctx.barrier()
+            launches = sum(v - calls0.get(k, 0) for k, v in _lib.CALLS.items())
+            blocks.append(max_over_ranks(e0.elapsed_time(e1), dist, device))
+            # every rank takes the same decision: the times above are already the maximum over ranks
+            if sum(blocks) >= min_seconds * 1e3 or len(blocks) >= 200:
+                break
+            job.restore(snap)
+    timed_seconds = time.perf_counter() - t_span
+    if use_graph:
+        launches += K * job.graph_launches          # replays launch the captured kernels without library calls
+    ms_block = statistics.median(blocks)
+    out = {"value": w["tokens_per_step"] * K / (ms_block * 1e-3), "ms_per_step": ms_block / K, "repeats": len(blocks),
+           "timed_seconds": timed_seconds, "ms_per_step_min": min(blocks) / K, "ms_per_step_max": max(blocks) / K,
+           "kv_gbs_whole_step": world * kv_block / (ms_block * 1e-3) / 1e9, "launches": launches}
+    cs = clocks.summary() if not own_clocks else None
+    out["clocks"] = cs
+    out["ms_x_mhz"] = (ms_block / K) * cs["sm_mhz"] if cs and cs.get("sm_mhz") else None
+
+    if with_roofline:
+        # ---- per-kernel timing for the roofline (attention only, append only) -----
+        job.restore(snap)
+        st = job.infer_state(job.seq_ids, job.lens_dev)
+        mk, mc, ec, bt = job.mk, job.model_config, job.engine_config, job.bm.block_table
+        reps = max(3, min(10, K))
+        for layer in range(w["L"]):
+            mk.paged_attention(job.q[layer], job.k_cache, job.v_cache, [], [], bt, mc, ec, st, layer, job.o[layer])
+        torch.cuda.synchronize()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        # at least 32 launches back to back (layers in turn), as one graph so that no launch waits for Python and
+        # the cost of starting a replay is spread thin even for the 2- and 4-layer workloads
+        rounds = max(1, -(-32 // w["L"]))
+        if use_graph:
+            attn_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(attn_graph, capture_error_mode="thread_local"):
+                for _ in range(rounds):
+                    for layer in range(w["L"]):
+                        mk.paged_attention(job.q[layer], job.k_cache, job.v_cache, [], [], bt, mc, ec, st, layer,
+                                           job.o[layer])
+            attn_graph.replay()
+            torch.cuda.synchronize()
+        a0.record()
+        for _ in range(reps):
+            if use_graph:
+                attn_graph.replay()
+                continue
+            for _ in range(rounds):
+                for layer in range(w["L"]):
+                    mk.paged_attention(job.q[layer], job.k_cache, job.v_cache, [], [], bt, mc, ec, st, layer,
+                                       job.o[layer])
+        a1.record()
+        torch.cuda.synchronize()
+        attn_ms = a0.elapsed_time(a1) / (reps * rounds * w["L"])
+        was_fused = mk.kvcache_mgmt.FUSE_DECODE_APPEND
+        mk.set_fused_decode_append(False)
+        a0.record()
+        for _ in range(reps):
+            for layer in range(w["L"]):
+                mk.store_kvcache(job.kn[layer], job.vn[layer], job.k_cache, job.v_cache, [], [], bt, mc, ec, st, layer)
+        a1.record()
+        torch.cuda.synchronize()
+        mk.set_fused_decode_append(was_fused)
+        append_ms = a0.elapsed_time(a1) / (reps * w["L"])
+        rope_ms = None
+        if w.get("rope"):       # the stand-alone rotary kernel on one layer's decode rows
+            was_rope = mk.rotary_emb.FUSE_DECODE_ROPE
+            mk.set_fused_decode_rope(False)
+            a0.record()
+            for _ in range(reps):
+                for layer in range(w["L"]):
+                    mk.rotary_embedding_inplace(job.q[layer], job.kn[layer], st)
+            a1.record()
+            torch.cuda.synchronize()
+            rope_ms = a0.elapsed_time(a1) / (reps * w["L"])
+            mk.set_fused_decode_rope(was_rope)
+        peak, peak_kind = measured_peak()
+        attn_bytes = job.kv_bytes_per_layer()
+        achieved = attn_bytes / (attn_ms * 1e-3) / 1e9
+        out["roofline"] = {"kernel": "attn_decode_f16_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
+                           "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                           "traffic": NCU_TRAFFIC_RATIO[name] * attn_bytes if name in NCU_TRAFFIC_RATIO else None,
+                           "algorithmic_bytes_per_launch": attn_bytes, "ms_per_launch": attn_ms,
+                           "append_ms_per_launch": append_ms, "rope_ms_per_launch": rope_ms}
+
+    # ---- host buffers through the public API ----------------------------------
+    if with_e2e:
+        job.restore(snap)
+        h2d, d2h = job.make_host_buffers()
+        host_step = job.step_host
+        Ke = max(3, min(K, 20))
+        if use_graph:
+            job.step_host()
+            job.capture_step_host(max_steps=Ke + 8)
+            host_step = job.step_host_graph
+        for _ in range(3):
+            host_step()
+        ctx.barrier()
+        e0.record()
+        for _ in range(Ke):
+            host_step()
+        e1.record()
+        ctx.barrier()
+        e2e_ms = max_over_ranks(e0.elapsed_time(e1), dist, device)
+        e2e = {"value": w["tokens_per_step"] * Ke / (e2e_ms * 1e-3), "unit": "tokens/s",
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": Ke, "ms_per_step": e2e_ms / Ke}
+        # the copies alone, every rank at once, each direction by itself: what the host side can feed
+        rates = {}
+        for nm, fn, nbytes in (("h2d", lambda: job.dqkv.copy_(job.hqkv, non_blocking=True), h2d),
+                               ("d2h", lambda: job.ho.copy_(job.o, non_blocking=True), d2h)):
+            fn()
+            ctx.barrier()
+            e0.record()
+            for _ in range(5):
+                fn()
+            e1.record()
+            ctx.barrier()
+            mine = nbytes * 5 / (e0.elapsed_time(e1) * 1e-3) / 1e9
+            rates[nm] = [-max_over_ranks(-mine, dist, device), max_over_ranks(mine, dist, device)]
+        e2e["copy_only_gbs_per_rank_min_max"] = rates
+        e2e["in_step_gbs_per_rank"] = {"h2d": h2d / (e2e_ms / Ke * 1e-3) / 1e9, "d2h": d2h / (e2e_ms / Ke * 1e-3) / 1e9}
+        copy_ms = max(h2d / rates["h2d"][0], d2h / rates["d2h"][0]) * 1e-6      # the two directions overlap
+        resident_ms = ms_block / K
+        if e2e_ms / Ke > 1.15 * resident_ms and copy_ms > 0.75 * e2e_ms / Ke:
+            e2e["e2e_limit"] = ("host-side copies: with every rank copying at once the slower direction alone takes "
+                                f"{copy_ms:.2f} ms per step against {resident_ms:.2f} ms for the resident step")
+        else:
+            e2e["e2e_limit"] = "the GPU step (copies overlap with it)"
+        out["e2e"] = e2e
+    if keep_job:
+        job.restore(snap)
+        out["job"] = job
+    return out
+
+
+def reference_gpu_column(job, steps):
+    """The reference's own Triton kernels (store_kvcache + paged_attention, worker/kernels/kvcache_mgmt.py:298-478 and
+    paged_attn.py:700-1015), compiled by Triton for this GPU, on the same resident batch: decode tokens/s of L x
+    (append + attention) per step - no block allocation, no Python beyond the reference's own wrappers."""
+    try:
+        from oracle import ref_loader
+        if not ref_loader.available():
+            return {"unavailable": ref_loader.why_unavailable()}
+        ref = ref_loader.load(with_ext=False)
+        import dataclasses
+        import triton
+        w = job.w
+        st = job.infer_state(job.seq_ids, job.lens_dev)
+        st_ref = ref.LlamaInferState(**{f.name: getattr(st, f.name) for f in dataclasses.fields(ref.LlamaInferState)})
+        mc, ec, bt = job.model_config, job.engine_config, job.bm.block_table
+        o = torch.empty_like(job.o[0])
+
+        def one_step(attn_only=False):
+            for layer in range(w["L"]):
+                if not attn_only:
+                    ref.store_kvcache(job.kn[layer], job.vn[layer], job.k_cache, job.v_cache, [], [], bt, mc, ec,
+                                      st_ref, layer)
+                ref.paged_attention(job.q[layer], job.k_cache, job.v_cache, [], [], bt, mc, ec, st_ref, layer, o)
+
+        one_step()                    # Triton compiles here (one variant per specialised layer number)
+        one_step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            one_step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        e0.record()
+        for _ in range(steps):
+            one_step(attn_only=True)
+        e1.record()
+        torch.cuda.synchronize()
+        attn_ms = e0.elapsed_time(e1) / (steps * w["L"])
+        nbytes = job.kv_bytes_per_layer()
+        return {"kind": "triton-jit of the reference's kernels", "triton": triton.__version__,
+                "value": w["B"] / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms, "steps": steps,
+                "attention_ms_per_layer": attn_ms, "attention_kv_gbs": nbytes / (attn_ms * 1e-3) / 1e9,
+                "seq_block_size": st.seq_block_size, "num_seq_blocks": st.num_seq_blocks,
+                "what": "L x (store_kvcache + paged_attention) on the resident batch, launched from Python"}
+    except Exception as e:      # a comparison column must not take the bench line down with it
+        return {"unavailable": f"{type(e).__name__}: {str(e)[:300]}"}
+
+
+def headshard_column(ctx, K, W, layers=8):
+    """The head-sharded CodeLlama-34B variant at the current world size (BASELINE configs[4]): every rank holds
+    Hkv / N kv heads of all 512 * N sequences; the output shards are all-gathered per layer (NCCL), or pushed into
+    every rank's full-width matrix from the attention epilogue.  `layers` of the model's 48 layers are run (the per-layer
+    cost does not depend on the layer count; this bounds memory and time next to the main workload)."""
+    import morphserve_b200
+    out = {"layers_run": layers, "layers_of_model": 48}
+    if 8 % ctx.world != 0:
+        return {"unavailable": f"8 kv heads do not divide over {ctx.world} ranks"}
+    morphserve_b200.set_fused_decode_append(False)
+    try:
+        for name in ("codellama-34b-gqa-decode-headshard", "codellama-34b-gqa-decode-headshard-push"):
+            base = dict(WORKLOADS[name], L=layers)
+            ww = shard_workload(base, ctx.rank, ctx.world)
+            try:
+                r = run_decode(ctx, ww, name, K, W, False, min_seconds=0.0, with_roofline=False)
+                out[name] = {"value": r["value"], "unit": "tokens/s", "ms_per_step": r["ms_per_step"],
+                             "ms_per_layer": r["ms_per_step"] / layers,
+                             "tokens_per_s_at_48_layers": r["value"] * layers / 48}
+            except Exception as e:
+                out[name] = {"unavailable": f"{type(e).__name__}: {str(e)[:300]}"}
+            torch.cuda.empty_cache()
+    finally:
+        morphserve_b200.set_fused_decode_append(True)
+    return out
+
+
+# ----------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -775,6 +1074,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="default workload only: skip the further columns (drop-in defaults, the reference's kernels on "
+                         "this GPU, the other workloads, the head-sharded variant)")
+    ap.add_argument("--min-seconds", type=float, default=2.0,
+                    help="repeat the timed block of --steps steps (from the same starting state) until this much time "
+                         "has been measured; the median block is reported")
     ap.add_argument("--no-cuda-graph", action="store_true",
                     help="resident leg: launch every call of the step from Python instead of capturing the step "
                          "(sync-free allocate + plan + all layers) in a CUDA graph once and replaying it")
@@ -838,22 +1143,16 @@ def main():
                               "resize": r}))
         return
     w = shard_workload(base, rank, world)
-    head_shard = bool(base.get("head_shard"))
-    config = {"workload": args.workload, "baseline_config": base["cfg"], "global_batch": w["B_global"],
-              "batch_per_gpu": w["B"], "num_q_heads": base["Hq"], "num_kv_heads": base["Hkv"], "head_dim": D,
-              "block_size": BS, "num_layers": w["L"], "context_len": f"uniform[{w.get('min_len', 1)},{w['max_len']}] + 1 per step"
-              + (f"; first {w['n_long']} at {w['long_len']}" if w.get("n_long") else ""),
-              "sharding": ((f"kv heads x{world}, o pushed to all ranks from the attention epilogue" if base.get("push")
-                            else f"kv heads x{world} + all-gather of o per layer") if head_shard
-                           else f"sequence x{world}"),
-              "l2": "inputs_exceed_l2"}
+    config = workload_config(args.workload, base, w, world)
 
     if args.impl == "reference":
         if rank != 0:
             return
         val, info = cpu_reference_sample(base, steps=K, warmup=min(W, 2))
+        config.update(host_numa_node=None, decode_append=None, step_launch=None)      # same keys as the other arm
         line = {"impl": "reference", "metric": "decode_tokens_per_s", "value": val, "unit": "tokens/s",
-                "n_gpus": args.gpus, "steps": K, "warmup": W, "ms_per_step": 1e3 * base["B"] / val,
+                "n_gpus": args.gpus, "steps": K, "warmup": W, "ms_per_step": info.pop("sample_ms_per_step"),
+                "ms_per_full_step_estimated": 1e3 * base["B"] / val,
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
                 "data": "synthetic", "config": config,
                 "cpu_baseline": dict(value=val, unit="tokens/s", **info),
@@ -873,143 +1172,76 @@ def main():
         if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
             del os.environ["NCCL_DEBUG"]        # keeps NCCL's banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=device)
-
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
+    ctx = RunContext(rank, world, dist, device)
 
     import morphserve_b200
-    from morphserve_b200 import _lib
     morphserve_b200.set_fused_decode_append(not args.no_fused_append)
     config["decode_append"] = "own launch" if args.no_fused_append else "fused into the attention launch"
     if w.get("rope"):
         fused_rope = not (args.no_fused_rope or args.no_fused_append)
         morphserve_b200.set_fused_decode_rope(fused_rope)
         config["rotary_embedding"] = "fused into the attention launch" if fused_rope else "own launch"
-    job = DecodeJob(w, rank, growth_tokens=2 * (K + W) + 16, device=device)
-
-    # ---- leg 1: inputs resident in HBM ----------------------------------------
-    clocks = ClockSampler(list(range(world)) if rank == 0 else []).start()     # comes up during the warm-up
-    step = job.step_resident
     use_graph = not args.no_cuda_graph and not base.get("head_shard")   # the captured step has no collective in it
-    config["step_launch"] = "python calls"
-    if use_graph:
-        job.step_resident()                       # sizes the workspace, loads the kernels
-        job.capture_step(max_steps=K + max(W, 3) + 4)
-        step = job.step_graph
-        config["step_launch"] = "cuda graph replay"
-    for _ in range(max(W, 3)):
-        step()
-    barrier()
-    calls0 = dict(_lib.CALLS)
-    kv_bytes = 0
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with clocks:
-        e0.record()
-        for _ in range(K):
-            step()
-            kv_bytes += job.kv_bytes_per_layer() * w["L"]
-        e1.record()
-        barrier()
-    ms = e0.elapsed_time(e1)
-    launches = sum(v - calls0.get(k, 0) for k, v in _lib.CALLS.items())
-    if use_graph:
-        launches += K * job.graph_launches          # replays launch the captured kernels without library calls
-    ms_max = max_over_ranks(ms, dist, device)
-    value = w["tokens_per_step"] * K / (ms_max * 1e-3)
+    config["step_launch"] = "cuda graph replay" if use_graph else "python calls"
 
-    # ---- per-kernel timing for the roofline (attention only, append only) -----
-    st = job.infer_state(job.seq_ids, job.lens_dev)
-    mk, mc, ec, bt = job.mk, job.model_config, job.engine_config, job.bm.block_table
-    reps = max(3, min(10, K))
-    for layer in range(w["L"]):
-        mk.paged_attention(job.q[layer], job.k_cache, job.v_cache, [], [], bt, mc, ec, st, layer, job.o[layer])
-    torch.cuda.synchronize()
-    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    if use_graph:       # the L launches back to back as one graph, so that no launch waits for Python
-        attn_graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(attn_graph, capture_error_mode="thread_local"):
-            for layer in range(w["L"]):
-                mk.paged_attention(job.q[layer], job.k_cache, job.v_cache, [], [], bt, mc, ec, st, layer, job.o[layer])
-        attn_graph.replay()
-        torch.cuda.synchronize()
-    a0.record()
-    for _ in range(reps):
-        if use_graph:
-            attn_graph.replay()
-            continue
-        for layer in range(w["L"]):
-            mk.paged_attention(job.q[layer], job.k_cache, job.v_cache, [], [], bt, mc, ec, st, layer, job.o[layer])
-    a1.record()
-    torch.cuda.synchronize()
-    attn_ms = a0.elapsed_time(a1) / (reps * w["L"])
-    a0.record()
-    for _ in range(reps):
-        for layer in range(w["L"]):
-            mk.store_kvcache(job.kn[layer], job.vn[layer], job.k_cache, job.v_cache, [], [], bt, mc, ec, st, layer)
-    a1.record()
-    torch.cuda.synchronize()
-    append_ms = a0.elapsed_time(a1) / (reps * w["L"])
-    rope_ms = None
-    if w.get("rope"):       # the stand-alone rotary kernel on one layer's decode rows
-        was_fused = mk.rotary_emb.FUSE_DECODE_ROPE
-        mk.set_fused_decode_rope(False)
-        a0.record()
-        for _ in range(reps):
-            for layer in range(w["L"]):
-                mk.rotary_embedding_inplace(job.q[layer], job.kn[layer], st)
-        a1.record()
-        torch.cuda.synchronize()
-        rope_ms = a0.elapsed_time(a1) / (reps * w["L"])
-        mk.set_fused_decode_rope(was_fused)
-    peak, peak_kind = measured_peak()
-    attn_bytes = job.kv_bytes_per_layer()
-    achieved = attn_bytes / (attn_ms * 1e-3) / 1e9
+    clocks = ClockSampler(list(range(world)) if rank == 0 else []).start()     # comes up during the warm-up
+    main_run = run_decode(ctx, w, args.workload, K, W, use_graph, min_seconds=args.min_seconds, clocks=clocks,
+                          with_e2e=not args.no_e2e, keep_job=True)
+    job = main_run.pop("job")
+    default_run = args.workload == "llama3-8b-gqa-decode" and not args.no_extras
 
-    # ---- leg 2: host buffers through the public API ---------------------------
-    e2e = None
-    if not args.no_e2e:
-        h2d, d2h = job.make_host_buffers()
-        host_step = job.step_host
-        Ke = max(3, min(K, 20))
-        if use_graph:
-            job.step_host()
-            job.capture_step_host(max_steps=Ke + 8)
-            host_step = job.step_host_graph
-        for _ in range(3):
-            host_step()
-        barrier()
-        e0.record()
-        for _ in range(Ke):
-            host_step()
-        e1.record()
-        barrier()
-        e2e_ms = max_over_ranks(e0.elapsed_time(e1), dist, device)
-        e2e = {"value": w["tokens_per_step"] * Ke / (e2e_ms * 1e-3), "unit": "tokens/s",
-               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": Ke}
+    extras = {}
+    if default_run:
+        # what a worker that calls this package exactly like the reference gets: two launches per layer issued from
+        # Python, the allocate that returns the new ids (one host synchronisation per step)
+        morphserve_b200.set_fused_decode_append(False)
+        extras["dropin_default"] = run_decode(ctx, w, args.workload, min(K, 10), 3, False, min_seconds=0.0, job=job,
+                                              with_roofline=False)
+        extras["dropin_default"]["what"] = ("store_kvcache + paged_attention as two launches per layer issued from "
+                                            "Python, BlockManager.allocate_blocks_for_seqs with its host round trip")
+        morphserve_b200.set_fused_decode_append(not args.no_fused_append)
+        if world == 1:
+            extras["reference_gpu"] = reference_gpu_column(job, steps=3)
+    del job
+    torch.cuda.empty_cache()
 
     if cpu_affinity_before is not None:
         os.sched_setaffinity(0, cpu_affinity_before)        # the CPU leg below uses every host core
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         v, info = cpu_reference_sample(base, steps=3, warmup=1)
+        info.pop("sample_ms_per_step")
         cpu = dict(value=v, unit="tokens/s", **info)
+
+    if default_run and world == 1:
+        others = {}
+        for name in ("llama2-7b-mha-decode", "codellama-34b-gqa-decode", "small-gqa-decode", "skewed-gqa-decode",
+                     "longctx-gqa-decode"):
+            ww = shard_workload(WORKLOADS[name], 0, 1)
+            r = run_decode(ctx, ww, name, 5, 3, use_graph, min_seconds=0.0)
+            others[name] = {"value": r["value"], "unit": "tokens/s", "ms_per_step": r["ms_per_step"],
+                            "num_layers": ww["L"], "batch": ww["B"], "roofline": r["roofline"]}
+            torch.cuda.empty_cache()
+        rz = resize_bench(WORKLOADS["kv-resize"], 3, 3, device)
+        peak, peak_kind = measured_peak()
+        others["kv-resize"] = {"value": rz["copy_gbs_incl_plan_and_remap"], "unit": "GB/s (read + write)",
+                               "ms_per_compaction": rz["ms_per_compaction"], "moved_blocks": rz["moved_blocks"],
+                               "copy_bytes": rz["copy_bytes"], "frac_of_peak": rz["copy_gbs_incl_plan_and_remap"] / peak,
+                               "peak_kind": peak_kind}
+        extras["other_workloads"] = others
+        torch.cuda.empty_cache()
+    if default_run and world > 1:
+        extras["headshard"] = headshard_column(ctx, K=3, W=2)
 
     if rank == 0:
         line = {
-            "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K,
-            "warmup": max(W, 3), "ms_per_step": ms_max / K, "higher_is_better": True,
-            "scaling": "weak",
+            "metric": "decode_tokens_per_s", "value": main_run["value"], "unit": "tokens/s", "n_gpus": world,
+            "steps": K, "warmup": max(W, 3), "ms_per_step": main_run["ms_per_step"], "repeats": main_run["repeats"],
+            "timed_seconds": main_run["timed_seconds"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": config,
-            "kv_gbs_whole_step": world * kv_bytes / (ms_max * 1e-3) / 1e9,
-            "roofline": {"kernel": "attn_decode_f16_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
-                         "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": (NCU_TRAFFIC_RATIO[args.workload] * attn_bytes
-                                     if args.workload in NCU_TRAFFIC_RATIO else None),
-                         "algorithmic_bytes_per_launch": attn_bytes, "ms_per_launch": attn_ms,
-                         "append_ms_per_launch": append_ms, "rope_ms_per_launch": rope_ms},
-            "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks.summary(),
+            "kv_gbs_whole_step": main_run["kv_gbs_whole_step"], "roofline": main_run["roofline"],
+            "cpu_baseline": cpu, "e2e": main_run.get("e2e"), "gpu_launches": main_run["launches"],
+            "clocks": main_run["clocks"], "ms_per_step_x_sm_mhz": main_run["ms_x_mhz"], **extras,
         }
         print(json.dumps(line))
     if dist is not None:

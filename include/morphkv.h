@@ -195,8 +195,32 @@ int mkv_paged_attention_decode_rope_append(
 int mkv_attn_configure(int warps, int stages, double item_factor, double split_balance, int loader);
 
 /*
+ * How the plan deals the launch's K/V tiles to the worker warps (process-wide tuning knob; default 1).
+ *   0: always in chunks drawn from a shared counter, longest first (sequences longer than the chunk are cut);
+ *   1: as 0 while no sequence has to be cut; otherwise every worker gets an equal contiguous range of the tile
+ *      stream and sequences are cut only where a range ends (all workers finish together; pieces are merged in
+ *      two levels when there are many);
+ *   2: equal ranges whenever the workspace allows it.
+ * Part of the scheduling the reference leaves to its launch grid (worker/kernels/paged_attn.py:832-853).
+ */
+int mkv_attn_set_static_deal(int mode);
+
+/*
+ * Testing / debugging aid: byte offsets of the regions inside an attention workspace of the given shape and the
+ * capacities the plan works with.  out[10] = {unit records, arrival counters, per-worker unit ranges, group
+ * counters, lse rows, partial rows, item capacity, unit-record capacity, most worker warps a launch can have,
+ * worker warps of a launch under the current tuning}.  No counterpart in the reference.
+ */
+int mkv_attn_workspace_layout(int device, int batch, int num_q_heads, int num_kv_heads, int head_dim,
+                              int max_blocks_per_seq_in_batch, int64_t *out);
+
+/*
  * Copies the device-side error word of a workspace to `*flags` (synchronises the
- * stream).  Bit 0: a block-table entry was outside the pool and was skipped.
+ * stream).  Bit 0: a block-table entry was outside the pool and was skipped; bit 1: a
+ * launch found no plan for its batch (or one made for more worker warps) and did
+ * nothing; bit 2: the plan ran out of item records; bits 3, 4: the TMA loader gave up.
+ * `workspace` NULL reads the word of the library's own scratch array on `device`, the
+ * one mkv_paged_attention_decode_noalloc works in.
  */
 int mkv_attn_read_error_flags(int device, void *stream, const void *workspace, int *flags /* host */);
 
@@ -227,6 +251,9 @@ int mkv_attn_read_error_flags(int device, void *stream, const void *workspace, i
  *    call's contents; each call re-initialises what it needs at its start.  Two
  *    calls that overlap on the GPU (different streams without an event between
  *    them) race on it: order them.
+ *  - Error bits (a block-table entry outside the pool, ...) land in the array's
+ *    header; read them with mkv_attn_read_error_flags(device, stream, NULL, &flags).
+ *    Every call starts with the word cleared.
  */
 int mkv_paged_attention_decode_noalloc(
     int device, void *stream, const void *q, void *o, const mkv_pool *pool, const int32_t *block_table,

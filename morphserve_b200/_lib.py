@@ -11,7 +11,8 @@ import ctypes as C
 import os
 
 MKV_MAX_SEGMENTS = 65
-_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libmorphkv.so")
+# MORPHKV_LIB names another build of the same library (a debug or instrumented build); default: the in-tree one
+_LIB_PATH = os.environ.get("MORPHKV_LIB") or os.path.join(os.path.dirname(os.path.abspath(__file__)), "libmorphkv.so")
 
 if not os.path.exists(_LIB_PATH):
     raise ImportError(
@@ -48,6 +49,8 @@ SIGNATURES = {
     "mkv_attn_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i]),
     "mkv_attn_plan": (_i, [_i, _vp, _vp, _sz, _vp, _vp, _i, _i, _i, _i, _i, _i]),
     "mkv_attn_configure": (_i, [_i, _i, C.c_double, C.c_double, _i]),
+    "mkv_attn_set_static_deal": (_i, [_i]),
+    "mkv_attn_workspace_layout": (_i, [_i, _i, _i, _i, _i, _i, C.POINTER(_i64)]),
     "mkv_paged_attention_decode_push": (_i, [_i, _vp, _vp, C.POINTER(_vp), _i, _i64, _i64, _vp, _vp, _pool, _vp, _i64,
                                              _vp, _vp, _i, _i, _i, _f, _i, _vp, _sz]),
     "mkv_paged_attention_decode_append": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _pool, _vp, _i64, _vp, _vp, _i, _i, _i, _f,

@@ -8,25 +8,33 @@
 //   plan kernel (once per decode step): cuts every sequence into chunks of
 //     `chunk` blocks so that there are a few work items per resident warp, and
 //     sorts the (sequence, chunk) items longest first.
+//     When no sequence is longer than the mean load of a worker warp allows,
+//     nothing is cut and the warps draw whole (sequence, kv head) units from a
+//     global counter (dynamic, longest first).  Otherwise the launch's tiles
+//     are dealt out STATICALLY: every worker warp gets an equal contiguous
+//     range of the tile stream, sequences are cut only where a range ends.
 //   decode kernel (once per layer): one persistent thread block per SM; every
-//     WARP is an independent worker that pulls (item, kv head) units from a
-//     global counter, streams the unit's K/V tiles through a private ring in
-//     shared memory - filled by TMA (cp.async.bulk.tensor, 128-byte swizzle, one
-//     mbarrier per stage; four 2 KiB boxes per tile issued by one lane) or, for
-//     pools of more than 8 segments, by 16-byte cp.async with the same kind of
-//     XOR swizzle - reads it with ldmatrix, and keeps an fp32 online softmax in
-//     base 2.  The next unit is claimed in three
+//     WARP is an independent worker that streams its units' K/V tiles through a
+//     private ring in shared memory - filled by 16-byte cp.async with an XOR
+//     swizzle (default) or by TMA (cp.async.bulk.tensor, 128-byte swizzle, one
+//     mbarrier per stage; four 2 KiB boxes per tile issued by one lane; pools
+//     of up to 8 segments) - reads it with ldmatrix, and keeps an fp32 online
+//     softmax in base 2.  The next unit is claimed in three
 //     non-blocking steps a few tiles before the current one ends and its first
 //     tiles are fetched into the stages the current unit frees, so the ring
 //     stays full across unit boundaries.  A sequence cut into several chunks
 //     goes through fp32 partials in the workspace; the warp that finishes a
-//     (sequence, kv head) last merges them (no second launch, no waiting).
+//     (sequence, kv head) last merges them (no second launch, no waiting); with
+//     many pieces the merge has two levels (groups of pieces first).
 //     Optionally the unit that owns the newest token's block also appends that
 //     token's K/V row (fused store_kvcache).
 //   plain kernel: any dtype / head_dim / block size, one warp per (seq, q head).
 //
 // No kernel here waits on another thread block; the only wait is a warp's wait for its
 // own bulk copy (mbarrier), which gives up after about a second and reports it.
+#include <atomic>
+#include <mutex>
+
 #include <cuda.h>  // CUtensorMap and its enums (types only: the encoder is fetched from the driver at run time)
 #include <math.h>
 #include <stdio.h>
@@ -60,38 +68,75 @@ struct alignas(256) WsHeader {
     int error_flags;
     int n_partial_rows;
     int cap_items;
+    int mode;           // 0: units = items x kv heads, drawn from work_counter; 1: static ranges per worker (wstart)
+    int n_workers;      // static mode: worker warps that own a range; the launch must bring at least as many
+    int n_units;        // static mode: unit records
 };
 
 struct WsLayout {
-    size_t items, items_tmp, arrive, lse, part_o, total;
+    size_t items, items_tmp, arrive, wstart, garrive, lse, part_o, total;
     int cap_items;
+    int cap_units;   // records the items region holds (static mode needs batch * Hkv + workers)
+    int max_workers;
 };
+constexpr int kMaxWarpsPerSm = 8;   // largest WARPS any variant of the decode kernel runs with
 
 static inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 
-static double g_item_factor = 0.0;
-static double item_factor() {
-    if (g_item_factor == 0.0) {
-        const char *e = getenv("MKV_ATTN_ITEM_FACTOR");  // tuning knob: work units per worker warp
-        double v = e ? atof(e) : 0.0;
-        g_item_factor = (v > 0.0) ? v : 4.0;
-    }
-    return g_item_factor;
+// Tuning knobs.  Process-wide, read with relaxed atomics on every call and initialised once from the environment:
+// mkv_attn_configure may run on one host thread while another launches; a launch then sees either the old or the
+// new value of each knob, never a torn one.  What a PLAN decided travels in the workspace header, so a launch
+// always follows the plan it was given.
+struct Tuning {
+    std::atomic<int> warps{8}, stages{3};
+    std::atomic<int> loader{0};        // 0 cp.async, 1 TMA, 2 no fast path at all (testing)
+    std::atomic<int> static_mode{1};   // 0 never deal statically, 1 when a sequence must be cut, 2 whenever possible
+    std::atomic<double> item_factor{4.0};    // work units per worker warp that bound the dynamic item list
+    std::atomic<double> split_balance{1.5};  // see plan_balance()
+    std::once_flag once;
+};
+static Tuning g_tuning;
+constexpr int kDefaultLoader = 0;  // 0 = cp.async (measured 1-2 % faster), 1 = TMA
+
+static Tuning &tuning() {
+    std::call_once(g_tuning.once, [] {
+        Tuning &t = g_tuning;
+        if (const char *e = getenv("MKV_ATTN_ITEM_FACTOR")) {
+            const double v = atof(e);
+            if (v > 0.0) t.item_factor = v;
+        }
+        if (const char *e = getenv("MKV_ATTN_SPLIT_BALANCE")) {  // 0 = cut as fine as the item cap allows
+            const double v = atof(e);
+            t.split_balance = v < 0.0 ? 0.0 : v;
+        }
+        if (const char *e = getenv("MKV_ATTN_VARIANT")) {  // "<warps>x<stages>"
+            int w = 0, st = 0;
+            if (sscanf(e, "%dx%d", &w, &st) == 2 && w > 0 && st > 1) {
+                t.warps = w;
+                t.stages = st;
+            }
+        }
+        t.loader = kDefaultLoader;
+        if (const char *e = getenv("MKV_ATTN_LOADER")) t.loader = strcmp(e, "cpasync") == 0 ? 0 : 1;
+        if (const char *e = getenv("MKV_ATTN_STATIC")) t.static_mode = atoi(e);
+    });
+    return g_tuning;
+}
+static double item_factor() { return tuning().item_factor.load(std::memory_order_relaxed); }
+
+// A sequence is only cut when it is longer than split_balance x the mean number of blocks per worker warp:
+// a cut costs fp32 partial rows and a merge, and pays only when one unit would otherwise outlast the rest.
+static float plan_balance(int sm_count, int num_kv_heads) {
+    return (float)(tuning().split_balance.load(std::memory_order_relaxed) * (double)num_kv_heads /
+                   ((double)sm_count * 8.0));
 }
 
-// A sequence is only cut into chunks shorter than split_balance() x the mean number of blocks per worker warp:
-// a cut costs fp32 partial rows and a merge, and pays only when one unit would otherwise outlast the rest.
-static double g_split_balance = -1.0;
-static double split_balance() {
-    if (g_split_balance < 0.0) {
-        const char *e = getenv("MKV_ATTN_SPLIT_BALANCE");  // tuning knob; 0 = cut as fine as the item cap allows
-        g_split_balance = e ? atof(e) : 1.5;
-        if (g_split_balance < 0.0) g_split_balance = 0.0;
-    }
-    return g_split_balance;
-}
-static float plan_balance(int sm_count, int num_kv_heads) {
-    return (float)(split_balance() * (double)num_kv_heads / ((double)sm_count * 8.0));
+// Warps per thread block of the decode kernel the current tuning selects (one of the compiled variants).
+static int decode_warps() {
+    const int w = tuning().warps.load(std::memory_order_relaxed), st = tuning().stages.load(std::memory_order_relaxed);
+    if (w == 6 && st == 4) return 6;
+    if (w == 7 && st == 4) return 7;
+    return 8;
 }
 
 static WsLayout make_layout(int sm_count, int batch, int num_q_heads, int num_kv_heads, int head_dim,
@@ -105,10 +150,16 @@ static WsLayout make_layout(int sm_count, int batch, int num_q_heads, int num_kv
     if (cap < batch) cap = batch;
     if (cap < 1) cap = 1;
     L.cap_items = (int)cap;
+    L.max_workers = sm_count * kMaxWarpsPerSm;
+    int64_t units = (int64_t)batch * num_kv_heads + L.max_workers;
+    if (units < cap) units = cap;
+    L.cap_units = (int)units;
     size_t off = sizeof(WsHeader);
-    L.items = off;       off = align256(off + (size_t)cap * 2 * sizeof(int4));  // 2 x int4 per item
+    L.items = off;       off = align256(off + (size_t)units * 2 * sizeof(int4));  // 2 x int4 per item / unit
     L.items_tmp = off;   off = align256(off + (size_t)cap * 2 * sizeof(int4));
     L.arrive = off;      off = align256(off + (size_t)batch * num_kv_heads * sizeof(int));
+    L.wstart = off;      off = align256(off + (size_t)(L.max_workers + 1) * sizeof(int));
+    L.garrive = off;     off = align256(off + (size_t)2 * L.max_workers * sizeof(int));
     L.lse = off;         off = align256(off + (size_t)cap * num_q_heads * sizeof(float));
     L.part_o = off;      off = align256(off + (size_t)cap * num_q_heads * head_dim * sizeof(float));
     L.total = off;
@@ -147,28 +198,96 @@ __device__ __forceinline__ int plan_scan(int v, int &total, int *warp_sums) {
     return warp_sums[wid] + incl - v;
 }
 
-__global__ void __launch_bounds__(1024) attn_plan_kernel(WsHeader *hdr, int4 *items, int4 *items_tmp,
-                                                       int *arrive, const int32_t *__restrict__ seq_lens,
-                                                       const int32_t *__restrict__ seq_ids, int batch,
-                                                       int num_kv_heads, int block_size, int cap_items,
-                                                       float balance) {
+struct PlanArgs {
+    WsHeader *hdr;
+    int4 *items;       // [cap_units] x 2
+    int4 *items_tmp;   // [cap_items] x 2; static mode: int prefix[batch + 1]
+    int *arrive;       // [batch * Hkv]
+    int *wstart;       // [max_workers + 1]
+    int *garrive;      // [2 * max_workers]
+    const int32_t *seq_lens;
+    const int32_t *seq_ids;
+    int batch, num_kv_heads, group, block_size;
+    int cap_items, cap_units, cap_rows;  // cap_rows: (row, query head) slots of the partial buffers
+    int workers;       // worker warps of the decode launch this plan is for
+    int max_workers;
+    int static_mode;   // 0 never, 1 when a sequence has to be cut, 2 whenever the buffers allow it
+    float balance;
+};
+
+// Worker that owns tile t when W workers own the ranges [floor(w T / W), floor((w + 1) T / W)).
+__device__ __forceinline__ int static_owner(long long t, long long T, int W) {
+    return (int)(((t + 1) * (long long)W - 1) / T);
+}
+
+// Static deal (mode 1).  The launch's tiles are ordered sequence by sequence, inside a sequence kv head by kv
+// head, inside a head block by block; worker w takes tiles [w T / W, (w + 1) T / W) of that order.  Its range
+// is cut into units where the (sequence, head) changes, so a (sequence, head) is split only where a range ends.
+// Walks worker w's range; with `out` it writes the unit records, and always returns how many there are.
+__device__ int static_walk(const PlanArgs &a, const int *prefix, long long T, int W, int w, int4 *out) {
+    const int Hkv = a.num_kv_heads;
+    long long t = (long long)w * T / W;
+    const long long hi = (long long)(w + 1) * T / W;
+    if (t >= hi) return 0;
+    // sequence holding tile t: the largest b with Hkv * prefix[b] <= t (empty sequences share their successor's start)
+    int lo_b = 0, hi_b = a.batch - 1;
+    while (lo_b < hi_b) {
+        const int mid = (lo_b + hi_b + 1) >> 1;
+        if ((long long)Hkv * prefix[mid] <= t) lo_b = mid; else hi_b = mid - 1;
+    }
+    int b = lo_b;
+    int nb = prefix[b + 1] - prefix[b];
+    long long rem = t - (long long)Hkv * prefix[b];
+    int h = (int)(rem / nb);
+    int blk = (int)(rem - (long long)h * nb);
+    int n_units = 0;
+    while (t < hi) {
+        const int n = (int)min((long long)(nb - blk), hi - t);
+        if (out) {
+            const long long p0 = (long long)Hkv * prefix[b] + (long long)h * nb;  // first tile of this (sequence, head)
+            const int f = static_owner(p0, T, W), l = static_owner(p0 + nb - 1, T, W);
+            // (batch index, first block, blocks, piece | head << 16) (len, pieces, first owner, table row)
+            out[2 * n_units] = make_int4(b, blk, n, (w - f) | (h << 16));
+            out[2 * n_units + 1] = make_int4(a.seq_lens[b], l - f + 1, f, a.seq_ids[b]);
+        }
+        ++n_units;
+        t += n;
+        blk += n;
+        if (blk == nb) {
+            blk = 0;
+            if (++h == Hkv) {
+                h = 0;
+                do { ++b; } while (b < a.batch && prefix[b + 1] == prefix[b]);
+                if (b >= a.batch) break;
+                nb = prefix[b + 1] - prefix[b];
+            }
+        }
+    }
+    return n_units;
+}
+
+__global__ void __launch_bounds__(1024) attn_plan_kernel(const PlanArgs a) {
     __shared__ int cnt[kNumCand];
-    __shared__ int s_total_blocks;
+    __shared__ int s_total_blocks, s_max_blocks;
     __shared__ int hist[kSortBins + 1];
     __shared__ int start[kSortBins + 1];
     __shared__ int warp_sums[33];
     __shared__ int s_chunk;
     const int tid = threadIdx.x;
+    WsHeader *hdr = a.hdr;
+    int4 *items = a.items, *items_tmp = a.items_tmp;
+    const int batch = a.batch, block_size = a.block_size, cap_items = a.cap_items;
 
     for (int k = tid; k < kNumCand; k += blockDim.x) cnt[k] = 0;
-    if (tid == 0) s_total_blocks = 0;
+    if (tid == 0) s_total_blocks = s_max_blocks = 0;
     for (int k = tid; k <= kSortBins; k += blockDim.x) hist[k] = 0;
     __syncthreads();
     for (int b = tid; b < batch; b += blockDim.x) {
-        int len = seq_lens[b];
+        int len = a.seq_lens[b];
         int nblk = len > 0 ? (len + block_size - 1) / block_size : 0;
         if (nblk > 0) {
             atomicAdd(&s_total_blocks, nblk);
+            atomicMax(&s_max_blocks, nblk);
             for (int k = 0; k < kNumCand; ++k) {
                 int c = chunk_candidate(k);
                 atomicAdd(&cnt[k], (nblk + c - 1) / c);
@@ -179,21 +298,75 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(WsHeader *hdr, int4 *it
     if (tid == 0) {
         int k = 0;
         while (k < kNumCand - 1 && cnt[k] > cap_items) ++k;
-        // balance x total blocks = the longest chunk worth keeping whole (see split_balance())
-        const float keep_whole = balance * (float)s_total_blocks;
+        // balance x total blocks = the longest chunk worth keeping whole (see plan_balance())
+        const float keep_whole = a.balance * (float)s_total_blocks;
         while (k < kNumCand - 1 && (float)chunk_candidate(k + 1) <= keep_whole) ++k;
         s_chunk = chunk_candidate(k);
     }
     __syncthreads();
     const int chunk = s_chunk;
+    for (int i = tid; i < batch * a.num_kv_heads; i += blockDim.x) a.arrive[i] = 0;
+    for (int i = tid; i < 2 * a.max_workers; i += blockDim.x) a.garrive[i] = 0;
+
+    // ---- static deal: taken when some sequence would have to be cut anyway (a cut costs partial rows and a merge
+    // either way; equal ranges then make every worker finish together, which chunks of a fixed size do not)
+    const long long T = (long long)s_total_blocks * a.num_kv_heads;
+    int W = a.workers;
+    if ((long long)W > T) W = (int)T;
+    if (W > a.cap_rows / (2 * a.group)) W = a.cap_rows / (2 * a.group);
+    const bool cuts = s_max_blocks > chunk;
+    if (((a.static_mode == 1 && cuts) || a.static_mode == 2) && W >= 1 &&
+        (long long)batch * a.num_kv_heads + W <= a.cap_units && a.num_kv_heads < 32768) {
+        int *prefix = reinterpret_cast<int *>(items_tmp);  // blocks before sequence b; [batch] = all
+        int carry = 0;
+        for (int base = 0; base < batch; base += blockDim.x) {
+            const int b = base + tid;
+            int nblk = 0;
+            if (b < batch) {
+                const int len = a.seq_lens[b];
+                nblk = len > 0 ? (len + block_size - 1) / block_size : 0;
+            }
+            int tot;
+            const int off = plan_scan(nblk, tot, warp_sums);
+            if (b < batch) prefix[b] = carry + off;
+            carry += tot;
+        }
+        if (tid == 0) prefix[batch] = carry;
+        __syncthreads();
+        int carry_u = 0;
+        for (int base = 0; base < a.max_workers + 1; base += blockDim.x) {
+            const int w = base + tid;
+            const int n = (w < W) ? static_walk(a, prefix, T, W, w, nullptr) : 0;
+            int tot;
+            const int off = plan_scan(n, tot, warp_sums);
+            if (w <= a.max_workers) a.wstart[w] = carry_u + off;  // workers >= W own an empty range
+            if (w < W) static_walk(a, prefix, T, W, w, items + 2 * (size_t)(carry_u + off));
+            carry_u += tot;
+        }
+        if (tid == 0) {
+            hdr->magic = kMagic;
+            hdr->batch = batch;
+            hdr->n_items = 0;
+            hdr->chunk_blocks = 0;
+            hdr->work_counter = 0;
+            hdr->done_counter = 0;
+            hdr->error_flags = 0;
+            hdr->n_partial_rows = 2 * W;
+            hdr->cap_items = cap_items;
+            hdr->mode = 1;
+            hdr->n_workers = W;
+            hdr->n_units = carry_u;
+        }
+        return;
+    }
 
     int carry_items = 0, carry_rows = 0;
     for (int base = 0; base < batch; base += blockDim.x) {
         const int b = base + tid;
         int nblk = 0, len = 0, row = 0;
         if (b < batch) {
-            len = seq_lens[b];
-            row = seq_ids[b];
+            len = a.seq_lens[b];
+            row = a.seq_ids[b];
             nblk = len > 0 ? (len + block_size - 1) / block_size : 0;
         }
         // chunk-sized pieces; a remainder of up to a quarter chunk stays with the piece before it (a 97-block
@@ -237,7 +410,6 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(WsHeader *hdr, int4 *it
         items[2 * pos] = it;
         items[2 * pos + 1] = items_tmp[2 * i + 1];
     }
-    for (int i = tid; i < batch * num_kv_heads; i += blockDim.x) arrive[i] = 0;
     if (tid == 0) {
         hdr->magic = kMagic;
         hdr->batch = batch;
@@ -248,6 +420,9 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(WsHeader *hdr, int4 *it
         hdr->error_flags = (carry_items > cap_items) ? 4 : 0;
         hdr->n_partial_rows = carry_rows;
         hdr->cap_items = cap_items;
+        hdr->mode = 0;
+        hdr->n_workers = 0;
+        hdr->n_units = n_items * a.num_kv_heads;
     }
 }
 
@@ -262,7 +437,7 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
-// ---- TMA (cp.async.bulk.tensor) + mbarrier: the tile loader of the default path
+// ---- TMA (cp.async.bulk.tensor) + mbarrier: the alternative tile loader (kDefaultLoader selects cp.async)
 __device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
 }
@@ -361,6 +536,8 @@ struct AttnParams {
     WsHeader *hdr;
     const int4 *items;
     int *arrive;
+    const int *wstart;  // static deal: worker w owns the unit records [wstart[w], wstart[w + 1])
+    int *garrive;       // static deal: arrival counters of the piece groups of a two-level merge
     float *lse;
     float *part_o;
 };
@@ -368,35 +545,53 @@ struct AttnParams {
 // Tensor maps of the pool segments for the TMA loader: segment s of K (and of V) as a 2-D fp16 tensor
 // [rows = blocks * L * Hkv * 16, 128], box 64 x 16, 128-byte swizzle.
 constexpr int kTmaMaxSegments = 8;
-constexpr int kDefaultLoader = 0;  // 0 = cp.async (measured 1-2 % faster), 1 = TMA
 struct TmaMaps {
     CUtensorMap k[kTmaMaxSegments];
     CUtensorMap v[kTmaMaxSegments];
 };
 
-// Merge of the split-KV partials of one (sequence, kv head): for each of the G query
-// heads, o = sum_s 2^(lse_s - m) o_s / sum_s 2^(lse_s - m).  Called by the warp that
-// arrived last.  Loads are issued in batches (2 heads x 4 chunks) before any of them
-// is used, so a merge costs a couple of L2 round trips instead of one per load.
-__device__ __forceinline__ void merge_splits(const AttnParams &p, int b, int hq0, int G, int nsplit, int64_t base,
-                                             int lane) {
+// Where the partial rows of one (sequence, kv head) live.  Piece s of it has the row
+// `base + s * stride + (s == 0 ? first_off : 0)`; query head r of the group sits at element row
+// `row * row_mul + head_off + r` of the lse / part_o buffers.
+//   dynamic deal: rows are per (sequence, chunk) item and hold all query heads: stride 1, row_mul = Hq, head_off = first
+//     query head of the group.
+//   static deal: worker w owns rows 2w and 2w + 1 (a worker holds at most two pieces of cut sequences: one that
+//     continues from the worker before it, one that continues into the next), piece s of a (sequence, head) whose
+//     first piece is at worker f lies at worker f + s: base = 2f, stride 2, first_off 1; rows hold one group.
+struct RowMap {
+    int64_t base;
+    int stride, first_off, row_mul, head_off;
+    __device__ __forceinline__ int64_t elem_row(int s, int r) const {
+        return (base + (int64_t)s * stride + (s == 0 ? first_off : 0)) * row_mul + head_off + r;
+    }
+};
+
+// Merge of `n` partial rows (pieces s0, s0 + step, ...) of one (sequence, kv head): for each of the G query
+// heads, o = sum_s 2^(lse_s - m) o_s / sum_s 2^(lse_s - m).  FINAL: the result is the attention output (fp16,
+// every destination matrix).  Otherwise it replaces the partial row of piece s0 (normalised, with its own lse),
+// one level of a two-level merge.  Loads are issued in batches (2 heads x 4 rows) before any of them is used, so a
+// merge costs a couple of L2 round trips instead of one per load.
+template <bool FINAL>
+__device__ __forceinline__ void merge_rows(const AttnParams &p, int b, int hq0, int G, const RowMap &map, int s0,
+                                           int step, int n, int lane) {
     constexpr int SB = 4;
     for (int r = 0; r < G; r += 2) {
         const bool two = (r + 1) < G;
-        const int hqa = hq0 + r, hqb = hq0 + (two ? r + 1 : r);
+        const int ra = r, rb = two ? r + 1 : r;
         float ma = -INFINITY, mb = -INFINITY, wa = 0.f, wb = 0.f;
         float4 acca = make_float4(0.f, 0.f, 0.f, 0.f), accb = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int s0 = 0; s0 < nsplit; s0 += SB) {
+        for (int i0 = 0; i0 < n; i0 += SB) {
             float la[SB], lb[SB];
             float4 va[SB], vb[SB];
 #pragma unroll
             for (int i = 0; i < SB; ++i) {
-                const bool ok = (s0 + i) < nsplit;
-                const int64_t row = base + (ok ? s0 + i : s0);
-                la[i] = __ldcg(p.lse + row * p.num_q_heads + hqa);
-                lb[i] = __ldcg(p.lse + row * p.num_q_heads + hqb);
-                va[i] = __ldcg(reinterpret_cast<const float4 *>(p.part_o + (row * p.num_q_heads + hqa) * kD + lane * 4));
-                vb[i] = __ldcg(reinterpret_cast<const float4 *>(p.part_o + (row * p.num_q_heads + hqb) * kD + lane * 4));
+                const bool ok = (i0 + i) < n;
+                const int sp = s0 + (ok ? i0 + i : i0) * step;
+                const int64_t ea = map.elem_row(sp, ra), eb = map.elem_row(sp, rb);
+                la[i] = __ldcg(p.lse + ea);
+                lb[i] = __ldcg(p.lse + eb);
+                va[i] = __ldcg(reinterpret_cast<const float4 *>(p.part_o + ea * kD + lane * 4));
+                vb[i] = __ldcg(reinterpret_cast<const float4 *>(p.part_o + eb * kD + lane * 4));
                 if (!ok) {
                     la[i] = -INFINITY;
                     lb[i] = -INFINITY;
@@ -422,27 +617,37 @@ __device__ __forceinline__ void merge_splits(const AttnParams &p, int b, int hq0
             ma = na;
             mb = nb;
         }
-        {
-            const float inv = 1.f / wa;
-            __half2 h01 = __floats2half2_rn(acca.x * inv, acca.y * inv);
-            __half2 h23 = __floats2half2_rn(acca.z * inv, acca.w * inv);
-            uint2 pk;
-            pk.x = *reinterpret_cast<uint32_t *>(&h01);
-            pk.y = *reinterpret_cast<uint32_t *>(&h23);
-            const int64_t at = (int64_t)b * p.out_row_stride + p.out_col_off + (int64_t)hqa * kD + lane * 4;
-            for (int r = 0; r < p.n_out; ++r) *reinterpret_cast<uint2 *>(p.out[r] + at) = pk;
-        }
-        if (two) {
-            const float inv = 1.f / wb;
-            __half2 h01 = __floats2half2_rn(accb.x * inv, accb.y * inv);
-            __half2 h23 = __floats2half2_rn(accb.z * inv, accb.w * inv);
-            uint2 pk;
-            pk.x = *reinterpret_cast<uint32_t *>(&h01);
-            pk.y = *reinterpret_cast<uint32_t *>(&h23);
-            const int64_t at = (int64_t)b * p.out_row_stride + p.out_col_off + (int64_t)hqb * kD + lane * 4;
-            for (int r = 0; r < p.n_out; ++r) *reinterpret_cast<uint2 *>(p.out[r] + at) = pk;
+#pragma unroll
+        for (int side = 0; side < 2; ++side) {
+            if (side == 1 && !two) break;
+            const float4 acc = side ? accb : acca;
+            const float w = side ? wb : wa, m = side ? mb : ma;
+            const int rr = side ? rb : ra;
+            const float inv = 1.f / w;
+            if (FINAL) {
+                __half2 h01 = __floats2half2_rn(acc.x * inv, acc.y * inv);
+                __half2 h23 = __floats2half2_rn(acc.z * inv, acc.w * inv);
+                uint2 pk;
+                pk.x = *reinterpret_cast<uint32_t *>(&h01);
+                pk.y = *reinterpret_cast<uint32_t *>(&h23);
+                const int64_t at = (int64_t)b * p.out_row_stride + p.out_col_off + (int64_t)(hq0 + rr) * kD + lane * 4;
+                for (int o = 0; o < p.n_out; ++o) *reinterpret_cast<uint2 *>(p.out[o] + at) = pk;
+            } else {
+                const int64_t e = map.elem_row(s0, rr);
+                __stcg(reinterpret_cast<float4 *>(p.part_o + e * kD + lane * 4),
+                       make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv));
+                if (lane == 0) __stcg(p.lse + e, log2f(w) + m);
+            }
         }
     }
+}
+
+// Pieces per group of a two-level merge: one level up to 8 pieces, otherwise about the square root of the count.
+__device__ __forceinline__ int merge_fan_in(int nsplit) {
+    if (nsplit <= 8) return nsplit;
+    int f = 8;
+    while (f * f < nsplit) ++f;
+    return f;
 }
 
 struct WorkMeta {
@@ -484,7 +689,19 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
     }
     const int Hkv = p.pool.num_kv_heads;
     const int G = p.group;
-    const unsigned total_units = (unsigned)hdr->n_items * (unsigned)Hkv;
+    const bool static_deal = hdr->mode == 1;
+    // worker number: consecutive workers sit on different SMs, so a launch with fewer ranges than workers spreads out
+    const int wid = warp * (int)gridDim.x + (int)blockIdx.x;
+    if (static_deal && (int)(gridDim.x * WARPS) < hdr->n_workers) {  // planned for more workers than this launch has
+        if (threadIdx.x == 0) atomicOr(&hdr->error_flags, 2);
+        return;
+    }
+    unsigned my_next = 0, my_end = 0;  // static deal: this worker's unit records
+    if (static_deal) {
+        my_next = (unsigned)__ldg(p.wstart + wid);
+        my_end = (unsigned)__ldg(p.wstart + wid + 1);
+    }
+    const unsigned total_units = static_deal ? my_end : (unsigned)hdr->n_items * (unsigned)Hkv;
     const bool row0 = g < G, row1 = HI && (g + 8) < G;
 
     // Claiming the next unit is a chain of three dependent global accesses (counter ->
@@ -495,7 +712,10 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
     int4 f_it = make_int4(0, 0, 0, 0), f_it1 = make_int4(0, 0, 0, 0);
     auto fetch_step = [&](WorkMeta &m) {
         if (fstage == 0) {
-            if (lane == 0) f_idx = atomicAdd(&hdr->work_counter, 1u);
+            if (static_deal)
+                f_idx = my_next++;
+            else if (lane == 0)
+                f_idx = atomicAdd(&hdr->work_counter, 1u);
             fstage = 1;
         } else if (fstage == 1) {
             const unsigned idx = __shfl_sync(0xffffffffu, f_idx, 0);
@@ -503,7 +723,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
             if (!m.valid) {
                 fstage = 3;
             } else {
-                const unsigned bc = idx / (unsigned)Hkv;
+                const unsigned bc = static_deal ? idx : idx / (unsigned)Hkv;
                 m.h = (int)(idx - bc * (unsigned)Hkv);
                 f_it = __ldg(p.items + 2 * bc);       // (batch index, first block, blocks, chunk index)
                 f_it1 = __ldg(p.items + 2 * bc + 1);  // (len, chunks, partial row, table row)
@@ -514,6 +734,10 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
             m.start = f_it.y;
             m.nblk = f_it.z;
             m.split = f_it.w;
+            if (static_deal) {  // (piece | head << 16); the third word of the second half is the first owner
+                m.split = f_it.w & 0xffff;
+                m.h = f_it.w >> 16;
+            }
             m.len = f_it1.x;
             m.nsplit = f_it1.y;
             m.prow = f_it1.z;
@@ -846,8 +1070,15 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
                 }
             }
         } else {
-            float *po = p.part_o + ((int64_t)cur.prow * p.num_q_heads + hq0) * kD;
-            float *pl = p.lse + (int64_t)cur.prow * p.num_q_heads + hq0;
+            RowMap map;
+            if (static_deal) {
+                map = RowMap{2 * (int64_t)cur.prow, 2, 1, G, 0};  // cur.prow = first owner of this (sequence, head)
+            } else {
+                map = RowMap{(int64_t)cur.prow - cur.split, 1, 0, p.num_q_heads, hq0};
+            }
+            const int64_t e0 = map.elem_row(cur.split, 0);
+            float *po = p.part_o + e0 * kD;
+            float *pl = p.lse + e0;
 #pragma unroll
             for (int n = 0; n < 16; ++n) {
                 if (row0)
@@ -863,14 +1094,43 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
             }
             __threadfence();
             __syncwarp();
+            // Announce the piece; whoever announces last merges.  With many pieces (static deal only) the pieces form
+            // groups of F: the last piece of a group folds the group into its first row, and the last GROUP to finish
+            // folds those rows into the output, so no warp ever reads more than F + pieces/F rows in a row.
+            const int F = static_deal ? merge_fan_in(cur.nsplit) : cur.nsplit;
             int *cnt = p.arrive + (int64_t)cur.b * Hkv + cur.h;
-            int old = 0;
-            if (lane == 0) old = atomicAdd(cnt, 1);
-            old = __shfl_sync(0xffffffffu, old, 0);
-            if (old == cur.nsplit - 1) {  // every chunk of this (sequence, kv head) is in the workspace
-                __threadfence();
-                if (lane == 0) *cnt = 0;
-                merge_splits(p, cur.b, hq0, G, cur.nsplit, (int64_t)cur.prow - cur.split, lane);
+            bool last = true;
+            int top_n = cur.nsplit, top_step = 1;
+            if (F < cur.nsplit) {
+                const int grp = cur.split / F;
+                const int gsize = min(F, cur.nsplit - grp * F);
+                // counter of the group: one per partial row, indexed by the row of the group's first piece
+                int *gc = p.garrive + (map.base + (int64_t)(grp * F) * map.stride + (grp == 0 ? map.first_off : 0));
+                int old = 0;
+                if (lane == 0) old = atomicAdd(gc, 1);
+                old = __shfl_sync(0xffffffffu, old, 0);
+                last = old == gsize - 1;
+                if (last) {
+                    __threadfence();
+                    if (lane == 0) *gc = 0;
+                    if (gsize > 1) {
+                        merge_rows<false>(p, cur.b, hq0, G, map, grp * F, 1, gsize, lane);
+                        __threadfence();
+                        __syncwarp();
+                    }
+                }
+                top_n = (cur.nsplit + F - 1) / F;
+                top_step = F;
+            }
+            if (last) {
+                int old = 0;
+                if (lane == 0) old = atomicAdd(cnt, 1);
+                old = __shfl_sync(0xffffffffu, old, 0);
+                if (old == top_n - 1) {  // every piece (group) of this (sequence, kv head) is in the workspace
+                    __threadfence();
+                    if (lane == 0) *cnt = 0;
+                    merge_rows<true>(p, cur.b, hq0, G, map, 0, top_step, top_n, lane);
+                }
             }
         }
     }
@@ -972,33 +1232,17 @@ __global__ void attn_decode_plain_kernel(const __grid_constant__ PoolView pool, 
 }
 
 // ------------------------------------------------------------------ host side
-struct AttnConfig {
-    int warps = 8, stages = 3;
-    bool init = false;
-};
-static AttnConfig g_attn_cfg;
-
-static AttnConfig &attn_config() {
-    AttnConfig &c = g_attn_cfg;
-    if (!c.init) {
-        const char *e = getenv("MKV_ATTN_VARIANT");  // tuning knob: "<warps>x<stages>"
-        if (e) sscanf(e, "%dx%d", &c.warps, &c.stages);
-        c.init = true;
-    }
-    return c;
-}
-
 template <int WARPS, int STAGES, bool HI, bool TMA>
 static cudaError_t launch_decode_one(const AttnParams &p, const TmaMaps &tm, int sm_count, cudaStream_t s) {
     const int smem = WARPS * STAGES * kStageBytes + (TMA ? WARPS * STAGES * 8 : 0);
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];  // per device; setting the attribute twice is harmless
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_f16_kernel<WARPS, STAGES, HI, TMA>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
-        configured[dev] = true;
+        if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
     }
     attn_decode_f16_kernel<WARPS, STAGES, HI, TMA><<<sm_count, WARPS * 32, smem, s>>>(p, tm);
     return cudaGetLastError();
@@ -1015,11 +1259,9 @@ static cudaError_t launch_decode(const AttnParams &p, const TmaMaps *tm, int sm_
 }
 
 static cudaError_t launch_decode_configured(const AttnParams &p, const TmaMaps *tm, int sms, cudaStream_t s) {
-    const AttnConfig &c = attn_config();
-    if (c.warps == 6 && c.stages == 4) return launch_decode<6, 4>(p, tm, sms, s);
-    if (c.warps == 12 && c.stages == 2) return launch_decode<12, 2>(p, tm, sms, s);
-    if (c.warps == 9 && c.stages == 3) return launch_decode<9, 3>(p, tm, sms, s);
-    if (c.warps == 7 && c.stages == 4) return launch_decode<7, 4>(p, tm, sms, s);
+    const int w = decode_warps();
+    if (w == 6) return launch_decode<6, 4>(p, tm, sms, s);
+    if (w == 7) return launch_decode<7, 4>(p, tm, sms, s);
     return launch_decode<8, 3>(p, tm, sms, s);
 }
 
@@ -1032,26 +1274,18 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
 
 static EncodeTiledFn tensor_map_encoder() {
     static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
+    static std::once_flag once;
+    std::call_once(once, [] {
         void *ptr = nullptr;
         cudaDriverEntryPointQueryResult q;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
             q == cudaDriverEntryPointSuccess)
             fn = (EncodeTiledFn)ptr;
-        tried = true;
-    }
+    });
     return fn;
 }
 
-static int g_loader = -1;
-static int loader_choice() {  // tuning knob MKV_ATTN_LOADER: "tma" (1) or "cpasync" (0); 2 = no fast path at all
-    if (g_loader < 0) {
-        const char *e = getenv("MKV_ATTN_LOADER");
-        g_loader = e ? (strcmp(e, "cpasync") == 0 ? 0 : 1) : kDefaultLoader;
-    }
-    return g_loader;
-}
+static int loader_choice() { return tuning().loader.load(std::memory_order_relaxed); }
 
 // Fills `tm` for the pool; false if the TMA loader cannot serve it (then the cp.async loader runs).
 static bool make_tma_maps(const PoolView &pv, TmaMaps *tm) {
@@ -1087,6 +1321,46 @@ static bool fast_path_ok(const PoolView &pv, int num_q_heads, const void *q, con
     return true;
 }
 
+// One plan launch for `ws` (laid out by L).  `workers` = worker warps of the decode launch that will follow.
+static void launch_plan(char *ws, const WsLayout &L, const int32_t *seq_lens, const int32_t *seq_ids, int batch,
+                        int num_q_heads, int num_kv_heads, int block_size, int sm_count, int workers, cudaStream_t s) {
+    PlanArgs a;
+    a.hdr = (WsHeader *)ws;
+    a.items = (int4 *)(ws + L.items);
+    a.items_tmp = (int4 *)(ws + L.items_tmp);
+    a.arrive = (int *)(ws + L.arrive);
+    a.wstart = (int *)(ws + L.wstart);
+    a.garrive = (int *)(ws + L.garrive);
+    a.seq_lens = seq_lens;
+    a.seq_ids = seq_ids;
+    a.batch = batch;
+    a.num_kv_heads = num_kv_heads;
+    a.group = num_q_heads / num_kv_heads;
+    a.block_size = block_size;
+    a.cap_items = L.cap_items;
+    a.cap_units = L.cap_units;
+    a.cap_rows = (int)std::min<int64_t>((int64_t)L.cap_items * num_q_heads, 0x7fffffff);
+    a.workers = workers;
+    a.max_workers = L.max_workers;
+    // the static deal exists in the tensor-core kernel only (fp16, head_dim 128, block 16, groups of up to 16)
+    const bool fast_shape = block_size == kBS && num_q_heads % num_kv_heads == 0 && a.group <= 16;
+    a.static_mode = fast_shape ? tuning().static_mode.load(std::memory_order_relaxed) : 0;
+    a.balance = plan_balance(sm_count, num_kv_heads);
+    attn_plan_kernel<<<1, 1024, 0, s>>>(a);
+}
+
+static cudaError_t builtin_scratch_address(int device, void **out);  // defined with the array, at the end of the file
+
+static void fill_workspace_params(AttnParams &p, char *ws, const WsLayout &L) {
+    p.hdr = (WsHeader *)ws;
+    p.items = (const int4 *)(ws + L.items);
+    p.arrive = (int *)(ws + L.arrive);
+    p.wstart = (const int *)(ws + L.wstart);
+    p.garrive = (int *)(ws + L.garrive);
+    p.lse = (float *)(ws + L.lse);
+    p.part_o = (float *)(ws + L.part_o);
+}
+
 }  // namespace mkv
 
 using namespace mkv;
@@ -1105,6 +1379,7 @@ int mkv_attn_plan(int device, void *stream, void *workspace, size_t workspace_by
                   const int32_t *seq_ids, int batch, int num_q_heads, int num_kv_heads, int head_dim, int block_size,
                   int max_blocks_per_seq_in_batch) {
     if (batch < 0 || num_q_heads < 1 || num_kv_heads < 1 || head_dim < 1 || block_size < 1) return MKV_ERR_SHAPE;
+    if (num_q_heads % num_kv_heads != 0) return MKV_ERR_SHAPE;
     if (!workspace || ((uintptr_t)workspace % 256) != 0) return MKV_ERR_WORKSPACE;
     if (batch > 0 && (!seq_lens || !seq_ids)) return MKV_ERR_NULL;
     int sms = 0;
@@ -1114,11 +1389,8 @@ int mkv_attn_plan(int device, void *stream, void *workspace, size_t workspace_by
     if (workspace_bytes < L.total) return MKV_ERR_WORKSPACE;
     DeviceGuard guard(device);
     if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
-    char *ws = (char *)workspace;
-    attn_plan_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(
-        (WsHeader *)ws, (int4 *)(ws + L.items), (int4 *)(ws + L.items_tmp),
-        (int *)(ws + L.arrive), seq_lens, seq_ids, batch, num_kv_heads, block_size, L.cap_items,
-        plan_balance(sms, num_kv_heads));
+    launch_plan((char *)workspace, L, seq_lens, seq_ids, batch, num_q_heads, num_kv_heads, block_size, sms,
+                sms * decode_warps(), (cudaStream_t)stream);
     MKV_LAUNCH_CHECK();
     return MKV_OK;
 }
@@ -1221,11 +1493,7 @@ static int attention_decode_impl(int device, void *stream, const void *q, void *
     p.group = num_q_heads / pv.num_kv_heads;
     p.cur_layer = cur_layer;
     p.scale_log2 = scale_log2;
-    p.hdr = (WsHeader *)ws;
-    p.items = (const int4 *)(ws + L.items);
-    p.arrive = (int *)(ws + L.arrive);
-    p.lse = (float *)(ws + L.lse);
-    p.part_o = (float *)(ws + L.part_o);
+    fill_workspace_params(p, ws, L);
 
     TmaMaps tm;
     const bool use_tma = make_tma_maps(pv, &tm);
@@ -1292,27 +1560,46 @@ int mkv_paged_attention_decode_push(int device, void *stream, const void *q, voi
 }
 
 int mkv_attn_configure(int warps, int stages, double item_factor_value, double split_balance_value, int loader) {
-    AttnConfig &c = attn_config();
+    Tuning &t = tuning();
     if (warps > 0 && stages > 1) {
-        c.warps = warps;
-        c.stages = stages;
+        t.warps.store(warps, std::memory_order_relaxed);
+        t.stages.store(stages, std::memory_order_relaxed);
     }
-    if (item_factor_value > 0.0) {
-        item_factor();
-        g_item_factor = item_factor_value;
-    }
-    if (split_balance_value >= 0.0) g_split_balance = split_balance_value;
-    if (loader >= 0 && loader <= 2) {
-        loader_choice();
-        g_loader = loader;
-    }
+    if (item_factor_value > 0.0) t.item_factor.store(item_factor_value, std::memory_order_relaxed);
+    if (split_balance_value >= 0.0) t.split_balance.store(split_balance_value, std::memory_order_relaxed);
+    if (loader >= 0 && loader <= 2) t.loader.store(loader, std::memory_order_relaxed);
+    return MKV_OK;
+}
+
+int mkv_attn_workspace_layout(int device, int batch, int num_q_heads, int num_kv_heads, int head_dim,
+                              int max_blocks_per_seq_in_batch, int64_t *out) {
+    if (!out) return MKV_ERR_NULL;
+    if (batch < 0 || num_q_heads < 1 || num_kv_heads < 1 || head_dim < 1) return MKV_ERR_SHAPE;
+    int sms = 0;
+    int st = mkv_sm_count(device, &sms);
+    if (st) return st;
+    const WsLayout L = make_layout(sms, batch, num_q_heads, num_kv_heads, head_dim, max_blocks_per_seq_in_batch);
+    const int64_t v[10] = {(int64_t)L.items, (int64_t)L.arrive, (int64_t)L.wstart, (int64_t)L.garrive, (int64_t)L.lse,
+                           (int64_t)L.part_o, L.cap_items, L.cap_units, L.max_workers, (int64_t)sms * decode_warps()};
+    for (int i = 0; i < 10; ++i) out[i] = v[i];
+    return MKV_OK;
+}
+
+int mkv_attn_set_static_deal(int mode) {
+    if (mode < 0 || mode > 2) return MKV_ERR_RANGE;
+    tuning().static_mode.store(mode, std::memory_order_relaxed);
     return MKV_OK;
 }
 
 int mkv_attn_read_error_flags(int device, void *stream, const void *workspace, int *flags) {
-    if (!workspace || !flags) return MKV_ERR_NULL;
+    if (!flags) return MKV_ERR_NULL;
     DeviceGuard guard(device);
     if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
+    if (!workspace) {  // the library's own scratch array on `device` (mkv_paged_attention_decode_noalloc)
+        void *builtin = nullptr;
+        MKV_CUDA_TRY(builtin_scratch_address(device, &builtin));
+        workspace = builtin;
+    }
     const WsHeader *hdr = (const WsHeader *)workspace;
     MKV_CUDA_TRY(cudaMemcpyAsync(flags, &hdr->error_flags, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     MKV_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
@@ -1340,18 +1627,16 @@ static __device__ __align__(256) unsigned char g_builtin_scratch[kBuiltinScratch
 // a handle for the runtime, not a device address, so it is resolved once per
 // device, with that device current, and the resolved pointer is what kernels get.
 static cudaError_t builtin_scratch_address(int device, void **out) {
-    static void *ptrs[64] = {};
-    static bool ready[64] = {};
+    static std::atomic<void *> ptrs[64];  // published with release / read with acquire: host threads may race here
     if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
-    if (!ready[device]) {
-        void *ptr = nullptr;
+    void *ptr = ptrs[device].load(std::memory_order_acquire);
+    if (ptr == nullptr) {
         cudaError_t e = cudaGetSymbolAddress((void **)&ptr, g_builtin_scratch);  // current device == `device`
         if (e != cudaSuccess) return e;
         if (ptr == nullptr) return cudaErrorInvalidSymbol;
-        ptrs[device] = ptr;
-        ready[device] = true;
+        ptrs[device].store(ptr, std::memory_order_release);  // two threads resolving at once store the same value
     }
-    *out = ptrs[device];
+    *out = ptr;
     return cudaSuccess;
 }
 
@@ -1390,10 +1675,13 @@ int mkv_paged_attention_decode_noalloc(int device, void *stream, const void *q, 
     const float scale_log2 = softmax_scale * kLog2e;
     char *ws = (char *)scratch;
 
-    if (!fast) {  // the plain kernel needs no scratch beyond the error word
+    if (scratch == nullptr) return MKV_ERR_WORKSPACE;  // never hand a null scratch pointer to a kernel
+
+    if (!fast) {  // the plain kernel needs no scratch beyond the error word, which starts clean for every call
         const int threads = 128;
         const unsigned grid = (unsigned)ceil_div64((int64_t)batch * num_q_heads, threads / 32);
         int *flags = &((WsHeader *)ws)->error_flags;
+        MKV_CUDA_TRY(cudaMemsetAsync(flags, 0, sizeof(int), s));
         if (pv.elem_bytes == 2)
             attn_decode_plain_kernel<__half><<<grid, threads, 0, s>>>(pv, (const __half *)q, (__half *)o, block_table,
                                                                      table_stride, seq_ids, seq_lens, batch,
@@ -1406,12 +1694,9 @@ int mkv_paged_attention_decode_noalloc(int device, void *stream, const void *q, 
         return MKV_OK;
     }
 
-    // The plan kernel rewrites everything that must start clean: header, work and
-    // done counters, the arrival counters of every (sequence, kv head), the item list.
-    attn_plan_kernel<<<1, 1024, 0, s>>>((WsHeader *)ws, (int4 *)(ws + L.items), (int4 *)(ws + L.items_tmp),
-                                        (int *)(ws + L.arrive), seq_lens, seq_ids,
-                                        batch, pv.num_kv_heads, pv.block_size, L.cap_items,
-                                        plan_balance(sms, pv.num_kv_heads));
+    // The plan kernel rewrites everything that must start clean: header (error word included), work and done
+    // counters, the arrival counters of every (sequence, kv head) and of the piece groups, the unit list.
+    launch_plan(ws, L, seq_lens, seq_ids, batch, num_q_heads, pv.num_kv_heads, pv.block_size, sms, sms * 8, s);
     MKV_LAUNCH_CHECK();
     AttnParams p;
     p.pool = pv;
@@ -1433,11 +1718,7 @@ int mkv_paged_attention_decode_noalloc(int device, void *stream, const void *q, 
     p.group = num_q_heads / pv.num_kv_heads;
     p.cur_layer = cur_layer;
     p.scale_log2 = scale_log2;
-    p.hdr = (WsHeader *)ws;
-    p.items = (const int4 *)(ws + L.items);
-    p.arrive = (int *)(ws + L.arrive);
-    p.lse = (float *)(ws + L.lse);
-    p.part_o = (float *)(ws + L.part_o);
+    fill_workspace_params(p, ws, L);
     TmaMaps tm;
     const bool use_tma = make_tma_maps(pv, &tm);
     cudaError_t e = launch_decode<8, 3>(p, use_tma ? &tm : nullptr, sms, s);

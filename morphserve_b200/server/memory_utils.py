@@ -153,3 +153,61 @@ def shrink_kvcache(engine, num_chunks_to_release: int) -> int:
             break
         released += 1
     return released
+
+
+# --------------------------------------------------------------------------
+# The KV half of the reference's two elastic transitions, callable from its scheduler
+# --------------------------------------------------------------------------
+def org2quant_and_update_kvcache(engine, update_kvcache: bool = True, replace_layer=None, acquire=None) -> int:
+    """Expand: the next layer (from the last one downward, worker/model.py:81) gives up its fp16 slab and the pool
+    gains the chunk carved out of it.  server/memory_utils.py:93-112, KV part and bookkeeping; swapping the layer's
+    weights is the caller's `replace_layer(engine, layer_id)` (the reference's swap_layer_in_place, :103), which
+    must have put the quantised image into the slab before the chunk behind it is zero-filled.
+    Returns the layer that was replaced.  Raises RuntimeError where the reference exits (no layer left, :99-101)."""
+    model = engine.model
+    layer_id = model.next_unquantized_layer
+    if layer_id < 0:
+        raise RuntimeError("no fp16 layer left to replace")
+    if replace_layer is not None:
+        replace_layer(engine, layer_id)
+    if update_kvcache:
+        update_kvcache_after_replacing_layer(engine, layer_id, acquire)
+    model.is_layer_quant_list[layer_id] = True
+    model.layer_quant_list.append(layer_id)
+    model.next_unquantized_layer -= 1
+    return layer_id
+
+
+def quant2org_and_update_kvcache(engine, update_kvcache: bool = True, restore_layer=None, compact: bool = True) -> bool:
+    """Release: the most recently replaced layer gets its fp16 weights back and the pool loses the LAST chunk.
+    server/memory_utils.py:617-662.  The reference gives up (returns False, :622-624) whenever a single live
+    block sits in that chunk; with `compact` the live blocks are first moved below the chunk
+    (`compact_kvcache`, block tables remapped), so the release only fails when the rest of the pool has too few free
+    blocks to take them.  The chunk's memory is about to be overwritten by the restored weights - on another stream
+    in the reference (csrc/src/memory_manager.cpp:291-322) - so the copies are waited for before `restore_layer(engine,
+    layer_id)` (the reference's free_quantized_layer + replace_layer_quant2org + rebuild, :626-641) runs."""
+    model = engine.model
+    bm = model.gpu_block_manager
+    layer_id = model.next_unquantized_layer + 1
+    if update_kvcache and not if_kv_cache_unused(engine, layer_id):
+        if not compact:
+            return False
+        boundary = bm.num_blocks_org + (len(model.k_cache_new) - 1) * model.kv_cache_new_block_size
+        if compact_kvcache(engine, boundary) < 0:
+            return False
+        torch.cuda.current_stream(bm.is_block_free.device).synchronize()
+    if update_kvcache:
+        free_kv_cache_tensors(engine, layer_id)
+    if restore_layer is not None:
+        restore_layer(engine, layer_id)
+    if update_kvcache:
+        n = model.kv_cache_new_block_size
+        bm.num_blocks -= n
+        bm.num_free_blocks -= n
+        bm.is_block_free = bm.is_block_free[:-n]
+        if getattr(engine, "scheduler", None) is not None:
+            engine.scheduler.num_gpu_blocks -= n
+    model.is_layer_quant_list[layer_id] = False
+    model.layer_quant_list.remove(layer_id)
+    model.next_unquantized_layer = layer_id
+    return True

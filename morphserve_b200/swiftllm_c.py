@@ -1,10 +1,8 @@
 """Stand-in for the reference's native extension module ``swiftllm_c``
-(csrc/src/entrypoints.cpp:6-33) for the KV path: block swap and elastic chunk
-carving.  Same function names and argument order; the work is done by
-``libmorphkv.so`` through its C ABI.
-
-Layer replacement (``replace_layer_*``, ``register_layer_memory_tensor_map_*``)
-is weight swapping, not the KV path, and is not provided here.
+(csrc/src/entrypoints.cpp:6-33): block swap, elastic chunk carving, and the data
+movement of a layer replacement (``replace_layer_*`` with the registration calls
+around it), which is what produces and retires elastic chunks.  Same function
+names and argument order; the work is done by ``libmorphkv.so`` through its C ABI.
 """
 from __future__ import annotations
 

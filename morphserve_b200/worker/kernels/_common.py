@@ -72,13 +72,19 @@ class _Workspace:
         self.generation = 0
 
 
+# One workspace per (device, stream): launches on one stream are ordered and may share scratch, launches on
+# different streams may overlap on the GPU and must not (the reference's layer code runs attention on a side
+# stream, worker/layers/transformer_layer.py:177-191; two models or two host threads bring their own streams).
+# The tensor is allocated while its stream is current, so the caching allocator ties the block to that stream
+# and dropping an old entry cannot hand its memory to work that overlaps with launches still queued on it.
 _workspaces: dict = {}
 _ws_bytes_cache: dict = {}
+_MAX_WORKSPACES = 32
 
 
-def attn_workspace(dev: int, batch: int, hq: int, hkv: int, d: int, max_blocks: int) -> _Workspace:
-    """Persistent per-device scratch for the decode kernel (plan, split-KV
-    partials, counters).  Grown when a larger batch arrives, never shrunk."""
+def attn_workspace(dev: int, batch: int, hq: int, hkv: int, d: int, max_blocks: int, stream: int = None) -> _Workspace:
+    """Persistent scratch of the decode kernel (plan, split-KV partials, counters) for launches on `stream`
+    (default: the current stream of `dev`).  Grown when a larger batch arrives, never shrunk."""
     key = (dev, batch, hq, hkv, d, max_blocks)
     need = _ws_bytes_cache.get(key)
     if need is None:
@@ -86,12 +92,20 @@ def attn_workspace(dev: int, batch: int, hq: int, hkv: int, d: int, max_blocks: 
         if need == 0:
             raise RuntimeError("mkv_attn_workspace_bytes failed")
         _ws_bytes_cache[key] = need
-    ws = _workspaces.get(dev)
+    if stream is None:
+        stream = torch.cuda.current_stream(dev).cuda_stream
+    ws = _workspaces.get((dev, stream))
     if ws is None:
-        ws = _workspaces[dev] = _Workspace()
+        if len(_workspaces) >= _MAX_WORKSPACES:      # streams come and go: forget the oldest entry
+            _workspaces.pop(next(iter(_workspaces)))
+        ws = _workspaces[(dev, stream)] = _Workspace()
     if ws.nbytes < need:
         grow = max(need, int(ws.nbytes * 1.5))
-        ws.tensor = torch.empty(grow, dtype=torch.uint8, device=torch.device("cuda", dev))
+        if torch.cuda.current_stream(dev).cuda_stream == stream:
+            ws.tensor = torch.empty(grow, dtype=torch.uint8, device=torch.device("cuda", dev))
+        else:
+            with torch.cuda.stream(torch.cuda.ExternalStream(stream, device=dev)):
+                ws.tensor = torch.empty(grow, dtype=torch.uint8, device=torch.device("cuda", dev))
         assert ws.tensor.data_ptr() % 256 == 0
         ws.nbytes = grow
         ws.generation += 1
@@ -99,11 +113,14 @@ def attn_workspace(dev: int, batch: int, hq: int, hkv: int, d: int, max_blocks: 
 
 
 def read_attn_error_flags(dev: int) -> int:
-    """Debug helper: bit 0 = a block-table entry pointed outside the pool."""
-    ws = _workspaces.get(dev)
-    if ws is None or ws.tensor is None:
-        return 0
-    flags = C.c_int(0)
-    check(lib.mkv_attn_read_error_flags(dev, torch.cuda.current_stream(dev).cuda_stream,
-                                        ws.tensor.data_ptr(), C.byref(flags)), "mkv_attn_read_error_flags")
-    return flags.value
+    """Debug helper: the error words of every attention workspace of the device, OR-ed.  Bit 0 = a block-table
+    entry pointed outside the pool."""
+    out = 0
+    for (d, _), ws in list(_workspaces.items()):
+        if d != dev or ws.tensor is None:
+            continue
+        flags = C.c_int(0)
+        check(lib.mkv_attn_read_error_flags(dev, torch.cuda.current_stream(dev).cuda_stream,
+                                            ws.tensor.data_ptr(), C.byref(flags)), "mkv_attn_read_error_flags")
+        out |= flags.value
+    return out

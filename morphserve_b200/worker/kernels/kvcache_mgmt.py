@@ -95,3 +95,19 @@ def store_kvcache(
             dev, stream, k_dec.data_ptr(), v_dec.data_ptr(), pool, block_table.data_ptr(), stride,
             seq_ids.data_ptr(), infer_state.decoding_seq_lens.data_ptr(), n_dec, cur_layer),
             "mkv_store_kv_decode")
+
+
+def store_kvcache_performance_test(k, v, k_cache, v_cache, k_cache_new, v_cache_new, block_table, model_config,
+                                   engine_config, infer_state, cur_layer: int):
+    """Import parity: the reference's layer code imports this name next to ``store_kvcache``
+    (worker/layers/transformer_layer.py:14) although it never calls it.  The reference's version
+    (worker/kernels/kvcache_mgmt.py:481-524) writes into the original pool only, ignoring the chunk lists."""
+    return store_kvcache(k, v, k_cache, v_cache, [], [], block_table, model_config, engine_config, infer_state,
+                         cur_layer)
+
+
+def store_kvcache_org_version(k, v, k_cache, v_cache, block_table, model_config, engine_config, infer_state,
+                              cur_layer: int):
+    """Import parity: the pre-elastic signature the reference keeps (worker/kernels/kvcache_mgmt.py:254-295)."""
+    return store_kvcache(k, v, k_cache, v_cache, [], [], block_table, model_config, engine_config, infer_state,
+                         cur_layer)

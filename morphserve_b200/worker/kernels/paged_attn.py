@@ -21,17 +21,25 @@ from ._common import attn_workspace, device_and_stream, make_pool, require_cuda
 from .kvcache_mgmt import flush_pending_append
 
 
-def _plan_for(infer_state, ws, dev, stream, lens, seq_ids, batch, hq, hkv, d, bs, max_blocks):
-    token = (ws.generation, dev, batch, max_blocks, lens.data_ptr(), seq_ids.data_ptr())
+def _plan_for(infer_state, ws, dev, stream, lens, seq_ids, batch, hq, hkv, d, bs, max_blocks, cur_layer):
+    """Plan once per decode step.  A plan made for this infer state is reused by the later layers of the same step
+    only: the layer number has to go UP from call to call (the reference's model walks its layers in order,
+    worker/model.py:276-291).  A call whose layer is not above the previous one starts a new step - the caller may
+    have updated ``decoding_seq_lens`` in place and reused the object - and is planned afresh, as is anything whose
+    tensors, batch or workspace changed."""
+    token = (ws.generation, dev, stream, batch, max_blocks, lens.data_ptr(), seq_ids.data_ptr())
     state = getattr(infer_state, "__dict__", None)
-    if state is not None and state.get("_mkv_plan_token") == token:
-        return
+    if state is not None:
+        seen = state.get("_mkv_plan_token")
+        if seen is not None and seen[0] == token and cur_layer > seen[1]:
+            state["_mkv_plan_token"] = (token, cur_layer)
+            return
     ws.generation += 1
     token = (ws.generation,) + token[1:]
     check(lib.mkv_attn_plan(dev, stream, ws.tensor.data_ptr(), ws.nbytes, lens.data_ptr(), seq_ids.data_ptr(), batch,
                             hq, hkv, d, bs, max_blocks), "mkv_attn_plan")
     if state is not None:
-        state["_mkv_plan_token"] = token
+        state["_mkv_plan_token"] = (token, cur_layer)
 
 
 def paged_attention(
@@ -70,8 +78,8 @@ def paged_attention(
         max_len = engine_config.max_blocks_per_seq * bs
     max_blocks = min((max_len + bs - 1) // bs, block_table.shape[1])
 
-    ws = attn_workspace(dev, batch, hq, hkv, d, max_blocks)
-    _plan_for(infer_state, ws, dev, stream, lens, seq_ids, batch, hq, hkv, d, bs, max_blocks)
+    ws = attn_workspace(dev, batch, hq, hkv, d, max_blocks, stream)
+    _plan_for(infer_state, ws, dev, stream, lens, seq_ids, batch, hq, hkv, d, bs, max_blocks, cur_layer)
     state = getattr(infer_state, "__dict__", None)
     pending = state.get("_mkv_pending_append") if state is not None else None
     rope = state.get("_mkv_pending_rope") if state is not None else None
@@ -141,8 +149,8 @@ def paged_attention_push(
     seq_ids = infer_state.seq_ids[infer_state.num_prefill_seqs:]
     max_len = getattr(infer_state, "max_decoding_len", None) or engine_config.max_blocks_per_seq * bs
     max_blocks = min((max_len + bs - 1) // bs, block_table.shape[1])
-    ws = attn_workspace(dev, batch, hq, hkv, d, max_blocks)
-    _plan_for(infer_state, ws, dev, stream, lens, seq_ids, batch, hq, hkv, d, bs, max_blocks)
+    ws = attn_workspace(dev, batch, hq, hkv, d, max_blocks, stream)
+    _plan_for(infer_state, ws, dev, stream, lens, seq_ids, batch, hq, hkv, d, bs, max_blocks, cur_layer)
     ptrs = (C.c_void_p * len(out_ptrs))(*[int(x) for x in out_ptrs])
     check(lib.mkv_paged_attention_decode_push(
         dev, stream, q.data_ptr(), ptrs, len(out_ptrs), int(out_row_stride), int(out_col_offset),

@@ -85,3 +85,38 @@ def plan_rule(lens, num_kv_heads, batch_cap_items, sm_count, split_balance=1.5, 
         items += ns
         rows += ns if ns > 1 else 0
     return chunk, items, rows
+
+
+def static_deal(lens, num_kv_heads, workers, cap_rows, group, block_size=16):
+    """The plan's static deal restated on the host.  Tiles are ordered sequence by sequence, kv head by kv head,
+    block by block; worker w of W owns tiles [w*T//W, (w+1)*T//W) where W = min(workers, tiles, cap_rows // (2 *
+    group)).  A range is cut into units where the (sequence, head) changes.  Returns (W, wstart, units) with
+    units[i] = (batch index, first block, blocks, piece, head, len, pieces, first owner)."""
+    nblk = [(int(n) + block_size - 1) // block_size if n > 0 else 0 for n in lens]
+    T = sum(nblk) * num_kv_heads
+    W = min(workers, T, cap_rows // (2 * group))
+    pairs = []                                   # (first tile, b, h, blocks)
+    t = 0
+    for b, n in enumerate(nblk):
+        for h in range(num_kv_heads if n else 0):
+            pairs.append((t, b, h, n))
+            t += n
+
+    def owner(tile):
+        return ((tile + 1) * W - 1) // T
+
+    units, wstart = [], [0]
+    pi = 0
+    for w in range(W):
+        lo, hi = w * T // W, (w + 1) * T // W
+        while pi < len(pairs) and pairs[pi][0] + pairs[pi][3] <= lo:
+            pi += 1
+        pj = pi
+        while pj < len(pairs) and pairs[pj][0] < hi:
+            p0, b, h, n = pairs[pj]
+            a, z = max(lo, p0), min(hi, p0 + n)
+            f, last = owner(p0), owner(p0 + n - 1)
+            units.append((b, a - p0, z - a, w - f, h, int(lens[b]), last - f + 1, f))
+            pj += 1
+        wstart.append(len(units))
+    return W, wstart, units

@@ -382,37 +382,61 @@ def test_push_variant_writes_the_column_slice_of_every_destination():
         assert (o[:, : first_head * 128] == 7.0).all() and (o[:, (first_head + 8) * 128:] == 7.0).all()
 
 
-@pytest.mark.parametrize("seed", range(6))
+@pytest.mark.parametrize("seed", range(10))
 def test_plan_kernel_follows_the_stated_rule(seed):
-    """Chunk size, item count and partial-row count in the workspace header against the rule restated on the host
-    (tests/helpers.py::plan_rule), for batches from 1 to 3000 sequences and several split_balance settings."""
+    """What the plan leaves in the workspace against the rules restated on the host (tests/helpers.py), for batches
+    from 1 to 3000 sequences and several split_balance settings.  No sequence longer than the chunk: chunk size, item
+    count and partial-row count of the dynamic deal (`plan_rule`).  Otherwise the static deal: every worker's range
+    of unit records, record by record (`static_deal`)."""
+    import ctypes as C
     from morphserve_b200._lib import lib, check
     from morphserve_b200.worker.kernels._common import attn_workspace
     rs = np.random.RandomState(77 + seed)
     B = int(rs.choice([1, 7, 64, 256, 900, 3000]))
     Hkv = int(rs.choice([1, 2, 8, 32]))
-    Hq = Hkv * int(rs.choice([1, 4, 8]))
+    G = int(rs.choice([1, 4, 8]))
+    Hq = Hkv * G
     max_len = int(rs.choice([40, 700, 1536, 30000])) if B <= 256 else int(rs.choice([40, 700]))
     lens = rs.randint(1, max_len + 1, size=B).astype(np.int32)
+    if seed % 3 == 0:
+        lens[rs.randint(0, B, size=max(1, B // 10))] = 0            # sequences without any token
     balance = float(rs.choice([0.0, 1.0, 1.5, 4.0]))
     max_blocks = (int(lens.max()) + 15) // 16
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     check(lib.mkv_attn_configure(-1, -1, -1.0, balance, -1), "mkv_attn_configure")
     try:
         ws = attn_workspace(0, B, Hq, Hkv, 128, max_blocks)
-        lens_t, ids_t = H.to_dev(lens), torch.arange(B, dtype=torch.int32, device="cuda")
+        lay = (C.c_int64 * 10)()
+        check(lib.mkv_attn_workspace_layout(0, B, Hq, Hkv, 128, max_blocks, lay), "mkv_attn_workspace_layout")
+        lens_t, ids_t = H.to_dev(lens), torch.arange(B, dtype=torch.int32, device="cuda") + 3
         stream = torch.cuda.current_stream().cuda_stream
         check(lib.mkv_attn_plan(0, stream, ws.tensor.data_ptr(), ws.nbytes, lens_t.data_ptr(), ids_t.data_ptr(), B,
                                 Hq, Hkv, 128, 16, max_blocks), "mkv_attn_plan")
         ws.generation += 1
         torch.cuda.synchronize()
-        hdr = ws.tensor[:64].cpu().numpy().view(np.int32)
+        raw = ws.tensor.cpu().numpy()
     finally:
         check(lib.mkv_attn_configure(-1, -1, -1.0, 1.5, -1), "mkv_attn_configure")
-    magic, batch, n_items, chunk, _, _, flags, n_rows, cap = [int(x) for x in hdr[:9]]
-    assert magic == 0x4d4b5631 and batch == B and flags == 0
+    hdr = raw[:64].view(np.int32)
+    magic, batch, n_items, chunk, _, _, flags, n_rows, cap, mode, n_workers, n_units = [int(x) for x in hdr[:12]]
+    off_items, _, off_wstart, _, _, _, cap_items, cap_units, max_workers, workers = [int(x) for x in lay]
+    assert magic == 0x4d4b5631 and batch == B and flags == 0 and cap == cap_items
     exp_chunk, exp_items, exp_rows = H.plan_rule(lens, Hkv, cap, sms, balance)
-    assert (chunk, n_items, n_rows) == (exp_chunk, exp_items, exp_rows)
+    longest = (int(lens.max()) + 15) // 16
+    if longest <= exp_chunk:
+        assert mode == 0 and (chunk, n_items, n_rows) == (exp_chunk, exp_items, exp_rows)
+        assert exp_rows == 0 and n_units == n_items * Hkv
+        return
+    W, wstart, units = H.static_deal(lens, Hkv, workers, cap_items * Hq, G)
+    assert B * Hkv + W <= cap_units
+    assert (mode, n_workers, n_units, n_rows) == (1, W, len(units), 2 * W)
+    got_start = raw[off_wstart:off_wstart + 4 * (max_workers + 1)].view(np.int32)
+    np.testing.assert_array_equal(got_start[:W + 1], wstart)
+    assert (got_start[W:] == len(units)).all()
+    rec = raw[off_items:off_items + 32 * len(units)].view(np.int32).reshape(-1, 8)
+    exp = np.array([(b, first, n, piece | (h << 16), ln, pieces, owner, b + 3)
+                    for (b, first, n, piece, h, ln, pieces, owner) in units], dtype=np.int32)
+    np.testing.assert_array_equal(rec, exp)
 
 
 def test_launch_without_a_matching_plan_touches_nothing():

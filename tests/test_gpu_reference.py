@@ -11,7 +11,11 @@ implementations then run on the same seeded inputs at the full benchmark sizes:
   and every head within rtol 2e-3 / atol 1e-2;
 * ``BlockManager`` (worker/block_manager.py): tables, counts, bitmap and the
   returned ids equal after every operation of a seeded trace;
-* ``rotary_embedding_inplace`` (worker/kernels/rotary_emb.py:43-58): bit-equal.
+* ``rotary_embedding_inplace`` (worker/kernels/rotary_emb.py:43-58): within one fp16 rounding.  The kernel's
+  source multiplies and adds in fp16; run as written (the Triton interpreter, which the committed fixtures come
+  from) every product and sum rounds separately and this package matches that bit for bit.  Compiled for a GPU, the
+  compiler fuses one multiply of each output into the add, so the compiled kernel differs from its own interpreted
+  run by a rounding - and from this package by the same amount.
 
 The tests skip (with the reason) when ``oracle/_ref`` has not been staged.
 """
@@ -126,8 +130,8 @@ def _slab_chunks(n_chunks, chunk_blocks, L, Hkv, device, gen):
     return kl, vl, P, slab
 
 
-@pytest.mark.parametrize("L,nb_org,chunk,n_chunks,B", [(32, 8192, 1024, 8, 128), (2, 300, 32, 3, 37)])
-def test_elastic_pool_against_reference_kernels(ref, L, nb_org, chunk, n_chunks, B):
+@pytest.mark.parametrize("L,nb_org,chunk,n_chunks,B,max_len", [(32, 8192, 1024, 8, 128, 1536), (2, 300, 32, 3, 37, 260)])
+def test_elastic_pool_against_reference_kernels(ref, L, nb_org, chunk, n_chunks, B, max_len):
     """The config-4 pool shape (8192 original blocks + 8 chunks of 1024, Llama-3-8B GQA, 32 layers) with the
     chunks laid out as weight slabs, block tables drawn over the WHOLE id range so that most sequences mix
     original and elastic blocks; and a small 3-chunk case."""
@@ -136,9 +140,10 @@ def test_elastic_pool_against_reference_kernels(ref, L, nb_org, chunk, n_chunks,
     Hq, Hkv = 32, 8
     g = torch.Generator().manual_seed(4000 + L)
     dg = torch.Generator(device=dev).manual_seed(4001 + L)
-    lens = torch.randint(1, 1537, (B,), generator=g, dtype=torch.int64)
+    lens = torch.randint(1, max_len + 1, (B,), generator=g, dtype=torch.int64)
     need = (lens + BS - 1) // BS
     total = nb_org + chunk * n_chunks
+    assert int(need.sum()) <= total
     perm = torch.randperm(total, generator=g)
     mbps = 128
     table = torch.full((B + 5, mbps), -1, dtype=torch.int32)
@@ -272,4 +277,8 @@ def test_rotary_embedding_against_reference_kernel(ref):
     ref.rotary_embedding_inplace(qr, kr, st)
     mk.rotary_embedding_inplace(q, k, st)
     torch.cuda.synchronize()
-    assert torch.equal(q, qr) and torch.equal(k, kr)
+    # one rounding of a product of operands of magnitude up to ~5: half an fp16 step at 4 is 2e-3
+    for a, b in ((q, qr), (k, kr)):
+        diff = (a.float() - b.float()).abs()
+        assert bool((diff <= 4e-3 + 1e-3 * b.float().abs()).all()), f"max difference {float(diff.max())}"
+        assert float((diff == 0).float().mean()) > 0.5        # most outputs round the same way either way
