@@ -23,6 +23,7 @@ barriers and the slowest rank's device time is used.
 from __future__ import annotations
 
 import argparse
+import contextlib
 import json
 import os
 import statistics
@@ -245,6 +246,15 @@ class DecodeJob:
                     self.symm = symm.rendezvous(self.o_full, dist.group.WORLD)
                     self.peer_ptrs = [int(x) for x in self.symm.buffer_ptrs]
                     self.layer_bytes = B * w["Hq_global"] * D * 2
+                    # one "slice landed" word per source rank, on every rank; rank r writes word r everywhere
+                    self.ready = symm.empty((n,), dtype=torch.int32, device=device)
+                    self.ready.zero_()
+                    self.ready_symm = symm.rendezvous(self.ready, dist.group.WORLD)
+                    self.ready_ptrs = [int(x) + 4 * dist.get_rank() for x in self.ready_symm.buffer_ptrs]
+                    self.ready_status = torch.zeros((1,), dtype=torch.int32, device=device)
+                    self.push_epoch = 0
+                    torch.cuda.synchronize()
+                    dist.barrier()
                 else:
                     # gathered outputs, [rank, sequence, local heads * D]: the consumer reads the permuted view
                     self.o_full = torch.empty((L, n, B, Hq * D), dtype=torch.float16, device=device)
@@ -270,10 +280,16 @@ class DecodeJob:
         if self.dist is not None and self.w.get("push"):
             w = self.w
             for layer in range(w["L"]):
+                self.push_epoch += 1
                 mk.paged_attention_push(q[layer], self.k_cache, self.v_cache, [], [], bt, mc, ec, st, layer,
                                         [p + layer * self.layer_bytes for p in self.peer_ptrs],
-                                        w["Hq_global"] * D, w["head_offset"] * D, k_new=kn[layer], v_new=vn[layer])
-                self.symm.barrier()        # every rank's slice of this layer has landed everywhere
+                                        w["Hq_global"] * D, w["head_offset"] * D, k_new=kn[layer], v_new=vn[layer],
+                                        ready_ptrs=self.ready_ptrs, epoch=self.push_epoch)
+                # every rank's slice of this layer has landed HERE once all words show this epoch (bounded wait;
+                # a word that stays behind sets its bit in ready_status); what consumes o_full[layer] queues behind it
+                mk.wait_ready(self.ready, self.push_epoch, self.ready_status, timeout_s=1.0)
+            # one barrier per step: nobody starts overwriting the matrices of the next step while a peer still reads
+            self.symm.barrier()
             return
         for layer in range(self.w["L"]):
             if self.cos_table is not None:
@@ -1005,11 +1021,14 @@ def reference_gpu_column(job, steps):
         o = torch.empty_like(job.o[0])
 
         def one_step(attn_only=False):
-            for layer in range(w["L"]):
-                if not attn_only:
-                    ref.store_kvcache(job.kn[layer], job.vn[layer], job.k_cache, job.v_cache, [], [], bt, mc, ec,
-                                      st_ref, layer)
-                ref.paged_attention(job.q[layer], job.k_cache, job.v_cache, [], [], bt, mc, ec, st_ref, layer, o)
+            # the reference's wrappers print timing reports (whenever a call took long, e.g. while Triton compiles):
+            # they belong on stderr here, stdout carries the one JSON line
+            with contextlib.redirect_stdout(sys.stderr):
+                for layer in range(w["L"]):
+                    if not attn_only:
+                        ref.store_kvcache(job.kn[layer], job.vn[layer], job.k_cache, job.v_cache, [], [], bt, mc, ec,
+                                          st_ref, layer)
+                    ref.paged_attention(job.q[layer], job.k_cache, job.v_cache, [], [], bt, mc, ec, st_ref, layer, o)
 
         one_step()                    # Triton compiles here (one variant per specialised layer number)
         one_step()

@@ -141,17 +141,33 @@ int mkv_paged_attention_decode_append(
  * rank's full-width [batch, Hq_total*head_dim] matrix through peer-mapped
  * pointers - plain stores over NVLink from the kernel's epilogue, so the
  * "all-gather" rides inside the attention launch.  Nothing is loaded from a
- * peer.  The caller makes the peers' stores visible before reading its matrix
- * (a barrier across the ranks after the launch).  out_ptrs is a HOST array of
- * n_out <= 8 device-accessible pointers; k_new / v_new as in
- * mkv_paged_attention_decode_append, or NULL.  fp16 / head_dim 128 / block 16.
+ * peer.  Before a rank reads its matrix the peers' stores must have landed: either
+ * the caller runs a barrier across the ranks after the launch, or it passes
+ * `ready_ptrs` (HOST array of n_ready <= 8 device-accessible int32 words, one per
+ * destination, each in THAT destination's memory; NULL / 0: no signal): when the last store
+ * of the launch is done the kernel writes `epoch` into every one of them behind a
+ * system-wide fence, and the destination waits with mkv_wait_ready.  Epochs must grow
+ * from launch to launch.  out_ptrs is a HOST array of n_out <= 8 device-accessible
+ * pointers; k_new / v_new as in mkv_paged_attention_decode_append, or NULL.
+ * fp16 / head_dim 128 / block 16.
  */
 int mkv_paged_attention_decode_push(
     int device, void *stream, const void *q, void *const *out_ptrs, int n_out, int64_t out_row_stride,
-    int64_t out_col_offset, const void *k_new, const void *v_new, const mkv_pool *pool,
+    int64_t out_col_offset, int32_t *const *ready_ptrs, int n_ready, int32_t epoch,
+    const void *k_new, const void *v_new, const mkv_pool *pool,
     const int32_t *block_table, int64_t table_stride, const int32_t *seq_ids, const int32_t *seq_lens,
     int batch, int num_q_heads, int cur_layer, float softmax_scale, int max_blocks_per_seq_in_batch,
     void *workspace, size_t workspace_bytes);
+
+/*
+ * Waits, on `stream`, until flags[0..n) (device memory of THIS GPU, written by the peers' push launches) have all
+ * reached `epoch`, for at most timeout_ns (capped at two seconds): one warp polls with system-scope acquire loads.
+ * A flag that does not arrive in time sets its bit in *status (device int32, accumulated; the caller clears and
+ * reads it) and the kernel returns - a rank that died or skipped its launch costs the others the timeout, never a
+ * hang.  Kernels queued behind it on the stream may read the pushed data.  No counterpart in the reference.
+ */
+int mkv_wait_ready(int device, void *stream, const int32_t *flags, int n, int32_t epoch, int64_t timeout_ns,
+                   int32_t *status);
 
 /*
  * Rotary position embedding of q [num_tokens, Hq, D] and k [num_tokens, Hkv, D] in place
@@ -159,11 +175,22 @@ int mkv_paged_attention_decode_push(
  * of store_kvcache: worker/layers/transformer_layer.py:93-98).  cos_table / sin_table:
  * fp16 [num_tokens, D/2], the rows of the reference's tables gathered for the tokens'
  * positions (worker/model.py:240-241, 432-433).  Halves [0, D/2) and [D/2, D) of every head
- * become (x0*cos - x1*sin, x0*sin + x1*cos); with fp16 data every product and sum is rounded
- * to fp16 on its own, as in the reference kernel.  elem_bytes 2 (fp16) or 4 (fp32).
+ * become (x0*cos - x1*sin, x0*sin + x1*cos), rounded as mkv_rope_set_rounding selects.
+ * elem_bytes 2 (fp16) or 4 (fp32).
  */
 int mkv_rotary_embedding(int device, void *stream, void *q, void *k, const void *cos_table, const void *sin_table,
                          int64_t num_tokens, int num_q_heads, int num_kv_heads, int head_dim, int elem_bytes);
+
+/*
+ * How the rotation is rounded (process-wide; applies to mkv_rotary_embedding and to the rotation fused into the
+ * decode kernel).  The reference writes it in the data's precision (worker/kernels/rotary_emb.py:36-41):
+ *   as_compiled != 0 (default): x0*cos - rn(x1*sin) and x0*sin + rn(x1*cos), the first product fused into the add
+ *     with one rounding - what the reference's kernel computes once Triton has compiled it for a GPU (bit-equal to
+ *     the kernel compiled by Triton 3.6 for sm_100);
+ *   as_compiled == 0: every product and every sum rounded on its own - what the same source gives when run
+ *     operation by operation (the Triton interpreter); also selected by MKV_ROPE_ROUNDING=written.
+ */
+int mkv_rope_set_rounding(int as_compiled);
 
 /*
  * mkv_rotary_embedding (decode rows) + mkv_store_kv_decode + mkv_paged_attention_decode of one
@@ -201,9 +228,12 @@ int mkv_attn_configure(int warps, int stages, double item_factor, double split_b
  *      stream and sequences are cut only where a range ends (all workers finish together; pieces are merged in
  *      two levels when there are many);
  *   2: equal ranges whenever the workspace allows it.
+ * `unit_cost` (default 1): with equal ranges, what starting a unit is worth in tiles - every (sequence, kv head)
+ * counts as that many tiles more than it has, so a worker that is dealt many short sequences is dealt fewer tiles.
+ * Negative values keep the current setting of either knob.
  * Part of the scheduling the reference leaves to its launch grid (worker/kernels/paged_attn.py:832-853).
  */
-int mkv_attn_set_static_deal(int mode);
+int mkv_attn_set_static_deal(int mode, int unit_cost);
 
 /*
  * Testing / debugging aid: byte offsets of the regions inside an attention workspace of the given shape and the
@@ -285,11 +315,17 @@ int mkv_store_kv_prefill(int device, void *stream, const void *k, const void *v,
 
 /* ---- block table ------------------------------------------------------ */
 /*
+ * `num_rows` (everywhere below) = entries of num_allocated = rows of block_table (the reference's
+ * max_seqs_in_block_table).  A sequence id outside [0, num_rows) touches nothing: the reference's torch indexing
+ * would raise for it; here it is skipped, and reported by the calls that have a status to report into
+ * (mkv_block_need counts it with the shrinking sequences, mkv_block_allocate refuses the whole request).
+ */
+/*
  * need[i] = ceil(target_lens[i]/block_size) - num_allocated[seq_ids[i]];
  * totals[0] = sum(need), totals[1] = number of negative entries (the reference
  * asserts there are none, worker/block_manager.py:94-99).
  */
-int mkv_block_need(int device, void *stream, const int32_t *num_allocated, const int32_t *seq_ids,
+int mkv_block_need(int device, void *stream, const int32_t *num_allocated, int num_rows, const int32_t *seq_ids,
                    const int32_t *target_lens, int batch, int block_size,
                    int32_t *need /* device [batch] */, int64_t *totals /* device [2] */);
 
@@ -307,8 +343,8 @@ int mkv_block_need(int device, void *stream, const int32_t *num_allocated, const
  * allocation, so a whole decode step can be enqueued (or captured in a CUDA graph) ahead of time;
  * the host reads `status` whenever it next needs the free-block count.
  */
-int mkv_block_allocate(int device, void *stream, int32_t *num_allocated, int32_t *block_table, int64_t table_stride,
-                       const int32_t *seq_ids, const int32_t *target_lens, int batch, int block_size,
+int mkv_block_allocate(int device, void *stream, int32_t *num_allocated, int num_rows, int32_t *block_table,
+                       int64_t table_stride, const int32_t *seq_ids, const int32_t *target_lens, int batch, int block_size,
                        uint8_t *bitmap /* is_block_free */, int64_t num_blocks, int32_t *need, int64_t *ids,
                        int64_t ids_capacity, int64_t *status);
 
@@ -334,7 +370,7 @@ int mkv_bitmap_scatter(int device, void *stream, uint8_t *bitmap, int64_t bitmap
  * (worker/kernels/block_mgmt.py:5-46).  Sequence i takes
  * candidates[cumsum(need)[i]-need[i] : cumsum(need)[i]] (batch order).
  */
-int mkv_block_table_set(int device, void *stream, int32_t *num_allocated, int32_t *block_table,
+int mkv_block_table_set(int device, void *stream, int32_t *num_allocated, int num_rows, int32_t *block_table,
                         int64_t table_stride, const int64_t *candidates, const int32_t *seq_ids,
                         const int32_t *need, int batch);
 
@@ -347,14 +383,14 @@ int mkv_block_table_set(int device, void *stream, int32_t *num_allocated, int32_
  * total_out (device, may be NULL) receives the number of blocks freed, or, with
  * accumulate != 0, is increased by it (a running count the host reads later).
  */
-int mkv_block_table_unset(int device, void *stream, int32_t *num_allocated, const int32_t *block_table,
+int mkv_block_table_unset(int device, void *stream, int32_t *num_allocated, int num_rows, const int32_t *block_table,
                           int64_t table_stride, const int32_t *seq_ids, int batch, uint8_t *is_block_free,
                           int64_t num_blocks, int32_t *gathered, int64_t gathered_capacity,
                           int64_t *total_out, int accumulate);
 
 /* sum over the batch of num_allocated[seq_ids[i]] -> *total_out (device). */
-int mkv_block_table_count(int device, void *stream, const int32_t *num_allocated, const int32_t *seq_ids,
-                          int batch, int64_t *total_out);
+int mkv_block_table_count(int device, void *stream, const int32_t *num_allocated, int num_rows,
+                          const int32_t *seq_ids, int batch, int64_t *total_out);
 
 /* ---- elastic resize --------------------------------------------------- */
 /*

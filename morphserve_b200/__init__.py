@@ -30,8 +30,8 @@ from .worker.infer_state import LlamaInferState
 from .worker.kv_model import KVCacheModelState
 from .worker.kernels import block_mgmt, kvcache_mgmt, paged_attn, rotary_emb
 from .worker.kernels.kvcache_mgmt import set_fused_decode_append, store_kvcache
-from .worker.kernels.paged_attn import paged_attention, paged_attention_push
-from .worker.kernels.rotary_emb import rotary_embedding_inplace, set_fused_decode_rope
+from .worker.kernels.paged_attn import paged_attention, paged_attention_push, wait_ready
+from .worker.kernels.rotary_emb import rotary_embedding_inplace, set_fused_decode_rope, set_rope_rounding
 
 __version__ = "0.1.0"
 
@@ -79,7 +79,7 @@ def install_as_swiftllm(overwrite: bool = True) -> None:
                 setattr(sys.modules[parent], parts[-1], mod)
 
 
-__all__ = ["paged_attention", "paged_attention_push", "store_kvcache", "set_fused_decode_append",
-           "rotary_embedding_inplace", "set_fused_decode_rope", "BlockManager", "LlamaInferState",
+__all__ = ["paged_attention", "paged_attention_push", "wait_ready", "store_kvcache", "set_fused_decode_append",
+           "rotary_embedding_inplace", "set_fused_decode_rope", "set_rope_rounding", "BlockManager", "LlamaInferState",
            "KVCacheModelState",
            "swiftllm_c", "memory_utils", "install_as_swiftllm"]

@@ -49,10 +49,11 @@ SIGNATURES = {
     "mkv_attn_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i]),
     "mkv_attn_plan": (_i, [_i, _vp, _vp, _sz, _vp, _vp, _i, _i, _i, _i, _i, _i]),
     "mkv_attn_configure": (_i, [_i, _i, C.c_double, C.c_double, _i]),
-    "mkv_attn_set_static_deal": (_i, [_i]),
+    "mkv_attn_set_static_deal": (_i, [_i, _i]),
     "mkv_attn_workspace_layout": (_i, [_i, _i, _i, _i, _i, _i, C.POINTER(_i64)]),
-    "mkv_paged_attention_decode_push": (_i, [_i, _vp, _vp, C.POINTER(_vp), _i, _i64, _i64, _vp, _vp, _pool, _vp, _i64,
-                                             _vp, _vp, _i, _i, _i, _f, _i, _vp, _sz]),
+    "mkv_paged_attention_decode_push": (_i, [_i, _vp, _vp, C.POINTER(_vp), _i, _i64, _i64, C.POINTER(_vp), _i, C.c_int32,
+                                             _vp, _vp, _pool, _vp, _i64, _vp, _vp, _i, _i, _i, _f, _i, _vp, _sz]),
+    "mkv_wait_ready": (_i, [_i, _vp, _vp, _i, C.c_int32, _i64, _vp]),
     "mkv_paged_attention_decode_append": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _pool, _vp, _i64, _vp, _vp, _i, _i, _i, _f,
                                                _i, _vp, _sz]),
     "mkv_paged_attention_decode": (_i, [_i, _vp, _vp, _vp, _pool, _vp, _i64, _vp, _vp, _i, _i, _i, _f, _i, _vp, _sz]),
@@ -60,18 +61,19 @@ SIGNATURES = {
     "mkv_paged_attention_decode_noalloc": (_i, [_i, _vp, _vp, _vp, _pool, _vp, _i64, _vp, _vp, _i, _i, _i, _f, _i]),
     "mkv_noalloc_scratch_bytes": (_sz, []),
     "mkv_rotary_embedding": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i]),
+    "mkv_rope_set_rounding": (_i, [_i]),
     "mkv_paged_attention_decode_rope_append": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _pool, _vp, _i64, _vp, _vp,
                                                    _i, _i, _i, _f, _i, _vp, _sz]),
     "mkv_store_kv_decode": (_i, [_i, _vp, _vp, _vp, _pool, _vp, _i64, _vp, _vp, _i, _i]),
     "mkv_store_kv_prefill": (_i, [_i, _vp, _vp, _vp, _pool, _vp, _i64, _vp, _vp, _vp, _i, _i, _i]),
-    "mkv_block_need": (_i, [_i, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp]),
+    "mkv_block_need": (_i, [_i, _vp, _vp, _i, _vp, _vp, _i, _i, _vp, _vp]),
     "mkv_slab_upload": (_i, [_i, _vp, _sz, _vp, _sz]),
-    "mkv_block_allocate": (_i, [_i, _vp, _vp, _vp, _i64, _vp, _vp, _i, _i, _vp, _i64, _vp, _vp, _i64, _vp]),
+    "mkv_block_allocate": (_i, [_i, _vp, _vp, _i, _vp, _i64, _vp, _vp, _i, _i, _vp, _i64, _vp, _vp, _i64, _vp]),
     "mkv_bitmap_select": (_i, [_i, _vp, _vp, _i64, _i64, _i, _i64, _i, _vp, _vp, _vp]),
     "mkv_bitmap_scatter": (_i, [_i, _vp, _vp, _i64, _vp, _i64, _i]),
-    "mkv_block_table_set": (_i, [_i, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _i]),
-    "mkv_block_table_unset": (_i, [_i, _vp, _vp, _vp, _i64, _vp, _i, _vp, _i64, _vp, _i64, _vp, _i]),
-    "mkv_block_table_count": (_i, [_i, _vp, _vp, _vp, _i, _vp]),
+    "mkv_block_table_set": (_i, [_i, _vp, _vp, _i, _vp, _i64, _vp, _vp, _vp, _i]),
+    "mkv_block_table_unset": (_i, [_i, _vp, _vp, _i, _vp, _i64, _vp, _i, _vp, _i64, _vp, _i64, _vp, _i]),
+    "mkv_block_table_count": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp]),
     "mkv_chunk_layout": (_i, [C.c_uint64, C.c_uint64, C.c_uint64, _i, _i, _i, _i, _i,
                               C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(_i64)]),
     "mkv_copy_blocks": (_i, [_i, _vp, _pool, _vp, _vp, _i64]),

@@ -32,6 +32,7 @@
 //
 // No kernel here waits on another thread block; the only wait is a warp's wait for its
 // own bulk copy (mbarrier), which gives up after about a second and reports it.
+#include <algorithm>
 #include <atomic>
 #include <mutex>
 
@@ -91,6 +92,7 @@ struct Tuning {
     std::atomic<int> warps{8}, stages{3};
     std::atomic<int> loader{0};        // 0 cp.async, 1 TMA, 2 no fast path at all (testing)
     std::atomic<int> static_mode{1};   // 0 never deal statically, 1 when a sequence must be cut, 2 whenever possible
+    std::atomic<int> unit_cost{1};     // static deal: tiles that starting a unit is worth
     std::atomic<double> item_factor{4.0};    // work units per worker warp that bound the dynamic item list
     std::atomic<double> split_balance{1.5};  // see plan_balance()
     std::once_flag once;
@@ -119,6 +121,7 @@ static Tuning &tuning() {
         t.loader = kDefaultLoader;
         if (const char *e = getenv("MKV_ATTN_LOADER")) t.loader = strcmp(e, "cpasync") == 0 ? 0 : 1;
         if (const char *e = getenv("MKV_ATTN_STATIC")) t.static_mode = atoi(e);
+        if (const char *e = getenv("MKV_ATTN_UNIT_COST")) t.unit_cost = std::max(0, std::min(64, atoi(e)));
     });
     return g_tuning;
 }
@@ -212,6 +215,7 @@ struct PlanArgs {
     int workers;       // worker warps of the decode launch this plan is for
     int max_workers;
     int static_mode;   // 0 never, 1 when a sequence has to be cut, 2 whenever the buffers allow it
+    int unit_cost;     // static deal: what starting a unit costs a worker, in tiles
     float balance;
 };
 
@@ -221,11 +225,15 @@ __device__ __forceinline__ int static_owner(long long t, long long T, int W) {
 }
 
 // Static deal (mode 1).  The launch's tiles are ordered sequence by sequence, inside a sequence kv head by kv
-// head, inside a head block by block; worker w takes tiles [w T / W, (w + 1) T / W) of that order.  Its range
-// is cut into units where the (sequence, head) changes, so a (sequence, head) is split only where a range ends.
-// Walks worker w's range; with `out` it writes the unit records, and always returns how many there are.
+// head, inside a head block by block; in front of every (sequence, head) stand `unit_cost` PHANTOM tiles, which
+// stand for what starting a unit costs a worker (descriptor, block ids, query fragments, the first tile's
+// latency).  Worker w takes tiles [w T / W, (w + 1) T / W) of that order, phantoms included, so a worker that
+// gets many short sequences gets fewer tiles.  Its range is cut into units where the (sequence, head) changes, so a
+// (sequence, head) is split only where a range ends.  `prefix[b]` = tiles, phantoms included, of ONE head of all
+// sequences before b.  Walks worker w's range; with `out` it writes the unit records, and always returns how many
+// there are.
 __device__ int static_walk(const PlanArgs &a, const int *prefix, long long T, int W, int w, int4 *out) {
-    const int Hkv = a.num_kv_heads;
+    const int Hkv = a.num_kv_heads, oc = a.unit_cost;
     long long t = (long long)w * T / W;
     const long long hi = (long long)(w + 1) * T / W;
     if (t >= hi) return 0;
@@ -236,21 +244,24 @@ __device__ int static_walk(const PlanArgs &a, const int *prefix, long long T, in
         if ((long long)Hkv * prefix[mid] <= t) lo_b = mid; else hi_b = mid - 1;
     }
     int b = lo_b;
-    int nb = prefix[b + 1] - prefix[b];
+    int nb = prefix[b + 1] - prefix[b];  // phantoms included
     long long rem = t - (long long)Hkv * prefix[b];
     int h = (int)(rem / nb);
     int blk = (int)(rem - (long long)h * nb);
     int n_units = 0;
     while (t < hi) {
         const int n = (int)min((long long)(nb - blk), hi - t);
-        if (out) {
-            const long long p0 = (long long)Hkv * prefix[b] + (long long)h * nb;  // first tile of this (sequence, head)
-            const int f = static_owner(p0, T, W), l = static_owner(p0 + nb - 1, T, W);
-            // (batch index, first block, blocks, piece | head << 16) (len, pieces, first owner, table row)
-            out[2 * n_units] = make_int4(b, blk, n, (w - f) | (h << 16));
-            out[2 * n_units + 1] = make_int4(a.seq_lens[b], l - f + 1, f, a.seq_ids[b]);
+        if (blk + n > oc) {  // the piece holds real tiles: blocks [max(blk, oc) - oc, blk + n - oc)
+            if (out) {
+                const long long p0 = (long long)Hkv * prefix[b] + (long long)h * nb;  // first tile of this (sequence, head)
+                const int f = static_owner(p0 + oc, T, W), l = static_owner(p0 + nb - 1, T, W);
+                const int first = max(blk, oc) - oc;
+                // (batch index, first block, blocks, piece | head << 16) (len, pieces, first owner, table row)
+                out[2 * n_units] = make_int4(b, first, blk + n - oc - first, (w - f) | (h << 16));
+                out[2 * n_units + 1] = make_int4(a.seq_lens[b], l - f + 1, f, a.seq_ids[b]);
+            }
+            ++n_units;
         }
-        ++n_units;
         t += n;
         blk += n;
         if (blk == nb) {
@@ -310,21 +321,31 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(const PlanArgs a) {
 
     // ---- static deal: taken when some sequence would have to be cut anyway (a cut costs partial rows and a merge
     // either way; equal ranges then make every worker finish together, which chunks of a fixed size do not)
-    const long long T = (long long)s_total_blocks * a.num_kv_heads;
+    __shared__ int s_nonempty;
+    if (tid == 0) s_nonempty = 0;
+    __syncthreads();
+    {
+        int mine = 0;
+        for (int b = tid; b < batch; b += blockDim.x) mine += a.seq_lens[b] > 0;
+        if (mine) atomicAdd(&s_nonempty, mine);
+    }
+    __syncthreads();
+    // tiles of the launch, the phantom tiles in front of every non-empty (sequence, head) included
+    const long long T = ((long long)s_total_blocks + (long long)s_nonempty * a.unit_cost) * a.num_kv_heads;
     int W = a.workers;
     if ((long long)W > T) W = (int)T;
     if (W > a.cap_rows / (2 * a.group)) W = a.cap_rows / (2 * a.group);
     const bool cuts = s_max_blocks > chunk;
     if (((a.static_mode == 1 && cuts) || a.static_mode == 2) && W >= 1 &&
         (long long)batch * a.num_kv_heads + W <= a.cap_units && a.num_kv_heads < 32768) {
-        int *prefix = reinterpret_cast<int *>(items_tmp);  // blocks before sequence b; [batch] = all
+        int *prefix = reinterpret_cast<int *>(items_tmp);  // tiles of one head before sequence b; [batch] = all
         int carry = 0;
         for (int base = 0; base < batch; base += blockDim.x) {
             const int b = base + tid;
             int nblk = 0;
             if (b < batch) {
                 const int len = a.seq_lens[b];
-                nblk = len > 0 ? (len + block_size - 1) / block_size : 0;
+                nblk = len > 0 ? (len + block_size - 1) / block_size + a.unit_cost : 0;
             }
             int tot;
             const int off = plan_scan(nblk, tot, warp_sums);
@@ -518,12 +539,18 @@ struct AttnParams {
     int n_out;
     int64_t out_row_stride;
     int64_t out_col_off;
+    // "My slice has landed" signals for pushed outputs: when the launch's last store is done, `epoch` is written to
+    // ready[0..n_ready) - one word per destination, in the destination GPU's memory - after a system-wide fence.
+    int32_t *ready[8];
+    int n_ready;
+    int32_t epoch;
     const __half *k_new;  // fused append: [batch, Hkv, D] rows of the newest token, or nullptr
     const __half *v_new;
     // fused rotary embedding: cos/sin rows [batch, 64] of the newest token's position, or nullptr.  q and the
     // k_new row are then rotated on their way in (q in the A fragments, k_new before it is patched and stored).
     const __half *rope_cos;
     const __half *rope_sin;
+    int rope_fused;  // rounding of the rotation: as the compiled reference kernel (1) or operation by operation (0)
     const int32_t *block_table;
     int64_t table_stride;
     const int32_t *seq_ids;
@@ -671,7 +698,14 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
     const uint32_t bars = smem_u32(smem) + WARPS * STAGES * kStageBytes + warp * (STAGES * 8);
 
     WsHeader *hdr = p.hdr;
-    if (hdr->magic != kMagic || hdr->batch != p.batch) {  // no plan for this batch: refuse, touch nothing
+    // Everything the plan left for this launch, requested in ONE round trip before any of it is looked at: the
+    // header's first and third 16 bytes (magic, batch, n_items, chunk | cap_items, mode, n_workers, n_units) and,
+    // for the static deal, this worker's range of unit records.
+    const int wid = warp * (int)gridDim.x + (int)blockIdx.x;  // consecutive workers sit on different SMs
+    const int4 hdr_a = __ldcg(reinterpret_cast<const int4 *>(hdr));
+    const int4 hdr_c = __ldcg(reinterpret_cast<const int4 *>(&hdr->cap_items));
+    const unsigned range_lo = (unsigned)__ldcg(p.wstart + wid), range_hi = (unsigned)__ldcg(p.wstart + wid + 1);
+    if ((unsigned)hdr_a.x != kMagic || hdr_a.y != p.batch) {  // no plan for this batch: refuse, touch nothing
         if (threadIdx.x == 0) atomicOr(&hdr->error_flags, 2);
         return;
     }
@@ -689,19 +723,25 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
     }
     const int Hkv = p.pool.num_kv_heads;
     const int G = p.group;
-    const bool static_deal = hdr->mode == 1;
-    // worker number: consecutive workers sit on different SMs, so a launch with fewer ranges than workers spreads out
-    const int wid = warp * (int)gridDim.x + (int)blockIdx.x;
-    if (static_deal && (int)(gridDim.x * WARPS) < hdr->n_workers) {  // planned for more workers than this launch has
+    const bool static_deal = hdr_c.y == 1;
+    if (static_deal && (int)(gridDim.x * WARPS) < hdr_c.z) {  // planned for more workers than this launch has
         if (threadIdx.x == 0) atomicOr(&hdr->error_flags, 2);
         return;
     }
-    unsigned my_next = 0, my_end = 0;  // static deal: this worker's unit records
-    if (static_deal) {
-        my_next = (unsigned)__ldg(p.wstart + wid);
-        my_end = (unsigned)__ldg(p.wstart + wid + 1);
-    }
-    const unsigned total_units = static_deal ? my_end : (unsigned)hdr->n_items * (unsigned)Hkv;
+    // static deal: this worker's unit records are [my_next, my_end).  Lane l keeps record win_base + l in registers
+    // (a window of 32 records, refilled when it runs out), so that claiming a unit is a shuffle, not a load.
+    unsigned my_next = static_deal ? range_lo : 0u, my_end = static_deal ? range_hi : 0u;
+    unsigned win_base = my_next;
+    int4 win_a = make_int4(0, 0, 0, 0), win_b = make_int4(0, 0, 0, 0);
+    auto load_window = [&]() {
+        const unsigned i = win_base + (unsigned)lane;
+        if (i < my_end) {
+            win_a = __ldg(p.items + 2 * (size_t)i);
+            win_b = __ldg(p.items + 2 * (size_t)i + 1);
+        }
+    };
+    if (static_deal) load_window();
+    const unsigned total_units = static_deal ? my_end : (unsigned)hdr_a.z * (unsigned)Hkv;
     const bool row0 = g < G, row1 = HI && (g + 8) < G;
 
     // Claiming the next unit is a chain of three dependent global accesses (counter ->
@@ -711,11 +751,32 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
     unsigned f_idx = 0;
     int4 f_it = make_int4(0, 0, 0, 0), f_it1 = make_int4(0, 0, 0, 0);
     auto fetch_step = [&](WorkMeta &m) {
+        if (fstage == 0 && static_deal) {
+            // the record comes out of the window by shuffle; only the block ids are fetched (asynchronously: they
+            // are first used when this unit's tiles are requested)
+            const unsigned idx = my_next++;
+            m.valid = idx < my_end;
+            if (m.valid) {
+                if (idx >= win_base + 32u) {
+                    win_base = idx;
+                    load_window();
+                }
+                const int src = (int)(idx - win_base);
+                f_it.x = __shfl_sync(0xffffffffu, win_a.x, src);
+                f_it.y = __shfl_sync(0xffffffffu, win_a.y, src);
+                f_it.z = __shfl_sync(0xffffffffu, win_a.z, src);
+                f_it.w = __shfl_sync(0xffffffffu, win_a.w, src);
+                f_it1.x = __shfl_sync(0xffffffffu, win_b.x, src);
+                f_it1.y = __shfl_sync(0xffffffffu, win_b.y, src);
+                f_it1.z = __shfl_sync(0xffffffffu, win_b.z, src);
+                f_it1.w = __shfl_sync(0xffffffffu, win_b.w, src);
+                fstage = 2;
+            } else {
+                fstage = 3;
+            }
+        }
         if (fstage == 0) {
-            if (static_deal)
-                f_idx = my_next++;
-            else if (lane == 0)
-                f_idx = atomicAdd(&hdr->work_counter, 1u);
+            if (lane == 0) f_idx = atomicAdd(&hdr->work_counter, 1u);
             fstage = 1;
         } else if (fstage == 1) {
             const unsigned idx = __shfl_sync(0xffffffffu, f_idx, 0);
@@ -723,7 +784,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
             if (!m.valid) {
                 fstage = 3;
             } else {
-                const unsigned bc = static_deal ? idx : idx / (unsigned)Hkv;
+                const unsigned bc = idx / (unsigned)Hkv;
                 m.h = (int)(idx - bc * (unsigned)Hkv);
                 f_it = __ldg(p.items + 2 * bc);       // (batch index, first block, blocks, chunk index)
                 f_it1 = __ldg(p.items + 2 * bc + 1);  // (len, chunks, partial row, table row)
@@ -853,11 +914,12 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
                 for (int kk = 0; kk < 4; ++kk) {
                     const uint32_t c0 = __ldg(cb + kk * 8), c1 = __ldg(cb + kk * 8 + 4);
                     const uint32_t s0 = __ldg(sb + kk * 8), s1 = __ldg(sb + kk * 8 + 4);
-                    rope_rotate2(qf[kk][0], qf[kk + 4][0], c0, s0);
-                    rope_rotate2(qf[kk][2], qf[kk + 4][2], c1, s1);
+                    const bool rf = p.rope_fused != 0;
+                    rope_rotate2(qf[kk][0], qf[kk + 4][0], c0, s0, rf);
+                    rope_rotate2(qf[kk][2], qf[kk + 4][2], c1, s1, rf);
                     if (HI) {
-                        rope_rotate2(qf[kk][1], qf[kk + 4][1], c0, s0);
-                        rope_rotate2(qf[kk][3], qf[kk + 4][3], c1, s1);
+                        rope_rotate2(qf[kk][1], qf[kk + 4][1], c0, s0, rf);
+                        rope_rotate2(qf[kk][3], qf[kk + 4][3], c1, s1, rf);
                     }
                 }
             }
@@ -887,7 +949,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
                     const uint4 c = __ldg(reinterpret_cast<const uint4 *>(p.rope_cos + off));
                     const uint4 sn = __ldg(reinterpret_cast<const uint4 *>(p.rope_sin + off));
                     uint4 lo = lane < 8 ? new_row : other, hi = lane < 8 ? other : new_row;
-                    rope_rotate8(lo, hi, c, sn);
+                    rope_rotate8(lo, hi, c, sn, p.rope_fused != 0);
                     new_row = lane < 8 ? lo : hi;
                 }
             }
@@ -895,7 +957,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
 
         // The next unit is claimed late (kClaimAhead tiles before this one ends, or now if it is
         // that short): a warp that holds an unstarted unit for long hurts the longest-first balance.
-        const int claim_at = max(cur.nblk - kClaimAhead, 0);
+        // (With the static deal the order of units is fixed, so the next one is claimed at once: its block ids and
+        // first tiles are then on their way even when this unit is a single tile.)
+        const int claim_at = static_deal ? 0 : max(cur.nblk - kClaimAhead, 0);
 
         float oacc[16][4];
 #pragma unroll
@@ -1135,6 +1199,10 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
         }
     }
     if (!TMA) cp_async_wait<0>();
+    if (p.n_ready) {  // this warp's output stores (possibly into other GPUs) are visible everywhere before it counts as done
+        __threadfence_system();
+        __syncwarp();
+    }
     // the last worker to run dry re-arms the counters for the next launch
     if (lane == 0) {
         const unsigned workers = gridDim.x * WARPS;
@@ -1142,7 +1210,34 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
         if (d == workers - 1) {
             hdr->work_counter = 0;
             hdr->done_counter = 0;
+            if (p.n_ready) {  // every worker's stores are behind its fence and its count: tell the destinations
+                __threadfence_system();
+                for (int i = 0; i < p.n_ready; ++i) *reinterpret_cast<volatile int32_t *>(p.ready[i]) = p.epoch;
+            }
         }
+    }
+}
+
+// ------------------------------------------------------------------ waiting for pushed outputs
+// One warp; lane r polls flags[r] until it has reached `epoch` (flags only grow; the comparison survives wrap-around)
+// or `timeout_ns` have passed, in which case bit r of *status is set.  Never waits longer than the timeout: a rank
+// that does not signal costs its peers that much time and an error bit, not a hang.
+__global__ void wait_ready_kernel(const int32_t *flags, int n, int32_t epoch, long long timeout_ns, int32_t *status) {
+    const int lane = threadIdx.x;
+    if (lane >= n) return;
+    unsigned long long t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (;;) {
+        int32_t v;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flags + lane) : "memory");
+        if ((int32_t)(v - epoch) >= 0) return;
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        if ((long long)(t - t0) > timeout_ns) {
+            atomicOr(status, 1 << lane);
+            return;
+        }
+        __nanosleep(200);
     }
 }
 
@@ -1345,6 +1440,7 @@ static void launch_plan(char *ws, const WsLayout &L, const int32_t *seq_lens, co
     // the static deal exists in the tensor-core kernel only (fp16, head_dim 128, block 16, groups of up to 16)
     const bool fast_shape = block_size == kBS && num_q_heads % num_kv_heads == 0 && a.group <= 16;
     a.static_mode = fast_shape ? tuning().static_mode.load(std::memory_order_relaxed) : 0;
+    a.unit_cost = tuning().unit_cost.load(std::memory_order_relaxed);
     a.balance = plan_balance(sm_count, num_kv_heads);
     attn_plan_kernel<<<1, 1024, 0, s>>>(a);
 }
@@ -1399,6 +1495,9 @@ struct OutputSpec {  // where the attention result goes (see AttnParams::out)
     void *const *ptrs;
     int n;
     int64_t row_stride, col_off;
+    int32_t *const *ready;  // may be null: no signal
+    int n_ready;
+    int32_t epoch;
 };
 
 static int attention_decode_impl(int device, void *stream, const void *q, void *o, const OutputSpec *push,
@@ -1469,11 +1568,18 @@ static int attention_decode_impl(int device, void *stream, const void *q, void *
     AttnParams p;
     p.pool = pv;
     p.q = (const __half *)q;
+    p.n_ready = 0;
+    p.epoch = 0;
     if (push) {
         p.n_out = push->n;
         for (int i = 0; i < push->n; ++i) p.out[i] = (__half *)push->ptrs[i];
         p.out_row_stride = push->row_stride;
         p.out_col_off = push->col_off;
+        if (push->ready) {
+            p.n_ready = push->n_ready;
+            for (int i = 0; i < push->n_ready; ++i) p.ready[i] = push->ready[i];
+            p.epoch = push->epoch;
+        }
     } else {
         p.n_out = 1;
         p.out[0] = (__half *)o;
@@ -1484,6 +1590,7 @@ static int attention_decode_impl(int device, void *stream, const void *q, void *
     p.v_new = (const __half *)v_new;
     p.rope_cos = (const __half *)rope_cos;
     p.rope_sin = (const __half *)rope_sin;
+    p.rope_fused = rope_fused_rounding() ? 1 : 0;
     p.block_table = block_table;
     p.table_stride = table_stride;
     p.seq_ids = seq_ids;
@@ -1536,13 +1643,18 @@ int mkv_paged_attention_decode_rope_append(int device, void *stream, void *q, vo
 }
 
 int mkv_paged_attention_decode_push(int device, void *stream, const void *q, void *const *out_ptrs, int n_out,
-                                    int64_t out_row_stride, int64_t out_col_offset, const void *k_new,
+                                    int64_t out_row_stride, int64_t out_col_offset, int32_t *const *ready_ptrs,
+                                    int n_ready, int32_t epoch, const void *k_new,
                                     const void *v_new, const mkv_pool *pool, const int32_t *block_table,
                                     int64_t table_stride, const int32_t *seq_ids, const int32_t *seq_lens, int batch,
                                     int num_q_heads, int cur_layer, float softmax_scale,
                                     int max_blocks_per_seq_in_batch, void *workspace, size_t workspace_bytes) {
-    if (n_out < 1 || n_out > 8) return MKV_ERR_SHAPE;
-    if (!out_ptrs) return MKV_ERR_NULL;
+    if (n_out < 1 || n_out > 8 || n_ready < 0 || n_ready > 8) return MKV_ERR_SHAPE;
+    if (!out_ptrs || (n_ready > 0 && !ready_ptrs)) return MKV_ERR_NULL;
+    for (int i = 0; i < n_ready; ++i) {
+        if (!ready_ptrs[i]) return MKV_ERR_NULL;
+        if (((uintptr_t)ready_ptrs[i]) % 4 != 0) return MKV_ERR_ALIGN;
+    }
     if (out_row_stride < (int64_t)num_q_heads * 128 + out_col_offset || out_col_offset < 0) return MKV_ERR_SHAPE;
     if ((out_row_stride % 8) != 0 || (out_col_offset % 8) != 0) return MKV_ERR_ALIGN;
     for (int i = 0; i < n_out; ++i) {
@@ -1553,10 +1665,23 @@ int mkv_paged_attention_decode_push(int device, void *stream, const void *q, voi
     int st = validate_pool(pool, &pv);
     if (st) return st;
     if (!fast_path_ok(pv, num_q_heads, q, out_ptrs[0])) return MKV_ERR_SHAPE;  // fp16, head_dim 128, block 16 only
-    OutputSpec spec{out_ptrs, n_out, out_row_stride, out_col_offset};
+    OutputSpec spec{out_ptrs, n_out, out_row_stride, out_col_offset, n_ready > 0 ? ready_ptrs : nullptr, n_ready, epoch};
     return attention_decode_impl(device, stream, q, out_ptrs[0], &spec, k_new, v_new, pool, block_table,
                                  table_stride, seq_ids, seq_lens, batch, num_q_heads, cur_layer, softmax_scale,
                                  max_blocks_per_seq_in_batch, workspace, workspace_bytes);
+}
+
+int mkv_wait_ready(int device, void *stream, const int32_t *flags, int n, int32_t epoch, int64_t timeout_ns,
+                   int32_t *status) {
+    if (n < 0 || n > 32 || timeout_ns < 0) return MKV_ERR_SHAPE;
+    if (n == 0) return MKV_OK;
+    if (!flags || !status) return MKV_ERR_NULL;
+    if (timeout_ns > 2000000000ll) timeout_ns = 2000000000ll;  // two seconds at most, whatever the caller asks for
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
+    wait_ready_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(flags, n, epoch, (long long)timeout_ns, status);
+    MKV_LAUNCH_CHECK();
+    return MKV_OK;
 }
 
 int mkv_attn_configure(int warps, int stages, double item_factor_value, double split_balance_value, int loader) {
@@ -1585,9 +1710,10 @@ int mkv_attn_workspace_layout(int device, int batch, int num_q_heads, int num_kv
     return MKV_OK;
 }
 
-int mkv_attn_set_static_deal(int mode) {
-    if (mode < 0 || mode > 2) return MKV_ERR_RANGE;
-    tuning().static_mode.store(mode, std::memory_order_relaxed);
+int mkv_attn_set_static_deal(int mode, int unit_cost) {
+    if (mode > 2 || unit_cost > 64) return MKV_ERR_RANGE;
+    if (mode >= 0) tuning().static_mode.store(mode, std::memory_order_relaxed);
+    if (unit_cost >= 0) tuning().unit_cost.store(unit_cost, std::memory_order_relaxed);
     return MKV_OK;
 }
 
@@ -1705,10 +1831,13 @@ int mkv_paged_attention_decode_noalloc(int device, void *stream, const void *q, 
     p.out[0] = (__half *)o;
     p.out_row_stride = (int64_t)num_q_heads * kD;
     p.out_col_off = 0;
+    p.n_ready = 0;
+    p.epoch = 0;
     p.k_new = nullptr;
     p.v_new = nullptr;
     p.rope_cos = nullptr;
     p.rope_sin = nullptr;
+    p.rope_fused = 0;
     p.block_table = block_table;
     p.table_stride = table_stride;
     p.seq_ids = seq_ids;

@@ -40,7 +40,7 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int &total, int *warp
 __global__ void __launch_bounds__(kThreads) block_need_kernel(const int32_t *__restrict__ num_allocated,
                                                             const int32_t *__restrict__ seq_ids,
                                                             const int32_t *__restrict__ target_lens, int batch,
-                                                            int block_size, int32_t *__restrict__ need,
+                                                            int block_size, int num_rows, int32_t *__restrict__ need,
                                                             int64_t *__restrict__ totals) {
     __shared__ long long s_sum;
     __shared__ int s_neg;
@@ -53,7 +53,13 @@ __global__ void __launch_bounds__(kThreads) block_need_kernel(const int32_t *__r
     int neg = 0;
     for (int i = threadIdx.x; i < batch; i += blockDim.x) {
         int target = (target_lens[i] + (block_size - 1)) / block_size;
-        int n = target - num_allocated[seq_ids[i]];
+        const int s = seq_ids[i];
+        if ((unsigned)s >= (unsigned)num_rows) {  // no such row: nothing is needed for it, reported like a shrink
+            need[i] = 0;
+            ++neg;
+            continue;
+        }
+        int n = target - num_allocated[s];
         need[i] = n;
         sum += n;
         neg += (n < 0);
@@ -124,7 +130,7 @@ __global__ void __launch_bounds__(kThreads) block_allocate_kernel(
     int32_t *__restrict__ num_allocated, int32_t *__restrict__ block_table, int64_t table_stride,
     const int32_t *__restrict__ seq_ids, const int32_t *__restrict__ target_lens, int batch, int block_size,
     uint8_t *__restrict__ bitmap, int64_t num_blocks, int32_t *__restrict__ need, int64_t *__restrict__ ids,
-    int64_t ids_capacity, int64_t *__restrict__ status) {
+    int64_t ids_capacity, int64_t *__restrict__ status, int num_rows) {
     __shared__ int warp_sums[33];
     __shared__ long long s_sum;
     __shared__ int s_neg, s_full;
@@ -137,7 +143,13 @@ __global__ void __launch_bounds__(kThreads) block_allocate_kernel(
     long long sum = 0;
     int neg = 0, full = 0;
     for (int i = threadIdx.x; i < batch; i += blockDim.x) {
-        const int have = num_allocated[seq_ids[i]];
+        const int s = seq_ids[i];
+        if ((unsigned)s >= (unsigned)num_rows) {  // a sequence id without a row: the whole request is refused
+            need[i] = 0;
+            ++full;
+            continue;
+        }
+        const int have = num_allocated[s];
         const int n = (target_lens[i] + (block_size - 1)) / block_size - have;
         need[i] = n;
         sum += n;
@@ -220,7 +232,8 @@ __global__ void __launch_bounds__(kThreads) block_table_set_kernel(int32_t *__re
                                                                  int64_t table_stride,
                                                                  const int64_t *__restrict__ candidates,
                                                                  const int32_t *__restrict__ seq_ids,
-                                                                 const int32_t *__restrict__ need, int batch) {
+                                                                 const int32_t *__restrict__ need, int batch,
+                                                                 int num_rows) {
     __shared__ int warp_sums[33];
     int64_t carry = 0;
     for (int base = 0; base < batch; base += kThreads) {
@@ -228,13 +241,13 @@ __global__ void __launch_bounds__(kThreads) block_table_set_kernel(int32_t *__re
         int n = (i < batch) ? max(need[i], 0) : 0;
         int total;
         int off = block_exclusive_scan(n, total, warp_sums);
-        if (i < batch && n > 0) {
+        if (i < batch && n > 0 && (unsigned)seq_ids[i] < (unsigned)num_rows) {
             const int64_t s = seq_ids[i];
             const int have = num_allocated[s];
-            int room = (int)min((int64_t)n, table_stride - have);  // never write past the row
+            int room = (int)max((int64_t)0, min((int64_t)n, table_stride - have));  // never write past the row
             for (int j = 0; j < room; ++j)
                 block_table[s * table_stride + have + j] = (int32_t)candidates[carry + off + j];
-            num_allocated[s] = have + n;
+            num_allocated[s] = have + room;  // the count never names columns the row does not have
         }
         carry += total;
     }
@@ -247,16 +260,17 @@ __global__ void __launch_bounds__(kThreads) block_table_unset_kernel(int32_t *__
                                                                    uint8_t *__restrict__ is_block_free,
                                                                    int64_t num_blocks, int32_t *__restrict__ gathered,
                                                                    int64_t gathered_capacity,
-                                                                   int64_t *__restrict__ total_out, int accumulate) {
+                                                                   int64_t *__restrict__ total_out, int accumulate,
+                                                                   int num_rows) {
     __shared__ int warp_sums[33];
     int64_t carry = 0;
     for (int base = 0; base < batch; base += kThreads) {
         const int i = base + threadIdx.x;
         int64_t s = 0;
         int n = 0;
-        if (i < batch) {
+        if (i < batch && (unsigned)seq_ids[i] < (unsigned)num_rows) {
             s = seq_ids[i];
-            n = num_allocated[s];
+            n = (int)min((int64_t)max(num_allocated[s], 0), table_stride);  // a row holds table_stride columns
         }
         int total;
         int off = block_exclusive_scan(n, total, warp_sums);
@@ -270,18 +284,20 @@ __global__ void __launch_bounds__(kThreads) block_table_unset_kernel(int32_t *__
         carry += total;
     }
     __syncthreads();  // every count was read before any is cleared (duplicate ids in a batch)
-    for (int i = threadIdx.x; i < batch; i += blockDim.x) num_allocated[seq_ids[i]] = 0;
+    for (int i = threadIdx.x; i < batch; i += blockDim.x)
+        if ((unsigned)seq_ids[i] < (unsigned)num_rows) num_allocated[seq_ids[i]] = 0;
     if (threadIdx.x == 0 && total_out) *total_out = accumulate ? *total_out + carry : carry;
 }
 
 __global__ void __launch_bounds__(kThreads) block_table_count_kernel(const int32_t *__restrict__ num_allocated,
                                                                    const int32_t *__restrict__ seq_ids, int batch,
-                                                                   int64_t *__restrict__ total_out) {
+                                                                   int64_t *__restrict__ total_out, int num_rows) {
     __shared__ long long s_sum;
     if (threadIdx.x == 0) s_sum = 0;
     __syncthreads();
     long long sum = 0;
-    for (int i = threadIdx.x; i < batch; i += blockDim.x) sum += num_allocated[seq_ids[i]];
+    for (int i = threadIdx.x; i < batch; i += blockDim.x)
+        if ((unsigned)seq_ids[i] < (unsigned)num_rows) sum += num_allocated[seq_ids[i]];
     for (int d = 16; d > 0; d >>= 1) sum += __shfl_down_sync(0xffffffffu, sum, d);
     if ((threadIdx.x & 31) == 0) atomicAdd((unsigned long long *)&s_sum, (unsigned long long)sum);
     __syncthreads();
@@ -294,24 +310,25 @@ using namespace mkv;
 
 extern "C" {
 
-int mkv_block_need(int device, void *stream, const int32_t *num_allocated, const int32_t *seq_ids,
+int mkv_block_need(int device, void *stream, const int32_t *num_allocated, int num_rows, const int32_t *seq_ids,
                    const int32_t *target_lens, int batch, int block_size, int32_t *need, int64_t *totals) {
-    if (batch < 0 || block_size < 1) return MKV_ERR_SHAPE;
+    if (batch < 0 || block_size < 1 || num_rows < 0) return MKV_ERR_SHAPE;
     if (!totals) return MKV_ERR_NULL;
     if (batch > 0 && (!num_allocated || !seq_ids || !target_lens || !need)) return MKV_ERR_NULL;
     DeviceGuard guard(device);
     if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
     block_need_kernel<<<1, kThreads, 0, (cudaStream_t)stream>>>(num_allocated, seq_ids, target_lens, batch,
-                                                               block_size, need, totals);
+                                                               block_size, num_rows, need, totals);
     MKV_LAUNCH_CHECK();
     return MKV_OK;
 }
 
-int mkv_block_allocate(int device, void *stream, int32_t *num_allocated, int32_t *block_table, int64_t table_stride,
-                       const int32_t *seq_ids, const int32_t *target_lens, int batch, int block_size,
+int mkv_block_allocate(int device, void *stream, int32_t *num_allocated, int num_rows, int32_t *block_table,
+                       int64_t table_stride, const int32_t *seq_ids, const int32_t *target_lens, int batch, int block_size,
                        uint8_t *bitmap, int64_t num_blocks, int32_t *need, int64_t *ids, int64_t ids_capacity,
                        int64_t *status) {
-    if (batch < 0 || block_size < 1 || table_stride < 1 || num_blocks < 0 || ids_capacity < 0) return MKV_ERR_SHAPE;
+    if (batch < 0 || block_size < 1 || table_stride < 1 || num_blocks < 0 || ids_capacity < 0 || num_rows < 0)
+        return MKV_ERR_SHAPE;
     if (!status) return MKV_ERR_NULL;
     if (batch == 0) return MKV_OK;
     if (!num_allocated || !block_table || !seq_ids || !target_lens || !need) return MKV_ERR_NULL;
@@ -320,7 +337,7 @@ int mkv_block_allocate(int device, void *stream, int32_t *num_allocated, int32_t
     if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
     block_allocate_kernel<<<1, kThreads, 0, (cudaStream_t)stream>>>(num_allocated, block_table, table_stride, seq_ids,
                                                                    target_lens, batch, block_size, bitmap, num_blocks,
-                                                                   need, ids, ids_capacity, status);
+                                                                   need, ids, ids_capacity, status, num_rows);
     MKV_LAUNCH_CHECK();
     return MKV_OK;
 }
@@ -351,25 +368,25 @@ int mkv_bitmap_scatter(int device, void *stream, uint8_t *bitmap, int64_t bitmap
     return MKV_OK;
 }
 
-int mkv_block_table_set(int device, void *stream, int32_t *num_allocated, int32_t *block_table,
+int mkv_block_table_set(int device, void *stream, int32_t *num_allocated, int num_rows, int32_t *block_table,
                         int64_t table_stride, const int64_t *candidates, const int32_t *seq_ids,
                         const int32_t *need, int batch) {
-    if (batch < 0 || table_stride < 1) return MKV_ERR_SHAPE;
+    if (batch < 0 || table_stride < 1 || num_rows < 0) return MKV_ERR_SHAPE;
     if (batch == 0) return MKV_OK;
     if (!num_allocated || !block_table || !candidates || !seq_ids || !need) return MKV_ERR_NULL;
     DeviceGuard guard(device);
     if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
     block_table_set_kernel<<<1, kThreads, 0, (cudaStream_t)stream>>>(num_allocated, block_table, table_stride,
-                                                                    candidates, seq_ids, need, batch);
+                                                                    candidates, seq_ids, need, batch, num_rows);
     MKV_LAUNCH_CHECK();
     return MKV_OK;
 }
 
-int mkv_block_table_unset(int device, void *stream, int32_t *num_allocated, const int32_t *block_table,
+int mkv_block_table_unset(int device, void *stream, int32_t *num_allocated, int num_rows, const int32_t *block_table,
                           int64_t table_stride, const int32_t *seq_ids, int batch, uint8_t *is_block_free,
                           int64_t num_blocks, int32_t *gathered, int64_t gathered_capacity, int64_t *total_out,
                           int accumulate) {
-    if (batch < 0 || table_stride < 1 || num_blocks < 0 || gathered_capacity < 0) return MKV_ERR_SHAPE;
+    if (batch < 0 || table_stride < 1 || num_blocks < 0 || gathered_capacity < 0 || num_rows < 0) return MKV_ERR_SHAPE;
     if (batch == 0) return MKV_OK;
     if (!num_allocated || !block_table || !seq_ids || !is_block_free) return MKV_ERR_NULL;
     DeviceGuard guard(device);
@@ -377,19 +394,20 @@ int mkv_block_table_unset(int device, void *stream, int32_t *num_allocated, cons
     block_table_unset_kernel<<<1, kThreads, 0, (cudaStream_t)stream>>>(num_allocated, block_table, table_stride,
                                                                       seq_ids, batch, is_block_free, num_blocks,
                                                                       gathered, gathered_capacity, total_out,
-                                                                      accumulate);
+                                                                      accumulate, num_rows);
     MKV_LAUNCH_CHECK();
     return MKV_OK;
 }
 
-int mkv_block_table_count(int device, void *stream, const int32_t *num_allocated, const int32_t *seq_ids,
-                          int batch, int64_t *total_out) {
-    if (batch < 0) return MKV_ERR_SHAPE;
+int mkv_block_table_count(int device, void *stream, const int32_t *num_allocated, int num_rows,
+                          const int32_t *seq_ids, int batch, int64_t *total_out) {
+    if (batch < 0 || num_rows < 0) return MKV_ERR_SHAPE;
     if (!total_out) return MKV_ERR_NULL;
     if (batch > 0 && (!num_allocated || !seq_ids)) return MKV_ERR_NULL;
     DeviceGuard guard(device);
     if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
-    block_table_count_kernel<<<1, kThreads, 0, (cudaStream_t)stream>>>(num_allocated, seq_ids, batch, total_out);
+    block_table_count_kernel<<<1, kThreads, 0, (cudaStream_t)stream>>>(num_allocated, seq_ids, batch, total_out,
+                                                                      num_rows);
     MKV_LAUNCH_CHECK();
     return MKV_OK;
 }

@@ -1,17 +1,31 @@
 // Rotary position embedding of q and k in place, the step in front of the KV
 // append.  Element-wise, HBM/latency bound.  Follows the reference kernel's
 // arithmetic (worker/kernels/rotary_emb.py:7-41): the halves [0, D/2) and
-// [D/2, D) of every head rotate as (x0*cos - x1*sin, x0*sin + x1*cos); with fp16
-// data every product and every sum is rounded to fp16 on its own, so the
-// intrinsics below are the non-fusing ones.
+// [D/2, D) of every head rotate as (x0*cos - x1*sin, x0*sin + x1*cos), rounded
+// either as the compiled reference kernel rounds (default) or operation by
+// operation, as its source reads; see rope.cuh.
+#include <atomic>
+#include <stdlib.h>
+
 #include "rope.cuh"
 
 namespace mkv {
 
+static std::atomic<int> g_rope_fused{-1};
+bool rope_fused_rounding() {
+    int v = g_rope_fused.load(std::memory_order_relaxed);
+    if (v < 0) {
+        const char *e = getenv("MKV_ROPE_ROUNDING");  // "written" = every operation rounds; default: as compiled
+        v = (e && e[0] == 'w') ? 0 : 1;
+        g_rope_fused.store(v, std::memory_order_relaxed);
+    }
+    return v != 0;
+}
+
 // fp16 rows: one thread per 8-element piece of the low half of one head (16-byte loads).
 __global__ void rope_f16_kernel(__half *__restrict__ q, __half *__restrict__ k, const __half *__restrict__ cos_t,
                                 const __half *__restrict__ sin_t, int64_t num_tokens, int num_q_heads,
-                                int num_kv_heads, int head_dim) {
+                                int num_kv_heads, int head_dim, bool fused) {
     const int half_dim = head_dim >> 1;
     const int pieces = half_dim >> 3;
     const int heads = num_q_heads + num_kv_heads;
@@ -28,7 +42,7 @@ __global__ void rope_f16_kernel(__half *__restrict__ q, __half *__restrict__ k, 
         uint4 x1 = *reinterpret_cast<const uint4 *>(row + half_dim + piece * 8);
         const uint4 c = __ldg(reinterpret_cast<const uint4 *>(cos_t + tok * half_dim + piece * 8));
         const uint4 s = __ldg(reinterpret_cast<const uint4 *>(sin_t + tok * half_dim + piece * 8));
-        rope_rotate8(x0, x1, c, s);
+        rope_rotate8(x0, x1, c, s, fused);
         *reinterpret_cast<uint4 *>(row + piece * 8) = x0;
         *reinterpret_cast<uint4 *>(row + half_dim + piece * 8) = x1;
     }
@@ -39,7 +53,7 @@ __global__ void rope_f16_kernel(__half *__restrict__ q, __half *__restrict__ k, 
 template <typename T>
 __global__ void rope_scalar_kernel(T *__restrict__ q, T *__restrict__ k, const __half *__restrict__ cos_t,
                                    const __half *__restrict__ sin_t, int64_t num_tokens, int num_q_heads,
-                                   int num_kv_heads, int head_dim) {
+                                   int num_kv_heads, int head_dim, bool fused) {
     const int half_dim = head_dim >> 1;
     const int heads = num_q_heads + num_kv_heads;
     const int64_t total = num_tokens * heads * half_dim;
@@ -54,12 +68,22 @@ __global__ void rope_scalar_kernel(T *__restrict__ q, T *__restrict__ k, const _
         const __half c = cos_t[tok * half_dim + d], s = sin_t[tok * half_dim + d];
         const T x0 = row[d], x1 = row[half_dim + d];
         if constexpr (sizeof(T) == 2) {
-            row[d] = __hsub_rn(__hmul_rn(x0, c), __hmul_rn(x1, s));
-            row[half_dim + d] = __hadd_rn(__hmul_rn(x0, s), __hmul_rn(x1, c));
+            if (fused) {
+                row[d] = __hfma(x0, c, __hneg(__hmul_rn(x1, s)));
+                row[half_dim + d] = __hfma(x0, s, __hmul_rn(x1, c));
+            } else {
+                row[d] = __hsub_rn(__hmul_rn(x0, c), __hmul_rn(x1, s));
+                row[half_dim + d] = __hadd_rn(__hmul_rn(x0, s), __hmul_rn(x1, c));
+            }
         } else {
             const float cf = __half2float(c), sf = __half2float(s);
-            row[d] = __fsub_rn(__fmul_rn(x0, cf), __fmul_rn(x1, sf));
-            row[half_dim + d] = __fadd_rn(__fmul_rn(x0, sf), __fmul_rn(x1, cf));
+            if (fused) {
+                row[d] = __fmaf_rn(x0, cf, -__fmul_rn(x1, sf));
+                row[half_dim + d] = __fmaf_rn(x0, sf, __fmul_rn(x1, cf));
+            } else {
+                row[d] = __fsub_rn(__fmul_rn(x0, cf), __fmul_rn(x1, sf));
+                row[half_dim + d] = __fadd_rn(__fmul_rn(x0, sf), __fmul_rn(x1, cf));
+            }
         }
     }
 }
@@ -90,18 +114,24 @@ extern "C" int mkv_rotary_embedding(int device, void *stream, void *q, void *k, 
     int64_t blocks = ceil_div64(items, threads);
     const int64_t cap = (int64_t)sms * 16;
     if (blocks > cap) blocks = cap;
+    const bool fused = rope_fused_rounding();
     if (vec)
         rope_f16_kernel<<<(unsigned)blocks, threads, 0, s>>>((__half *)q, (__half *)k, (const __half *)cos_table,
                                                             (const __half *)sin_table, num_tokens, num_q_heads,
-                                                            num_kv_heads, head_dim);
+                                                            num_kv_heads, head_dim, fused);
     else if (elem_bytes == 2)
         rope_scalar_kernel<__half><<<(unsigned)blocks, threads, 0, s>>>(
             (__half *)q, (__half *)k, (const __half *)cos_table, (const __half *)sin_table, num_tokens, num_q_heads,
-            num_kv_heads, head_dim);
+            num_kv_heads, head_dim, fused);
     else
         rope_scalar_kernel<float><<<(unsigned)blocks, threads, 0, s>>>(
             (float *)q, (float *)k, (const __half *)cos_table, (const __half *)sin_table, num_tokens, num_q_heads,
-            num_kv_heads, head_dim);
+            num_kv_heads, head_dim, fused);
     MKV_LAUNCH_CHECK();
+    return MKV_OK;
+}
+
+extern "C" int mkv_rope_set_rounding(int as_compiled) {
+    mkv::g_rope_fused.store(as_compiled ? 1 : 0, std::memory_order_relaxed);
     return MKV_OK;
 }

@@ -115,7 +115,8 @@ class BlockManager:
         self.prepare_nosync(seq_ids.shape[0])
         dev, stream = device_and_stream(self.block_table)
         check(lib.mkv_block_allocate(
-            dev, stream, self.num_seq_allocated_blocks.data_ptr(), self.block_table.data_ptr(),
+            dev, stream, self.num_seq_allocated_blocks.data_ptr(), self.num_seq_allocated_blocks.shape[0],
+            self.block_table.data_ptr(),
             self.block_table.stride(0), seq_ids.data_ptr(), target_lens.data_ptr(), seq_ids.shape[0], self.block_size,
             self.is_block_free.data_ptr(), self.is_block_free.shape[0], self._alloc_need.data_ptr(),
             self._alloc_ids.data_ptr(), self._alloc_ids.shape[0], self._alloc_status.data_ptr()),
@@ -131,12 +132,40 @@ class BlockManager:
         self.prepare_nosync(seq_ids.shape[0])
         dev, stream = device_and_stream(self.block_table)
         check(lib.mkv_block_table_unset(dev, stream, self.num_seq_allocated_blocks.data_ptr(),
+                                        self.num_seq_allocated_blocks.shape[0],
                                         self.block_table.data_ptr(), self.block_table.stride(0),
                                         seq_ids.data_ptr(), seq_ids.shape[0], self.is_block_free.data_ptr(),
                                         self.is_block_free.shape[0], None, 0,
                                         self._alloc_status.data_ptr() + 4 * 8, 1), "mkv_block_table_unset")
         self._nosync_pending = True
         self._readback_enqueued = False
+
+    def gather_allocated_blocks_and_free_nosync(self, seq_ids: torch.Tensor, capacity: int = None):
+        """``gather_allocated_blocks_and_free`` without the host round trip that sizes its result
+        (worker/kernels/block_mgmt.py:115-116 reads the block count back to allocate the output): the ids go into a
+        buffer of ``capacity`` entries (default: as many as the sequences' rows could hold, at most the pool) and
+        the number of valid entries stays on the device.  Returns ``(ids, count)``: ``ids`` int32 ``[capacity]``,
+        batch order, entries from ``count`` on are -1; ``count`` int64 ``[1]`` on the device.  The free-block count
+        is folded in by the next ``sync_counters()``.  If the sequences hold more blocks than ``capacity`` the
+        surplus ids are freed but not reported; ``count`` then exceeds ``capacity``."""
+        assert seq_ids.dtype == torch.int32 and seq_ids.is_contiguous()
+        batch = seq_ids.shape[0]
+        if capacity is None:
+            capacity = min(batch * self.block_table.shape[1], self.is_block_free.shape[0])
+        self.prepare_nosync(batch)
+        dev, stream = device_and_stream(self.block_table)
+        ids = torch.full((max(int(capacity), 1),), -1, dtype=torch.int32, device=self.block_table.device)
+        count = torch.zeros((1,), dtype=torch.int64, device=self.block_table.device)
+        check(lib.mkv_block_table_unset(dev, stream, self.num_seq_allocated_blocks.data_ptr(),
+                                        self.num_seq_allocated_blocks.shape[0],
+                                        self.block_table.data_ptr(), self.block_table.stride(0),
+                                        seq_ids.data_ptr(), batch, self.is_block_free.data_ptr(),
+                                        self.is_block_free.shape[0], ids.data_ptr(), int(capacity),
+                                        count.data_ptr(), 0), "mkv_block_table_unset")
+        self._alloc_status[4:5] += count        # the running total of blocks freed without a host round trip
+        self._nosync_pending = True
+        self._readback_enqueued = False
+        return ids[:int(capacity)], count
 
     def prepare_nosync(self, batch: int) -> None:
         """Scratch of the sync-free allocate (status words, need per sequence, id list).  Called by it; call it
@@ -263,6 +292,7 @@ class BlockManager:
         dev, stream = device_and_stream(self.block_table)
         total = torch.empty((1,), dtype=torch.int64, device=self.block_table.device)
         check(lib.mkv_block_table_unset(dev, stream, self.num_seq_allocated_blocks.data_ptr(),
+                                        self.num_seq_allocated_blocks.shape[0],
                                         self.block_table.data_ptr(), self.block_table.stride(0),
                                         seq_ids.data_ptr(), seq_ids.shape[0], self.is_block_free.data_ptr(),
                                         self.is_block_free.shape[0], None, 0, total.data_ptr(), 0),

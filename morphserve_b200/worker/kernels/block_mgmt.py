@@ -23,7 +23,8 @@ def set_block_table_and_num_seq_alloc_blocks(
     dev, stream = device_and_stream(block_table)
     cand = candidate_blocks if candidate_blocks.dtype == torch.int64 else candidate_blocks.to(torch.int64)
     need = block_needed if block_needed.dtype == torch.int32 else block_needed.to(torch.int32)
-    check(lib.mkv_block_table_set(dev, stream, num_seq_allocated_blocks.data_ptr(), block_table.data_ptr(),
+    check(lib.mkv_block_table_set(dev, stream, num_seq_allocated_blocks.data_ptr(),
+                                  num_seq_allocated_blocks.shape[0], block_table.data_ptr(),
                                   block_table.stride(0), cand.contiguous().data_ptr(), seq_ids.data_ptr(),
                                   need.contiguous().data_ptr(), seq_ids.shape[0]), "mkv_block_table_set")
 
@@ -37,7 +38,8 @@ def unset_block_table_and_num_seq_alloc_blocks(
     """Mark the blocks of the given sequences free and zero their counts (rows keep their ids)."""
     require_cuda(block_table, "block_table")
     dev, stream = device_and_stream(block_table)
-    check(lib.mkv_block_table_unset(dev, stream, num_seq_allocated_blocks.data_ptr(), block_table.data_ptr(),
+    check(lib.mkv_block_table_unset(dev, stream, num_seq_allocated_blocks.data_ptr(),
+                                    num_seq_allocated_blocks.shape[0], block_table.data_ptr(),
                                     block_table.stride(0), seq_ids.data_ptr(), seq_ids.shape[0],
                                     is_block_free.data_ptr(), is_block_free.shape[0], None, 0, None, 0),
           "mkv_block_table_unset")
@@ -53,11 +55,13 @@ def gather_allocated_blocks_and_unset(
     require_cuda(block_table, "block_table")
     dev, stream = device_and_stream(block_table)
     total = torch.empty(1, dtype=torch.int64, device=block_table.device)
-    check(lib.mkv_block_table_count(dev, stream, num_seq_allocated_blocks.data_ptr(), seq_ids.data_ptr(),
+    check(lib.mkv_block_table_count(dev, stream, num_seq_allocated_blocks.data_ptr(),
+                                    num_seq_allocated_blocks.shape[0], seq_ids.data_ptr(),
                                     seq_ids.shape[0], total.data_ptr()), "mkv_block_table_count")
     n = int(total.item())       # the result's size is data dependent: one sync, as in the reference (:115-116)
     gathered = torch.empty((n,), dtype=torch.int32, device=block_table.device)
-    check(lib.mkv_block_table_unset(dev, stream, num_seq_allocated_blocks.data_ptr(), block_table.data_ptr(),
+    check(lib.mkv_block_table_unset(dev, stream, num_seq_allocated_blocks.data_ptr(),
+                                    num_seq_allocated_blocks.shape[0], block_table.data_ptr(),
                                     block_table.stride(0), seq_ids.data_ptr(), seq_ids.shape[0],
                                     is_block_free.data_ptr(), is_block_free.shape[0],
                                     gathered.data_ptr(), n, None, 0), "mkv_block_table_unset")

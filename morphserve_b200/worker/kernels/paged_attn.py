@@ -130,11 +130,14 @@ def paged_attention_push(
     out_col_offset: int,            # first column of this rank's slice (= first local query head * head_dim)
     k_new: torch.Tensor = None,     # optional fused append of the newest token's rows [batch, local kv heads, 128]
     v_new: torch.Tensor = None,
+    ready_ptrs=None,                # device addresses of this rank's "slice landed" word on every destination
+    epoch: int = 0,                 # value written there when the launch's last store is done; grows per launch
 ):
     """Decode attention for KV-head sharding (no counterpart in the single-GPU reference): the result is
     stored into the same column slice of every matrix in ``out_ptrs`` - the local one and, through
     peer-mapped pointers, the other ranks' - from inside the kernel, replacing attention + all-gather.
-    The caller runs a barrier across the ranks before anyone reads its matrix."""
+    Before anyone reads its matrix the caller either runs a barrier across the ranks, or passes ``ready_ptrs`` /
+    ``epoch`` and lets every rank ``wait_ready`` for the other ranks' words."""
     assert q.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous() and block_table.is_contiguous()
     require_cuda(q, "q")
     batch = infer_state.num_decoding_seqs
@@ -152,9 +155,23 @@ def paged_attention_push(
     ws = attn_workspace(dev, batch, hq, hkv, d, max_blocks, stream)
     _plan_for(infer_state, ws, dev, stream, lens, seq_ids, batch, hq, hkv, d, bs, max_blocks, cur_layer)
     ptrs = (C.c_void_p * len(out_ptrs))(*[int(x) for x in out_ptrs])
+    n_ready = len(ready_ptrs) if ready_ptrs else 0
+    ready = (C.c_void_p * max(n_ready, 1))(*[int(x) for x in (ready_ptrs or [0])])
     check(lib.mkv_paged_attention_decode_push(
         dev, stream, q.data_ptr(), ptrs, len(out_ptrs), int(out_row_stride), int(out_col_offset),
+        ready if n_ready else None, n_ready, int(epoch),
         k_new.data_ptr() if k_new is not None else None, v_new.data_ptr() if v_new is not None else None,
         pool, block_table.data_ptr(), block_table.stride(0), seq_ids.data_ptr(), lens.data_ptr(), batch, hq,
         cur_layer, float(infer_state.softmax_scale), max_blocks, ws.tensor.data_ptr(), ws.nbytes),
         "mkv_paged_attention_decode_push")
+
+
+def wait_ready(flags: torch.Tensor, epoch: int, status: torch.Tensor, timeout_s: float = 1.0) -> None:
+    """Queue, on the current stream, a bounded wait until every int32 word of ``flags`` (this GPU's memory; word r is
+    written by rank r's ``paged_attention_push``) has reached ``epoch``.  A word that does not arrive within
+    ``timeout_s`` sets its bit in ``status`` (int32 [1] on this GPU, accumulated) and the wait ends."""
+    require_cuda(flags, "flags")
+    assert flags.dtype == torch.int32 and status.dtype == torch.int32 and flags.is_contiguous()
+    dev, stream = device_and_stream(flags)
+    check(lib.mkv_wait_ready(dev, stream, flags.data_ptr(), flags.numel(), int(epoch), int(timeout_s * 1e9),
+                             status.data_ptr()), "mkv_wait_ready")

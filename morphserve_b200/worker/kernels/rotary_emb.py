@@ -2,8 +2,11 @@
 ``swiftllm.worker.kernels.rotary_emb.rotary_embedding_inplace``
 (worker/kernels/rotary_emb.py:43-58), same signature, q and k rotated in place
 with the cos/sin rows the infer state carries for every token
-(worker/model.py:432-433).  fp16 arithmetic rounds product by product like the
-reference kernel, so results are bit-identical to it.
+(worker/model.py:432-433).  Rounded the way the reference's kernel rounds once
+Triton has compiled it for a GPU (one multiply of each output fused into the
+add), so results are bit-identical to it; ``set_rope_rounding("written")`` rounds
+every operation on its own instead, which is what the same kernel gives in the
+Triton interpreter.
 """
 from __future__ import annotations
 
@@ -18,6 +21,14 @@ from ._common import device_and_stream, require_cuda
 # rotates q as it loads it and the new k row before it stores it (one launch per layer instead of
 # three).  q and k of the decode tokens then keep their unrotated values in memory.  Off by default.
 FUSE_DECODE_ROPE = False
+
+
+def set_rope_rounding(mode: str) -> None:
+    """"compiled" (default): bit-identical to the reference kernel as Triton compiles it for a GPU;
+    "written": every product and sum rounds on its own (the kernel's source, operation by operation)."""
+    if mode not in ("compiled", "written"):
+        raise ValueError("mode is 'compiled' or 'written'")
+    check(lib.mkv_rope_set_rounding(1 if mode == "compiled" else 0), "mkv_rope_set_rounding")
 
 
 def set_fused_decode_rope(enabled: bool) -> None:

@@ -50,17 +50,29 @@ def infer_state_fields(prompt_lens: Sequence[int], decoding_seq_lens: Sequence[i
 # --------------------------------------------------------------------------
 # rotary embedding (the step before the append: worker/layers/transformer_layer.py:93-98)
 # --------------------------------------------------------------------------
-def rotary_embedding(q: np.ndarray, k: np.ndarray, cos: np.ndarray, sin: np.ndarray):
+def rotary_embedding(q: np.ndarray, k: np.ndarray, cos: np.ndarray, sin: np.ndarray, rounding: str = "written"):
     """worker/kernels/rotary_emb.py:7-41: halves [0, D/2) and [D/2, D) of every head rotate as
     (x0*cos - x1*sin, x0*sin + x1*cos) with the token's cos/sin row.  All operands are fp16 in the
-    reference (tables: worker/model.py:240-241), so every product and every sum rounds to fp16;
-    numpy's fp16 arithmetic rounds the same way.  Returns new arrays (the reference writes in place)."""
+    reference (tables: worker/model.py:240-241).
+    rounding="written": every product and every sum rounds to the data type on its own (numpy's fp16
+    arithmetic does exactly that) - the kernel's source run operation by operation, which is how the
+    Triton interpreter runs it and where the committed fixtures come from.
+    rounding="compiled": x0*cos - rn(x1*sin) and x0*sin + rn(x1*cos) with ONE rounding of the outer
+    expression - what the kernel computes once Triton has compiled it for a GPU (the first product is
+    contracted into the add).  float64 holds the exact product and sum of the narrower operands.
+    Returns new arrays (the reference writes in place)."""
     h = q.shape[-1] // 2
     c = cos[:, None, :].astype(q.dtype)
     s = sin[:, None, :].astype(q.dtype)
 
     def rot(x):
         x0, x1 = x[..., :h], x[..., h:]
+        if rounding == "compiled":
+            w0, w1, wc, ws = (a.astype(np.float64) for a in (x0, x1, c, s))
+            lo = w0 * wc - (x1 * s).astype(np.float64)
+            hi = w0 * ws + (x1 * c).astype(np.float64)
+            return np.concatenate([lo, hi], axis=-1).astype(x.dtype)
+        assert rounding == "written"
         return np.concatenate([x0 * c - x1 * s, x0 * s + x1 * c], axis=-1).astype(x.dtype)
 
     return rot(q), rot(k)

@@ -87,15 +87,18 @@ def plan_rule(lens, num_kv_heads, batch_cap_items, sm_count, split_balance=1.5, 
     return chunk, items, rows
 
 
-def static_deal(lens, num_kv_heads, workers, cap_rows, group, block_size=16):
+def static_deal(lens, num_kv_heads, workers, cap_rows, group, unit_cost=1, block_size=16):
     """The plan's static deal restated on the host.  Tiles are ordered sequence by sequence, kv head by kv head,
-    block by block; worker w of W owns tiles [w*T//W, (w+1)*T//W) where W = min(workers, tiles, cap_rows // (2 *
-    group)).  A range is cut into units where the (sequence, head) changes.  Returns (W, wstart, units) with
-    units[i] = (batch index, first block, blocks, piece, head, len, pieces, first owner)."""
-    nblk = [(int(n) + block_size - 1) // block_size if n > 0 else 0 for n in lens]
+    block by block, with `unit_cost` phantom tiles in front of every non-empty (sequence, head); worker w of W owns
+    tiles [w*T//W, (w+1)*T//W) of that order, phantoms included, where W = min(workers, T, cap_rows // (2 * group)).
+    A range is cut into units where the (sequence, head) changes; pieces made of phantoms only are no units.
+    Returns (W, wstart, units) with units[i] = (batch index, first block, blocks, piece, head, len, pieces, first
+    owner)."""
+    oc = unit_cost
+    nblk = [(int(n) + block_size - 1) // block_size + oc if n > 0 else 0 for n in lens]
     T = sum(nblk) * num_kv_heads
     W = min(workers, T, cap_rows // (2 * group))
-    pairs = []                                   # (first tile, b, h, blocks)
+    pairs = []                                   # (first tile, b, h, tiles incl. phantoms)
     t = 0
     for b, n in enumerate(nblk):
         for h in range(num_kv_heads if n else 0):
@@ -115,8 +118,10 @@ def static_deal(lens, num_kv_heads, workers, cap_rows, group, block_size=16):
         while pj < len(pairs) and pairs[pj][0] < hi:
             p0, b, h, n = pairs[pj]
             a, z = max(lo, p0), min(hi, p0 + n)
-            f, last = owner(p0), owner(p0 + n - 1)
-            units.append((b, a - p0, z - a, w - f, h, int(lens[b]), last - f + 1, f))
+            if z - p0 > oc:                      # real tiles in the piece
+                f, last = owner(p0 + oc), owner(p0 + n - 1)
+                first = max(a - p0, oc) - oc
+                units.append((b, first, z - p0 - oc - first, w - f, h, int(lens[b]), last - f + 1, f))
             pj += 1
         wstart.append(len(units))
     return W, wstart, units

@@ -95,7 +95,7 @@ def test_host_side_argument_validation(L):
     assert lib.mkv_copy_blocks(0, None, C.byref(p), None, None, 3) == -1
     assert lib.mkv_copy_blocks(0, None, C.byref(p), None, None, 0) == 0
     assert lib.mkv_remap_block_table(0, None, None, 4, 4, None, None, None, 2) == -1
-    assert lib.mkv_block_need(0, None, 1, 1, 1, 4, 0, 1, 1) == -2
+    assert lib.mkv_block_need(0, None, 1, 8, 1, 1, 4, 0, 1, 1) == -2
 
 
 def test_swap_validates_ids_on_the_host(L):

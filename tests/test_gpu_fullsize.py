@@ -65,22 +65,27 @@ def _check_append_rows(pools_k, pools_v, table, rows, lens, k_new, v_new, layer,
     assert torch.equal(got_v, v_new), "appended V rows differ"
 
 
-@pytest.mark.parametrize("name,balance", [("llama3-8b-gqa-decode", None), ("llama2-7b-mha-decode", None),
-                                          ("llama3-8b-gqa-decode", 0.0)])
-def test_baseline_decode_config_full_size(name, balance):
+@pytest.mark.parametrize("name,balance,deal", [("llama3-8b-gqa-decode", None, 1), ("llama2-7b-mha-decode", None, 1),
+                                               ("llama3-8b-gqa-decode", 0.0, 0), ("llama3-8b-gqa-decode", 0.0, 1),
+                                               ("llama2-7b-mha-decode", None, 2)])
+def test_baseline_decode_config_full_size(name, balance, deal):
     """`balance` 0.0 makes the plan cut sequences as finely as its item cap allows, so that the split-KV merge
-    runs at full size too (with the default rule these batches are balanced without a cut)."""
+    runs at full size too (with the default rule these batches are balanced without a cut): once with the chunks
+    drawn from the shared counter (`deal` 0) and once with equal ranges per worker (1).  `deal` 2 forces the equal
+    ranges on a batch that would not be cut."""
     from morphserve_b200._lib import lib, check
     w = bench.shard_workload(bench.WORKLOADS[name], 0, 1)
     job = bench.DecodeJob(w, 0, growth_tokens=32, device=torch.device("cuda", 0))
     if balance is not None:
         check(lib.mkv_attn_configure(-1, -1, -1.0, balance, -1), "mkv_attn_configure")
+    check(lib.mkv_attn_set_static_deal(deal, -1), "mkv_attn_set_static_deal")
     try:
         for _ in range(2):
             job.step_resident()
         torch.cuda.synchronize()
     finally:
         check(lib.mkv_attn_configure(-1, -1, -1.0, 1.5, -1), "mkv_attn_configure")
+        check(lib.mkv_attn_set_static_deal(1, -1), "mkv_attn_set_static_deal")
     bm = job.bm
     lens = job.lens_dev
     # integers: every sequence owns exactly ceil(len/16) blocks, all distinct, bitmap consistent

@@ -23,7 +23,22 @@ L, HKV, BS, D = 4, 8, 16, 128
 
 @pytest.fixture(scope="module")
 def ref_c():
-    return ref_loader.load_ext()
+    c = ref_loader.load_ext()
+    yield c
+    # The reference keeps the registered tensor maps (Python objects) in C++ statics that are destroyed after the
+    # interpreter has shut down (csrc/src/memory_manager.cpp:8-13): leave empty lists behind so that nothing of
+    # Python's is left for those destructors to touch.
+    for layer in REGISTERED_MAP_LAYERS:
+        c.register_layer_memory_tensor_map_quant(layer, [])
+        c.register_layer_memory_tensor_map_org(layer, [])
+
+
+REGISTERED_MAP_LAYERS = (9, 10)
+
+
+def _same_bits(x, y):
+    """Equal as BYTES: the slabs hold random bits, which read as fp16 include NaNs."""
+    return torch.equal(x.contiguous().view(torch.uint8), y.contiguous().view(torch.uint8))
 
 
 def _pools(nb, ncpu, seed, pin=False):
@@ -191,7 +206,7 @@ def test_replace_layer_matches_the_reference_extension(ref_c):
         for x, y in zip(a, b):
             assert x.dtype == y.dtype and tuple(x.shape) == tuple(y.shape) and x.is_contiguous() and y.is_contiguous()
             assert x.data_ptr() - slabs["ref"].data_ptr() == y.data_ptr() - slabs["ours"].data_ptr()
-            assert torch.equal(x, y)
+            assert _same_bits(x, y)
         assert ref_c.verify_tensor_continuity(a) == ours.verify_tensor_continuity(b)
     for c in (ref_c, ours):
         with pytest.raises(RuntimeError, match="not registered"):

@@ -289,3 +289,103 @@ def test_replacing_the_bitmap_bumps_the_resize_generation():
     assert bm.resize_generation == g0 + 1 and bm.is_block_free.shape[0] == 40 and int(bm.num_free_blocks) == 40
     assert memory_utils.release_last_kvcache_chunk(eng)
     assert bm.resize_generation == g0 + 2 and bm.is_block_free.shape[0] == 32
+
+
+def test_gather_and_free_without_host_round_trip():
+    """The sync-free gather against the synchronous one on a twin manager: same ids in batch order, -1 behind them,
+    the count on the device, tables / bitmap / free count equal once the counters are read."""
+    from morphserve_b200 import BlockManager
+    rs = np.random.RandomState(4)
+    a, b = BlockManager("GPU", 500, 40, 16, 16), BlockManager("GPU", 500, 40, 16, 16)
+    ids = H.to_dev(np.arange(30, dtype=np.int32))
+    lens = H.to_dev(rs.randint(0, 200, size=30).astype(np.int32))
+    for bm in (a, b):
+        bm.allocate_blocks_for_seqs(ids, lens)
+    pick = H.to_dev(np.array([7, 0, 29, 12, 3], dtype=np.int32))
+    want = a.gather_allocated_blocks_and_free(pick)
+    got, count = b.gather_allocated_blocks_and_free_nosync(pick)
+    n = int(count.item())
+    assert n == want.shape[0] and got.shape[0] == min(5 * 16, 500)
+    assert torch.equal(got[:n], want.to(torch.int32)) and bool((got[n:] == -1).all())
+    assert int(b.num_free_blocks) == int(a.num_free_blocks)
+    assert torch.equal(a.is_block_free, b.is_block_free)
+    assert torch.equal(a.num_seq_allocated_blocks, b.num_seq_allocated_blocks)
+    # a buffer that is too small: everything is freed, the first `capacity` ids are reported, the count says so
+    pick2 = H.to_dev(np.array([1, 2, 4], dtype=np.int32))
+    want2 = a.gather_allocated_blocks_and_free(pick2)
+    got2, count2 = b.gather_allocated_blocks_and_free_nosync(pick2, capacity=3)
+    assert int(count2.item()) == want2.shape[0] > 3 and torch.equal(got2, want2[:3].to(torch.int32))
+    assert int(b.num_free_blocks) == int(a.num_free_blocks) and torch.equal(a.is_block_free, b.is_block_free)
+
+
+def test_mixed_prefill_and_decode_step_captured_in_a_cuda_graph():
+    """A step that admits prompts next to the decoding sequences - sync-free allocate for all of them, then per layer
+    one store_kvcache call (prompt scatter + decode append) and decode attention - captured once and replayed with
+    new contents in the same buffers; pools, tables and outputs equal the same calls issued one by one."""
+    import types
+    import morphserve_b200 as mk
+    dev = torch.device("cuda", 0)
+    L, Hq, Hkv, D, bs = 2, 8, 2, 128, 16
+    n_pre, n_dec, mbps, nb = 3, 5, 24, 200
+    plens = [40, 16, 7]
+    mc = types.SimpleNamespace(num_layers=L, num_q_heads=Hq, num_kv_heads=Hkv, head_dim=D)
+    ec = types.SimpleNamespace(block_size=bs, max_blocks_per_seq=mbps)
+    n_tok = sum(plens) + n_dec
+
+    def run(captured: bool):
+        g = torch.Generator(device=dev).manual_seed(21)
+        bm = mk.BlockManager("GPU", nb, 16, mbps, bs)
+        dec_ids = torch.arange(n_pre, n_pre + n_dec, dtype=torch.int32, device=dev)
+        dec_lens = torch.tensor([100, 33, 16, 250, 64], dtype=torch.int32, device=dev)
+        bm.allocate_blocks_for_seqs(dec_ids, dec_lens)
+        kc = torch.randn((nb, L, Hkv, bs, D), generator=g, dtype=torch.float16, device=dev)
+        vc = torch.randn((nb, L, Hkv, bs, D), generator=g, dtype=torch.float16, device=dev)
+        seq_ids = torch.arange(n_pre + n_dec, dtype=torch.int32, device=dev)
+        # fixed-address buffers the graph reads: lengths of all sequences, k / v / q of the step
+        lens_all = torch.cat([torch.tensor(plens, dtype=torch.int32, device=dev), dec_lens + 1])
+        k = torch.empty((L, n_tok, Hkv, D), dtype=torch.float16, device=dev)
+        v = torch.empty_like(k)
+        q = torch.empty((L, n_dec, Hq, D), dtype=torch.float16, device=dev)
+        o = torch.zeros((L, n_dec, Hq * D), dtype=torch.float16, device=dev)
+        starts = torch.tensor(np.cumsum([0] + plens[:-1]), dtype=torch.int32, device=dev)
+        z = torch.zeros(0, dtype=torch.int32, device=dev)
+        st = mk.LlamaInferState(
+            batch_size=n_pre + n_dec, num_tokens=n_tok, seq_ids=seq_ids, softmax_scale=D ** -0.5, num_prefill_seqs=n_pre,
+            num_prefill_tokens=sum(plens), prefill_seq_start_locs=starts, prefill_seq_start_locs_with_end=z,
+            prefill_seq_lens=lens_all[:n_pre], max_prefill_len=max(plens), num_decoding_seqs=n_dec,
+            decoding_seq_lens=lens_all[n_pre:], max_decoding_len=300, seq_block_size=512, num_seq_blocks=1,
+            num_blocks_org=nb, kv_cache_new_block_size=0, org_layer_param_size=0, position_cos=z, position_sin=z,
+            ignore_kvcache=False)
+
+        def step():
+            bm.allocate_blocks_for_seqs_nosync(seq_ids, lens_all)
+            for layer in range(L):
+                mk.store_kvcache(k[layer], v[layer], kc, vc, [], [], bm.block_table, mc, ec, st, layer)
+                mk.paged_attention(q[layer], kc, vc, [], [], bm.block_table, mc, ec, st, layer, o[layer])
+
+        def fill():
+            for t in (k, v, q):
+                t.normal_(generator=g)
+
+        fill()
+        if captured:
+            from morphserve_b200.worker.kernels._common import attn_workspace
+            bm.prepare_nosync(n_pre + n_dec)
+            cs = torch.cuda.Stream(dev)
+            attn_workspace(0, n_dec, Hq, Hkv, D, mbps, cs.cuda_stream)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=cs):
+                step()
+            graph.replay()
+            bm.nosync_replayed()
+        else:
+            step()
+        torch.cuda.synchronize()
+        return kc, vc, o.clone(), bm
+
+    a, b = run(False), run(True)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) and torch.equal(a[2], b[2])
+    assert bool(a[2].abs().sum() > 0)
+    assert torch.equal(a[3].block_table, b[3].block_table) and torch.equal(a[3].is_block_free, b[3].is_block_free)
+    assert int(a[3].num_free_blocks) == int(b[3].num_free_blocks)

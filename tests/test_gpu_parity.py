@@ -160,12 +160,14 @@ def test_decode_attention_sweep_against_oracle(B, Hq, Hkv, max_len, L, layer):
     assert read_attn_error_flags(0) == 0
 
 
+@pytest.mark.parametrize("deal", [(0, 1), (1, 0), (1, 1), (2, 3)])
 @pytest.mark.parametrize("balance", [0.0, 1.5, 1000.0])
 @pytest.mark.parametrize("shape", ["spread", "one_long"])
-def test_split_rule_extremes(balance, shape):
+def test_split_rule_extremes(balance, shape, deal):
     """The plan cuts a sequence only when it is long against the mean load of a worker warp.  Finest cut (0),
     the default, and "never cut" (1000) must all give the oracle's result, on a batch with a spread of lengths
-    and on one long sequence among short ones."""
+    and on one long sequence among short ones - with chunks drawn from the shared counter (deal 0), with equal
+    ranges per worker when something has to be cut (1) or always (2), and with several unit costs."""
     from morphserve_b200._lib import lib, check
     rs = np.random.RandomState(314)
     if shape == "spread":
@@ -180,10 +182,12 @@ def test_split_rule_extremes(balance, shape):
     c = cases.build_decode_case(seed=2718, B=B, Hq=Hq, Hkv=Hkv, D=128, bs=16, L=1, layer=0, num_blocks_org=nb,
                                 dtype=np.float16, lens=lens)
     check(lib.mkv_attn_configure(-1, -1, -1.0, balance, -1), "mkv_attn_configure")
+    check(lib.mkv_attn_set_static_deal(deal[0], deal[1]), "mkv_attn_set_static_deal")
     try:
         o, kp, vp = H.run_decode_step(H.device_case(c))
     finally:
         check(lib.mkv_attn_configure(-1, -1, -1.0, 1.5, -1), "mkv_attn_configure")
+        check(lib.mkv_attn_set_static_deal(1, 1), "mkv_attn_set_static_deal")
     ex = O.paged_attention_exact(c["q"], kp, vp, c["block_table"], c["seq_ids"], c["seq_lens"], 0, c["scale"],
                                  c["num_blocks_org"], 0)
     _close(o, ex)
@@ -191,11 +195,15 @@ def test_split_rule_extremes(balance, shape):
     assert read_attn_error_flags(0) == 0
 
 
+@pytest.mark.parametrize("deal", [1, 2])
 @pytest.mark.parametrize("Hq,Hkv", [(8, 2), (16, 16)])
-def test_many_short_sequences_per_worker(Hq, Hkv):
+def test_many_short_sequences_per_worker(Hq, Hkv, deal):
     """More (sequence, kv head) units than worker warps, nearly all of one or two blocks, a few long ones in
     between: every warp runs several short units back to back, so the hand-over between units (claim of the next
-    unit, prefetch of its first tiles into freed stages) is exercised where it has the least slack."""
+    unit, prefetch of its first tiles into freed stages) is exercised where it has the least slack - with units
+    drawn from the shared counter (`deal` 1: nothing needs cutting here) and with equal ranges per worker (2), where
+    the records come out of the register window and the next unit is claimed at once."""
+    from morphserve_b200._lib import lib, check
     rs = np.random.RandomState(Hq)
     B = 1400
     lens = rs.randint(1, 41, size=B)
@@ -203,7 +211,11 @@ def test_many_short_sequences_per_worker(Hq, Hkv):
     nb = int(((lens + 15) // 16).sum()) + 7
     c = cases.build_decode_case(seed=4242 + Hkv, B=B, Hq=Hq, Hkv=Hkv, D=128, bs=16, L=1, layer=0, num_blocks_org=nb,
                                 dtype=np.float16, lens=lens)
-    o, kp, vp = H.run_decode_step(H.device_case(c))
+    check(lib.mkv_attn_set_static_deal(deal, -1), "mkv_attn_set_static_deal")
+    try:
+        o, kp, vp = H.run_decode_step(H.device_case(c))
+    finally:
+        check(lib.mkv_attn_set_static_deal(1, -1), "mkv_attn_set_static_deal")
     ex = O.paged_attention_exact(c["q"], kp, vp, c["block_table"], c["seq_ids"], c["seq_lens"], 0, c["scale"],
                                  c["num_blocks_org"], 0)
     _close(o, ex)
@@ -230,12 +242,15 @@ def _random_batch(rs):
     return B, Hkv * G, Hkv, lens
 
 
+@pytest.mark.parametrize("deal", [0, 1, 2])
 @pytest.mark.parametrize("seed", range(8))
-def test_random_batches_fast_path_against_plain_kernel(seed):
-    """Seeded random batches, all sequences compared on the GPU: the tensor-core kernel (plan, dynamic schedule,
-    split-KV merge, fused append when the fixture says so) against the library's plain kernel, which shares none
-    of that machinery and is held to the oracle by the tests above."""
+def test_random_batches_fast_path_against_plain_kernel(seed, deal):
+    """Seeded random batches, all sequences compared on the GPU: the tensor-core kernel (plan, either deal of the
+    tiles - `deal` 2 forces equal ranges per worker on every batch -, split-KV merge in one and two levels, fused
+    append when the fixture says so) against the library's plain kernel, which shares none of that machinery and is
+    held to the oracle by the tests above."""
     from morphserve_b200._lib import lib, check
+    check(lib.mkv_attn_set_static_deal(deal, seed % 3), "mkv_attn_set_static_deal")
     rs = np.random.RandomState(1000 + seed)
     B, Hq, Hkv, lens = _random_batch(rs)
     nb = int(((lens + 15) // 16).sum()) + 3
@@ -276,6 +291,7 @@ def test_random_batches_fast_path_against_plain_kernel(seed):
             if force_plain:
                 check(lib.mkv_attn_configure(-1, -1, -1.0, -1.0, DEFAULT_LOADER), "mkv_attn_configure")
         outs.append((o, k2, v2))
+    check(lib.mkv_attn_set_static_deal(1, 1), "mkv_attn_set_static_deal")
     (o_fast, k_fast, v_fast), (o_plain, k_plain, v_plain) = outs
     for a, b in zip(k_fast + v_fast, k_plain + v_plain):
         assert torch.equal(a, b), "appended pools differ"
@@ -401,9 +417,11 @@ def test_plan_kernel_follows_the_stated_rule(seed):
     if seed % 3 == 0:
         lens[rs.randint(0, B, size=max(1, B // 10))] = 0            # sequences without any token
     balance = float(rs.choice([0.0, 1.0, 1.5, 4.0]))
+    unit_cost = int(rs.choice([0, 1, 2]))
     max_blocks = (int(lens.max()) + 15) // 16
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     check(lib.mkv_attn_configure(-1, -1, -1.0, balance, -1), "mkv_attn_configure")
+    check(lib.mkv_attn_set_static_deal(-1, unit_cost), "mkv_attn_set_static_deal")
     try:
         ws = attn_workspace(0, B, Hq, Hkv, 128, max_blocks)
         lay = (C.c_int64 * 10)()
@@ -417,6 +435,7 @@ def test_plan_kernel_follows_the_stated_rule(seed):
         raw = ws.tensor.cpu().numpy()
     finally:
         check(lib.mkv_attn_configure(-1, -1, -1.0, 1.5, -1), "mkv_attn_configure")
+        check(lib.mkv_attn_set_static_deal(-1, 1), "mkv_attn_set_static_deal")
     hdr = raw[:64].view(np.int32)
     magic, batch, n_items, chunk, _, _, flags, n_rows, cap, mode, n_workers, n_units = [int(x) for x in hdr[:12]]
     off_items, _, off_wstart, _, _, _, cap_items, cap_units, max_workers, workers = [int(x) for x in lay]
@@ -427,7 +446,7 @@ def test_plan_kernel_follows_the_stated_rule(seed):
         assert mode == 0 and (chunk, n_items, n_rows) == (exp_chunk, exp_items, exp_rows)
         assert exp_rows == 0 and n_units == n_items * Hkv
         return
-    W, wstart, units = H.static_deal(lens, Hkv, workers, cap_items * Hq, G)
+    W, wstart, units = H.static_deal(lens, Hkv, workers, cap_items * Hq, G, unit_cost=unit_cost)
     assert B * Hkv + W <= cap_units
     assert (mode, n_workers, n_units, n_rows) == (1, W, len(units), 2 * W)
     got_start = raw[off_wstart:off_wstart + 4 * (max_workers + 1)].view(np.int32)

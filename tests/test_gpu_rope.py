@@ -1,6 +1,11 @@
 """GPU parity of the rotary embedding (the step in front of the KV append): the stand-alone
 kernel bit-exact against the reference's output (fixtures) and the oracle, and the form fused
-into the decode-attention launch against the three separate calls."""
+into the decode-attention launch against the three separate calls.
+
+Every test runs under both roundings the library offers: "written" (each operation rounds, the
+reference kernel in the Triton interpreter - the committed fixtures) and "compiled" (one multiply
+of each output fused into the add, the reference kernel compiled for a GPU; held to the compiled
+kernel itself in tests/test_gpu_reference.py)."""
 import os
 
 import numpy as np
@@ -14,6 +19,18 @@ from tests.golden import cases
 pytestmark = pytest.mark.gpu
 G = os.path.join(os.path.dirname(__file__), "golden")
 RTOL, ATOL = 2e-3, 1e-2
+ROUNDING = "written"
+
+
+@pytest.fixture(params=["written", "compiled"], autouse=True)
+def rounding(request):
+    import morphserve_b200 as mk
+    global ROUNDING
+    ROUNDING = request.param
+    mk.set_rope_rounding(ROUNDING)
+    yield ROUNDING
+    ROUNDING = "written"
+    mk.set_rope_rounding("compiled")      # the library's default
 
 
 def _state(c, cos, sin, n_dec=0):
@@ -27,6 +44,8 @@ def _state(c, cos, sin, n_dec=0):
 @pytest.mark.parametrize("name", list(cases.ROPE_CASES))
 def test_rotary_embedding_matches_reference_fixture(name):
     from morphserve_b200 import rotary_embedding_inplace
+    if ROUNDING != "written":
+        pytest.skip("the fixtures hold the reference kernel's output in the Triton interpreter: rounding as written")
     c = cases.build_rope_case(**cases.ROPE_CASES[name])
     gold = np.load(os.path.join(G, f"rope_{name}.npz"))
     q, k = H.to_dev(c["q"]), H.to_dev(c["k"])
@@ -49,7 +68,7 @@ def test_rotary_embedding_sweep_against_oracle(T, Hq, Hkv, D, dtype):
     q, k = H.to_dev(c["q"]), H.to_dev(c["k"])
     rotary_embedding_inplace(q, k, _state(c, H.to_dev(c["cos"]), H.to_dev(c["sin"])))
     torch.cuda.synchronize()
-    qo, ko = O.rotary_embedding(c["q"], c["k"], c["cos"], c["sin"])
+    qo, ko = O.rotary_embedding(c["q"], c["k"], c["cos"], c["sin"], rounding=ROUNDING)
     assert q.cpu().numpy().tobytes() == qo.tobytes()
     assert k.cpu().numpy().tobytes() == ko.tobytes()
 
@@ -107,7 +126,7 @@ def test_fused_rope_append_attention_equals_separate_calls(B, Hq, Hkv, max_len, 
         assert a.tobytes() == b.tobytes()
     assert o_fus.tobytes() == o_sep.tobytes()
     # and both agree with the oracle: rotated rows bit-exact in the pool, attention within tolerance
-    q_rot, k_rot = O.rotary_embedding(c["q"], c["k_new"], cos_np, sin_np)
+    q_rot, k_rot = O.rotary_embedding(c["q"], c["k_new"], cos_np, sin_np, rounding=ROUNDING)
     kpo, vpo = [p.copy() for p in c["k_pools"]], [p.copy() for p in c["v_pools"]]
     O.store_kvcache_decode(k_rot, c["v_new"], kpo, vpo, c["block_table"], c["seq_ids"], c["seq_lens"], c["layer"],
                            c["num_blocks_org"], c["chunk_blocks"])
@@ -130,7 +149,7 @@ def test_fused_rope_with_prefill_rows_in_the_batch():
     q_np = rs.standard_normal((T, Hq, D)).astype(np.float16)
     pos = np.concatenate([np.concatenate([np.arange(n) for n in c["prefill_lens"]]), c["decode_lens"] - 1])
     cos_np, sin_np = cases.rope_tables(pos, D)
-    q_rot, k_rot = O.rotary_embedding(q_np, c["k"], cos_np, sin_np)
+    q_rot, k_rot = O.rotary_embedding(q_np, c["k"], cos_np, sin_np, rounding=ROUNDING)
 
     kp = [H.to_dev(p) for p in c["k_pools"]]
     vp = [H.to_dev(p) for p in c["v_pools"]]
@@ -201,7 +220,7 @@ def test_pending_rope_is_flushed_when_no_fused_attention_follows():
     finally:
         mk.set_fused_decode_append(False)
         mk.set_fused_decode_rope(False)
-    q_rot, k_rot = O.rotary_embedding(c["q"], c["k_new"], cos_np, sin_np)
+    q_rot, k_rot = O.rotary_embedding(c["q"], c["k_new"], cos_np, sin_np, rounding=ROUNDING)
     assert d["q_t"].cpu().numpy().tobytes() == q_rot.tobytes()
     assert d["k_new_t"].cpu().numpy().tobytes() == k_rot.tobytes()
     kpo, vpo = [p.copy() for p in c["k_pools"]], [p.copy() for p in c["v_pools"]]
@@ -233,7 +252,7 @@ def test_rope_append_entry_on_a_shape_without_fused_path():
         cos.data_ptr(), sin.data_ptr(), pool, bt.data_ptr(), bt.stride(0), d["seq_ids_t"].data_ptr(),
         d["seq_lens_t"].data_ptr(), 4, 6, 1, float(c["scale"]), bt.shape[1], ws.tensor.data_ptr(), ws.nbytes), "rope_append")
     torch.cuda.synchronize()
-    q_rot, k_rot = O.rotary_embedding(c["q"], c["k_new"], cos_np, sin_np)
+    q_rot, k_rot = O.rotary_embedding(c["q"], c["k_new"], cos_np, sin_np, rounding=ROUNDING)
     assert d["q_t"].cpu().numpy().tobytes() == q_rot.tobytes()
     kpo, vpo = [p.copy() for p in c["k_pools"]], [p.copy() for p in c["v_pools"]]
     O.store_kvcache_decode(k_rot, c["v_new"], kpo, vpo, c["block_table"], c["seq_ids"], c["seq_lens"], 1, 40, 0)

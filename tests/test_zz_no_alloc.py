@@ -45,7 +45,7 @@ def _noalloc(d):
     from morphserve_b200.worker.kernels._common import make_pool
     pool = make_pool(d["k_pools_t"][0], d["v_pools_t"][0], d["k_pools_t"][1:], d["v_pools_t"][1:],
                      d["num_blocks_org"], d["chunk_blocks"])
-    o = torch.zeros((d["B"], d["Hq"] * d["D"]), dtype=torch.float16, device="cuda")
+    o = torch.zeros((d["B"], d["Hq"] * d["D"]), dtype=d["q_t"].dtype, device="cuda")
     max_blocks = int((int(d["seq_lens"].max()) + 15) // 16)
     before = torch.cuda.memory_allocated()
     st = lib.mkv_paged_attention_decode_noalloc(
@@ -90,3 +90,33 @@ def test_noalloc_entry_point_refuses_what_does_not_fit():
     assert st == -9
     assert b"built-in scratch" in lib.mkv_status_string(st)
     torch.cuda.synchronize()
+
+
+def _builtin_flags():
+    from morphserve_b200._lib import lib
+    flags = C.c_int(-1)
+    st = lib.mkv_attn_read_error_flags(0, torch.cuda.current_stream().cuda_stream, None, C.byref(flags))
+    assert st == 0
+    return flags.value
+
+
+@pytest.mark.parametrize("fp32", [False, True])
+def test_noalloc_entry_point_reports_a_block_id_outside_the_pool(fp32):
+    """Error bits of this entry point live in the library's own array; a NULL workspace makes
+    mkv_attn_read_error_flags read them.  A block-table entry that names no block of the pool is never turned into
+    an address (the kernels compare it with the pool's size first and read block 0 instead): the call completes,
+    bit 0 is set, and the next clean call starts with the word cleared - on the tensor-core path and on the plain
+    kernel (fp32 pool) alike."""
+    kw = dict(seed=73, B=5, Hq=8, Hkv=2, D=128, bs=16, L=1, layer=0, num_blocks_org=64,
+              dtype=np.float32 if fp32 else np.float16, lens=[40, 3, 100, 16, 33])
+    good = H.device_case(cases.build_decode_case(**kw))
+    _noalloc(good)
+    assert _builtin_flags() == 0
+    bad = cases.build_decode_case(**kw)
+    table = bad["block_table"].copy()
+    table[int(bad["seq_ids"][2]), 1] = 10 ** 6            # second block of the third sequence: far outside the pool
+    bad["block_table"] = table
+    _noalloc(H.device_case(bad))
+    assert _builtin_flags() & 1
+    _noalloc(good)
+    assert _builtin_flags() == 0
