@@ -59,6 +59,8 @@ WORKLOADS = {
     "kv-prefill": dict(cfg=3, prefill=True, L=4, Hq=32, Hkv=8, n_seqs=32, max_len=2048),
     # block swap between the pool and the host swap space (Llama-3-8B block = 2 x 1 MiB): 1024 blocks per direction
     "kv-swap": dict(cfg=3, swap=True, L=32, Hq=32, Hkv=8, nb=4096, n_swap=1024),
+    # the same with 4 layers (blocks of 2 x 128 KiB, pool 1 GB) for profiler captures
+    "kv-swap-small": dict(cfg=3, swap=True, L=4, Hq=32, Hkv=8, nb=4096, n_swap=1024),
     # the same with the all-gather folded into the attention launch: every rank stores its output slice straight
     # into all ranks' full-width matrices (peer-mapped symmetric memory), one barrier per layer
     "codellama-34b-gqa-decode-headshard-push": dict(cfg=5, B=512, Hq=64, Hkv=8, L=48, max_len=1536, free_frac=0.05,

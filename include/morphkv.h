@@ -222,18 +222,18 @@ int mkv_paged_attention_decode_rope_append(
 int mkv_attn_configure(int warps, int stages, double item_factor, double split_balance, int loader);
 
 /*
- * How the plan deals the launch's K/V tiles to the worker warps (process-wide tuning knob; default 1).
- *   0: always in chunks drawn from a shared counter, longest first (sequences longer than the chunk are cut);
- *   1: as 0 while no sequence has to be cut; otherwise every worker gets an equal contiguous range of the tile
- *      stream and sequences are cut only where a range ends (all workers finish together; pieces are merged in
- *      two levels when there are many);
- *   2: equal ranges whenever the workspace allows it.
- * `unit_cost` (default 1): with equal ranges, what starting a unit is worth in tiles - every (sequence, kv head)
+ * How the plan deals the launch's K/V tiles to the worker warps (process-wide tuning knobs).
+ *   mode 0: always in chunks drawn from a shared counter, longest first (sequences longer than the chunk are cut);
+ *   mode 1 (default): as 0 unless the batch is skewed - its longest sequence is longer than `ratio` chunks (default
+ *      8); then every worker gets an equal contiguous range of the tile stream, sequences are cut only where a range
+ *      ends (all workers finish together) and the pieces are merged in two levels when there are many;
+ *   mode 2: equal ranges whenever the workspace allows it.
+ * `unit_cost` (default 3): with equal ranges, what starting a unit is worth in tiles - every (sequence, kv head)
  * counts as that many tiles more than it has, so a worker that is dealt many short sequences is dealt fewer tiles.
- * Negative values keep the current setting of either knob.
+ * mode / unit_cost < 0 and ratio < 0 keep the current setting.
  * Part of the scheduling the reference leaves to its launch grid (worker/kernels/paged_attn.py:832-853).
  */
-int mkv_attn_set_static_deal(int mode, int unit_cost);
+int mkv_attn_set_static_deal(int mode, int unit_cost, int ratio);
 
 /*
  * Testing / debugging aid: byte offsets of the regions inside an attention workspace of the given shape and the

@@ -49,7 +49,7 @@ SIGNATURES = {
     "mkv_attn_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i]),
     "mkv_attn_plan": (_i, [_i, _vp, _vp, _sz, _vp, _vp, _i, _i, _i, _i, _i, _i]),
     "mkv_attn_configure": (_i, [_i, _i, C.c_double, C.c_double, _i]),
-    "mkv_attn_set_static_deal": (_i, [_i, _i]),
+    "mkv_attn_set_static_deal": (_i, [_i, _i, _i]),
     "mkv_attn_workspace_layout": (_i, [_i, _i, _i, _i, _i, _i, C.POINTER(_i64)]),
     "mkv_paged_attention_decode_push": (_i, [_i, _vp, _vp, C.POINTER(_vp), _i, _i64, _i64, C.POINTER(_vp), _i, C.c_int32,
                                              _vp, _vp, _pool, _vp, _i64, _vp, _vp, _i, _i, _i, _f, _i, _vp, _sz]),

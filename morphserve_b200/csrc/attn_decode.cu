@@ -92,7 +92,8 @@ struct Tuning {
     std::atomic<int> warps{8}, stages{3};
     std::atomic<int> loader{0};        // 0 cp.async, 1 TMA, 2 no fast path at all (testing)
     std::atomic<int> static_mode{1};   // 0 never deal statically, 1 when a sequence must be cut, 2 whenever possible
-    std::atomic<int> unit_cost{1};     // static deal: tiles that starting a unit is worth
+    std::atomic<int> unit_cost{3};     // static deal: tiles that starting a unit is worth
+    std::atomic<int> static_ratio{8};  // mode 1: static when the longest sequence exceeds this many chunks
     std::atomic<double> item_factor{4.0};    // work units per worker warp that bound the dynamic item list
     std::atomic<double> split_balance{1.5};  // see plan_balance()
     std::once_flag once;
@@ -122,6 +123,7 @@ static Tuning &tuning() {
         if (const char *e = getenv("MKV_ATTN_LOADER")) t.loader = strcmp(e, "cpasync") == 0 ? 0 : 1;
         if (const char *e = getenv("MKV_ATTN_STATIC")) t.static_mode = atoi(e);
         if (const char *e = getenv("MKV_ATTN_UNIT_COST")) t.unit_cost = std::max(0, std::min(64, atoi(e)));
+        if (const char *e = getenv("MKV_ATTN_STATIC_RATIO")) t.static_ratio = std::max(1, std::min(1 << 20, atoi(e)));
     });
     return g_tuning;
 }
@@ -214,7 +216,8 @@ struct PlanArgs {
     int cap_items, cap_units, cap_rows;  // cap_rows: (row, query head) slots of the partial buffers
     int workers;       // worker warps of the decode launch this plan is for
     int max_workers;
-    int static_mode;   // 0 never, 1 when a sequence has to be cut, 2 whenever the buffers allow it
+    int static_mode;   // 0 never, 1 when the longest sequence dwarfs the chunk, 2 whenever the buffers allow it
+    int static_ratio;  // mode 1: "dwarfs" = longer than static_ratio chunks
     int unit_cost;     // static deal: what starting a unit costs a worker, in tiles
     float balance;
 };
@@ -319,8 +322,10 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(const PlanArgs a) {
     for (int i = tid; i < batch * a.num_kv_heads; i += blockDim.x) a.arrive[i] = 0;
     for (int i = tid; i < 2 * a.max_workers; i += blockDim.x) a.garrive[i] = 0;
 
-    // ---- static deal: taken when some sequence would have to be cut anyway (a cut costs partial rows and a merge
-    // either way; equal ranges then make every worker finish together, which chunks of a fixed size do not)
+    // ---- static deal: taken when the batch is skewed - its longest sequence would be cut into many chunks.  Chunks of
+    // a fixed size then leave the workers unevenly loaded and one warp with a long merge at the very end; equal
+    // ranges make every worker finish together and the pieces are merged in two levels.  (With mild cutting -
+    // a few chunks per sequence - drawing chunks from the counter measured a little faster.)
     __shared__ int s_nonempty;
     if (tid == 0) s_nonempty = 0;
     __syncthreads();
@@ -335,7 +340,7 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(const PlanArgs a) {
     int W = a.workers;
     if ((long long)W > T) W = (int)T;
     if (W > a.cap_rows / (2 * a.group)) W = a.cap_rows / (2 * a.group);
-    const bool cuts = s_max_blocks > chunk;
+    const bool cuts = (long long)s_max_blocks > (long long)chunk * a.static_ratio;
     if (((a.static_mode == 1 && cuts) || a.static_mode == 2) && W >= 1 &&
         (long long)batch * a.num_kv_heads + W <= a.cap_units && a.num_kv_heads < 32768) {
         int *prefix = reinterpret_cast<int *>(items_tmp);  // tiles of one head before sequence b; [batch] = all
@@ -596,12 +601,12 @@ struct RowMap {
 // Merge of `n` partial rows (pieces s0, s0 + step, ...) of one (sequence, kv head): for each of the G query
 // heads, o = sum_s 2^(lse_s - m) o_s / sum_s 2^(lse_s - m).  FINAL: the result is the attention output (fp16,
 // every destination matrix).  Otherwise it replaces the partial row of piece s0 (normalised, with its own lse),
-// one level of a two-level merge.  Loads are issued in batches (2 heads x 4 rows) before any of them is used, so a
+// one level of a two-level merge.  Loads are issued in batches (2 heads x 8 rows) before any of them is used, so a
 // merge costs a couple of L2 round trips instead of one per load.
 template <bool FINAL>
 __device__ __forceinline__ void merge_rows(const AttnParams &p, int b, int hq0, int G, const RowMap &map, int s0,
                                            int step, int n, int lane) {
-    constexpr int SB = 4;
+    constexpr int SB = 8;
     for (int r = 0; r < G; r += 2) {
         const bool two = (r + 1) < G;
         const int ra = r, rb = two ? r + 1 : r;
@@ -1441,6 +1446,7 @@ static void launch_plan(char *ws, const WsLayout &L, const int32_t *seq_lens, co
     const bool fast_shape = block_size == kBS && num_q_heads % num_kv_heads == 0 && a.group <= 16;
     a.static_mode = fast_shape ? tuning().static_mode.load(std::memory_order_relaxed) : 0;
     a.unit_cost = tuning().unit_cost.load(std::memory_order_relaxed);
+    a.static_ratio = tuning().static_ratio.load(std::memory_order_relaxed);
     a.balance = plan_balance(sm_count, num_kv_heads);
     attn_plan_kernel<<<1, 1024, 0, s>>>(a);
 }
@@ -1710,10 +1716,11 @@ int mkv_attn_workspace_layout(int device, int batch, int num_q_heads, int num_kv
     return MKV_OK;
 }
 
-int mkv_attn_set_static_deal(int mode, int unit_cost) {
-    if (mode > 2 || unit_cost > 64) return MKV_ERR_RANGE;
+int mkv_attn_set_static_deal(int mode, int unit_cost, int ratio) {
+    if (mode > 2 || unit_cost > 64 || ratio == 0 || ratio > (1 << 20)) return MKV_ERR_RANGE;
     if (mode >= 0) tuning().static_mode.store(mode, std::memory_order_relaxed);
     if (unit_cost >= 0) tuning().unit_cost.store(unit_cost, std::memory_order_relaxed);
+    if (ratio > 0) tuning().static_ratio.store(ratio, std::memory_order_relaxed);
     return MKV_OK;
 }
 

@@ -111,6 +111,11 @@ def test_prepare_step_and_model_methods_against_the_reference_run(reference_run,
                                max_blocks_per_seq=R.MAX_BLOCKS_PER_SEQ)
     state = mk.KVCacheModelState(mc, ec, pin_swap=pin_swap)
     state.init_kvcache_and_swap(R.NUM_BLOCKS)
+    with torch.inference_mode():        # the model's tensors are inference tensors (worker/model.py:175)
+        _replay(R, ref, state)
+
+
+def _replay(R, ref, state):
     for i, step in enumerate(R.scenario()):
         if step[0] == "forward":
             st = state.prepare_step(step[1], step[2], step[3])

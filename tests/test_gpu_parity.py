@@ -182,12 +182,12 @@ def test_split_rule_extremes(balance, shape, deal):
     c = cases.build_decode_case(seed=2718, B=B, Hq=Hq, Hkv=Hkv, D=128, bs=16, L=1, layer=0, num_blocks_org=nb,
                                 dtype=np.float16, lens=lens)
     check(lib.mkv_attn_configure(-1, -1, -1.0, balance, -1), "mkv_attn_configure")
-    check(lib.mkv_attn_set_static_deal(deal[0], deal[1]), "mkv_attn_set_static_deal")
+    check(lib.mkv_attn_set_static_deal(deal[0], deal[1], 1), "mkv_attn_set_static_deal")
     try:
         o, kp, vp = H.run_decode_step(H.device_case(c))
     finally:
         check(lib.mkv_attn_configure(-1, -1, -1.0, 1.5, -1), "mkv_attn_configure")
-        check(lib.mkv_attn_set_static_deal(1, 1), "mkv_attn_set_static_deal")
+        check(lib.mkv_attn_set_static_deal(1, 3, 8), "mkv_attn_set_static_deal")
     ex = O.paged_attention_exact(c["q"], kp, vp, c["block_table"], c["seq_ids"], c["seq_lens"], 0, c["scale"],
                                  c["num_blocks_org"], 0)
     _close(o, ex)
@@ -211,11 +211,11 @@ def test_many_short_sequences_per_worker(Hq, Hkv, deal):
     nb = int(((lens + 15) // 16).sum()) + 7
     c = cases.build_decode_case(seed=4242 + Hkv, B=B, Hq=Hq, Hkv=Hkv, D=128, bs=16, L=1, layer=0, num_blocks_org=nb,
                                 dtype=np.float16, lens=lens)
-    check(lib.mkv_attn_set_static_deal(deal, -1), "mkv_attn_set_static_deal")
+    check(lib.mkv_attn_set_static_deal(deal, -1, 1), "mkv_attn_set_static_deal")
     try:
         o, kp, vp = H.run_decode_step(H.device_case(c))
     finally:
-        check(lib.mkv_attn_set_static_deal(1, -1), "mkv_attn_set_static_deal")
+        check(lib.mkv_attn_set_static_deal(1, -1, 8), "mkv_attn_set_static_deal")
     ex = O.paged_attention_exact(c["q"], kp, vp, c["block_table"], c["seq_ids"], c["seq_lens"], 0, c["scale"],
                                  c["num_blocks_org"], 0)
     _close(o, ex)
@@ -250,7 +250,7 @@ def test_random_batches_fast_path_against_plain_kernel(seed, deal):
     append when the fixture says so) against the library's plain kernel, which shares none of that machinery and is
     held to the oracle by the tests above."""
     from morphserve_b200._lib import lib, check
-    check(lib.mkv_attn_set_static_deal(deal, seed % 3), "mkv_attn_set_static_deal")
+    check(lib.mkv_attn_set_static_deal(deal, seed % 4, 1 + seed % 2 * 7), "mkv_attn_set_static_deal")
     rs = np.random.RandomState(1000 + seed)
     B, Hq, Hkv, lens = _random_batch(rs)
     nb = int(((lens + 15) // 16).sum()) + 3
@@ -291,7 +291,7 @@ def test_random_batches_fast_path_against_plain_kernel(seed, deal):
             if force_plain:
                 check(lib.mkv_attn_configure(-1, -1, -1.0, -1.0, DEFAULT_LOADER), "mkv_attn_configure")
         outs.append((o, k2, v2))
-    check(lib.mkv_attn_set_static_deal(1, 1), "mkv_attn_set_static_deal")
+    check(lib.mkv_attn_set_static_deal(1, 3, 8), "mkv_attn_set_static_deal")
     (o_fast, k_fast, v_fast), (o_plain, k_plain, v_plain) = outs
     for a, b in zip(k_fast + v_fast, k_plain + v_plain):
         assert torch.equal(a, b), "appended pools differ"
@@ -401,9 +401,9 @@ def test_push_variant_writes_the_column_slice_of_every_destination():
 @pytest.mark.parametrize("seed", range(10))
 def test_plan_kernel_follows_the_stated_rule(seed):
     """What the plan leaves in the workspace against the rules restated on the host (tests/helpers.py), for batches
-    from 1 to 3000 sequences and several split_balance settings.  No sequence longer than the chunk: chunk size, item
-    count and partial-row count of the dynamic deal (`plan_rule`).  Otherwise the static deal: every worker's range
-    of unit records, record by record (`static_deal`)."""
+    from 1 to 3000 sequences and several split_balance settings.  No sequence longer than `ratio` chunks: chunk size, item
+    count and partial-row count of the dynamic deal (`plan_rule`).  A longest sequence of more than `ratio` chunks:
+    the static deal, every worker's range of unit records, record by record (`static_deal`)."""
     import ctypes as C
     from morphserve_b200._lib import lib, check
     from morphserve_b200.worker.kernels._common import attn_workspace
@@ -417,11 +417,12 @@ def test_plan_kernel_follows_the_stated_rule(seed):
     if seed % 3 == 0:
         lens[rs.randint(0, B, size=max(1, B // 10))] = 0            # sequences without any token
     balance = float(rs.choice([0.0, 1.0, 1.5, 4.0]))
-    unit_cost = int(rs.choice([0, 1, 2]))
+    unit_cost = int(rs.choice([0, 1, 3]))
+    ratio = int(rs.choice([1, 8]))
     max_blocks = (int(lens.max()) + 15) // 16
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     check(lib.mkv_attn_configure(-1, -1, -1.0, balance, -1), "mkv_attn_configure")
-    check(lib.mkv_attn_set_static_deal(-1, unit_cost), "mkv_attn_set_static_deal")
+    check(lib.mkv_attn_set_static_deal(1, unit_cost, ratio), "mkv_attn_set_static_deal")
     try:
         ws = attn_workspace(0, B, Hq, Hkv, 128, max_blocks)
         lay = (C.c_int64 * 10)()
@@ -435,16 +436,16 @@ def test_plan_kernel_follows_the_stated_rule(seed):
         raw = ws.tensor.cpu().numpy()
     finally:
         check(lib.mkv_attn_configure(-1, -1, -1.0, 1.5, -1), "mkv_attn_configure")
-        check(lib.mkv_attn_set_static_deal(-1, 1), "mkv_attn_set_static_deal")
+        check(lib.mkv_attn_set_static_deal(1, 3, 8), "mkv_attn_set_static_deal")
     hdr = raw[:64].view(np.int32)
     magic, batch, n_items, chunk, _, _, flags, n_rows, cap, mode, n_workers, n_units = [int(x) for x in hdr[:12]]
     off_items, _, off_wstart, _, _, _, cap_items, cap_units, max_workers, workers = [int(x) for x in lay]
     assert magic == 0x4d4b5631 and batch == B and flags == 0 and cap == cap_items
     exp_chunk, exp_items, exp_rows = H.plan_rule(lens, Hkv, cap, sms, balance)
     longest = (int(lens.max()) + 15) // 16
-    if longest <= exp_chunk:
+    if longest <= ratio * exp_chunk:        # not skewed: chunks from the shared counter (cut or not)
         assert mode == 0 and (chunk, n_items, n_rows) == (exp_chunk, exp_items, exp_rows)
-        assert exp_rows == 0 and n_units == n_items * Hkv
+        assert n_units == n_items * Hkv
         return
     W, wstart, units = H.static_deal(lens, Hkv, workers, cap_items * Hq, G, unit_cost=unit_cost)
     assert B * Hkv + W <= cap_units
