@@ -210,7 +210,9 @@ int mkv_paged_attention_decode_rope_append(
  * Tuning knobs of the decode kernel (process-wide; not needed for normal use):
  * warps per SM and ring stages (values <= 0 keep the current ones) and the
  * number of work units planned per worker warp (<= 0 keeps).  Changing the item
- * factor changes mkv_attn_workspace_bytes: re-query it and plan again.
+ * factor changes mkv_attn_workspace_bytes: re-query it and plan again; changing
+ * warps / stages needs a new plan too (a plan is made for a number of worker
+ * warps; a launch with another number refuses to run, error bit 1).
  * `split_balance` (< 0 keeps; default 1.5): a sequence is only cut into chunks
  * when it is longer than split_balance x the mean number of KV blocks per worker
  * warp, since every cut costs fp32 partial rows and a merge; 0 cuts as finely as
@@ -224,9 +226,10 @@ int mkv_attn_configure(int warps, int stages, double item_factor, double split_b
 /*
  * How the plan deals the launch's K/V tiles to the worker warps (process-wide tuning knobs).
  *   mode 0: always in chunks drawn from a shared counter, longest first (sequences longer than the chunk are cut);
- *   mode 1 (default): as 0 unless the batch is skewed - its longest sequence is longer than `ratio` chunks (default
- *      8); then every worker gets an equal contiguous range of the tile stream, sequences are cut only where a range
- *      ends (all workers finish together) and the pieces are merged in two levels when there are many;
+ *   mode 1 (default): as 0 while no sequence has to be cut (none longer than `ratio` chunks, default 1); otherwise
+ *      every worker gets an equal contiguous range of the tile stream, sequences are cut only where a range ends (all
+ *      workers finish together), pieces that meet in one thread block are merged through shared memory and the rest
+ *      in two levels;
  *   mode 2: equal ranges whenever the workspace allows it.
  * `unit_cost` (default 3): with equal ranges, what starting a unit is worth in tiles - every (sequence, kv head)
  * counts as that many tiles more than it has, so a worker that is dealt many short sequences is dealt fewer tiles.

@@ -70,12 +70,14 @@ struct alignas(256) WsHeader {
     int n_partial_rows;
     int cap_items;
     int mode;           // 0: units = items x kv heads, drawn from work_counter; 1: static ranges per worker (wstart)
-    int n_workers;      // static mode: worker warps that own a range; the launch must bring at least as many
-    int n_units;        // static mode: unit records
+    int n_workers;      // static deal: worker warps that own a range (the launch must bring at least as many);
+                        // dynamic deal: worker warps of the launch the plan was made for (must match exactly)
+    int n_units;        // unit records (static deal) or items x kv heads (dynamic deal)
+    unsigned counter_init;  // dynamic deal: worker w starts on unit w, the counter hands out the units after those
 };
 
 struct WsLayout {
-    size_t items, items_tmp, arrive, wstart, garrive, lse, part_o, total;
+    size_t items, items_tmp, arrive, wstart, wrec, garrive, lse, part_o, total;
     int cap_items;
     int cap_units;   // records the items region holds (static mode needs batch * Hkv + workers)
     int max_workers;
@@ -93,7 +95,7 @@ struct Tuning {
     std::atomic<int> loader{0};        // 0 cp.async, 1 TMA, 2 no fast path at all (testing)
     std::atomic<int> static_mode{1};   // 0 never deal statically, 1 when a sequence must be cut, 2 whenever possible
     std::atomic<int> unit_cost{3};     // static deal: tiles that starting a unit is worth
-    std::atomic<int> static_ratio{8};  // mode 1: static when the longest sequence exceeds this many chunks
+    std::atomic<int> static_ratio{1};  // mode 1: static when the longest sequence exceeds this many chunks
     std::atomic<double> item_factor{4.0};    // work units per worker warp that bound the dynamic item list
     std::atomic<double> split_balance{1.5};  // see plan_balance()
     std::once_flag once;
@@ -140,7 +142,6 @@ static float plan_balance(int sm_count, int num_kv_heads) {
 static int decode_warps() {
     const int w = tuning().warps.load(std::memory_order_relaxed), st = tuning().stages.load(std::memory_order_relaxed);
     if (w == 6 && st == 4) return 6;
-    if (w == 7 && st == 4) return 7;
     return 8;
 }
 
@@ -164,6 +165,7 @@ static WsLayout make_layout(int sm_count, int batch, int num_q_heads, int num_kv
     L.items_tmp = off;   off = align256(off + (size_t)cap * 2 * sizeof(int4));
     L.arrive = off;      off = align256(off + (size_t)batch * num_kv_heads * sizeof(int));
     L.wstart = off;      off = align256(off + (size_t)(L.max_workers + 1) * sizeof(int));
+    L.wrec = off;        off = align256(off + (size_t)L.max_workers * 2 * sizeof(int4));  // first record of each worker
     L.garrive = off;     off = align256(off + (size_t)2 * L.max_workers * sizeof(int));
     L.lse = off;         off = align256(off + (size_t)cap * num_q_heads * sizeof(float));
     L.part_o = off;      off = align256(off + (size_t)cap * num_q_heads * head_dim * sizeof(float));
@@ -209,6 +211,7 @@ struct PlanArgs {
     int4 *items_tmp;   // [cap_items] x 2; static mode: int prefix[batch + 1]
     int *arrive;       // [batch * Hkv]
     int *wstart;       // [max_workers + 1]
+    int4 *wrec;        // [max_workers] x 2: copy of every worker's first record (static deal)
     int *garrive;      // [2 * max_workers]
     const int32_t *seq_lens;
     const int32_t *seq_ids;
@@ -322,10 +325,11 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(const PlanArgs a) {
     for (int i = tid; i < batch * a.num_kv_heads; i += blockDim.x) a.arrive[i] = 0;
     for (int i = tid; i < 2 * a.max_workers; i += blockDim.x) a.garrive[i] = 0;
 
-    // ---- static deal: taken when the batch is skewed - its longest sequence would be cut into many chunks.  Chunks of
-    // a fixed size then leave the workers unevenly loaded and one warp with a long merge at the very end; equal
-    // ranges make every worker finish together and the pieces are merged in two levels.  (With mild cutting -
-    // a few chunks per sequence - drawing chunks from the counter measured a little faster.)
+    // ---- static deal: taken when some sequence would have to be cut (longer than static_ratio chunks; default 1).
+    // A cut costs partial rows and a merge either way; chunks of a fixed size leave the workers unevenly loaded and,
+    // for one very long sequence, one warp with a long merge at the very end, while equal ranges make every worker
+    // finish together, most pieces of a cut sequence meet inside one thread block (merged through shared memory) and
+    // the rest is merged in two levels.
     __shared__ int s_nonempty;
     if (tid == 0) s_nonempty = 0;
     __syncthreads();
@@ -366,7 +370,14 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(const PlanArgs a) {
             int tot;
             const int off = plan_scan(n, tot, warp_sums);
             if (w <= a.max_workers) a.wstart[w] = carry_u + off;  // workers >= W own an empty range
-            if (w < W) static_walk(a, prefix, T, W, w, items + 2 * (size_t)(carry_u + off));
+            if (w < W) {
+                int4 *mine = items + 2 * (size_t)(carry_u + off);
+                static_walk(a, prefix, T, W, w, mine);
+                if (n > 0) {  // a copy at a place the worker can address before it has read anything else
+                    a.wrec[2 * w] = mine[0];
+                    a.wrec[2 * w + 1] = mine[1];
+                }
+            }
             carry_u += tot;
         }
         if (tid == 0) {
@@ -382,6 +393,7 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(const PlanArgs a) {
             hdr->mode = 1;
             hdr->n_workers = W;
             hdr->n_units = carry_u;
+            hdr->counter_init = 0;
         }
         return;
     }
@@ -441,14 +453,18 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(const PlanArgs a) {
         hdr->batch = batch;
         hdr->n_items = n_items;
         hdr->chunk_blocks = chunk;
-        hdr->work_counter = 0;
+        // worker w of the launch starts on unit w without asking (the units are sorted longest first, so these are the
+        // longest ones either way); the counter hands out what is left
+        const long long units = (long long)n_items * a.num_kv_heads;
+        hdr->counter_init = (unsigned)(units < a.workers ? units : a.workers);
+        hdr->work_counter = hdr->counter_init;
         hdr->done_counter = 0;
         hdr->error_flags = (carry_items > cap_items) ? 4 : 0;
         hdr->n_partial_rows = carry_rows;
         hdr->cap_items = cap_items;
         hdr->mode = 0;
-        hdr->n_workers = 0;
-        hdr->n_units = n_items * a.num_kv_heads;
+        hdr->n_workers = a.workers;
+        hdr->n_units = (int)units;
     }
 }
 
@@ -569,6 +585,7 @@ struct AttnParams {
     const int4 *items;
     int *arrive;
     const int *wstart;  // static deal: worker w owns the unit records [wstart[w], wstart[w + 1])
+    const int4 *wrec;   // static deal: copy of worker w's first record at [2w, 2w + 1]
     int *garrive;       // static deal: arrival counters of the piece groups of a two-level merge
     float *lse;
     float *part_o;
@@ -682,6 +699,24 @@ __device__ __forceinline__ int merge_fan_in(int nsplit) {
     return f;
 }
 
+// ---- CTA-local merge (static deal, groups of up to 8 query heads) -------------------------------------------
+// With the static deal consecutive workers are the warps of one thread block, so most pieces of a cut (sequence,
+// head) belong to warps of the SAME block.  Those are merged through shared memory: a piece is parked as fp32 rows
+// [8][128] plus 8 lse values, either in its warp's ring (the piece that starts a (sequence, head): it is the warp's
+// last unit, the ring is idle by then) or in the warp's "head slot" behind the rings (the piece that continues one:
+// the warp's first unit), and the last of the block's pieces to finish folds them - no global partial rows, no
+// device-wide fence, no global atomic.  Only a (sequence, head) that spans several blocks goes on to the global merge,
+// one row per block.
+constexpr int kSlotBytes = 8 * kD * 4 + 8 * 4;  // 4128
+
+template <int WARPS, int STAGES, bool TMA>
+__device__ __forceinline__ float *parked_piece(uint8_t *smem, int x, bool starts_pair) {
+    uint8_t *at = starts_pair ? smem + (size_t)x * (STAGES * kStageBytes)
+                              : smem + (size_t)WARPS * STAGES * kStageBytes + (TMA ? WARPS * STAGES * 8 : 0) +
+                                    (size_t)x * kSlotBytes;
+    return reinterpret_cast<float *>(at);
+}
+
 struct WorkMeta {
     bool valid;
     int b, h, start, nblk, split, nsplit, prow, len;
@@ -706,10 +741,22 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
     // Everything the plan left for this launch, requested in ONE round trip before any of it is looked at: the
     // header's first and third 16 bytes (magic, batch, n_items, chunk | cap_items, mode, n_workers, n_units) and,
     // for the static deal, this worker's range of unit records.
-    const int wid = warp * (int)gridDim.x + (int)blockIdx.x;  // consecutive workers sit on different SMs
+    const int wid = (int)blockIdx.x * WARPS + warp;  // consecutive workers are the warps of one block (CTA-local merge)
+    // arrival counters of the CTA-local merge, one per warp (keyed by the first warp of a group of pieces)
+    int *grp_cnt = reinterpret_cast<int *>(smem + (size_t)WARPS * STAGES * kStageBytes + (TMA ? WARPS * STAGES * 8 : 0) +
+                                           (size_t)WARPS * kSlotBytes);
     const int4 hdr_a = __ldcg(reinterpret_cast<const int4 *>(hdr));
     const int4 hdr_c = __ldcg(reinterpret_cast<const int4 *>(&hdr->cap_items));
     const unsigned range_lo = (unsigned)__ldcg(p.wstart + wid), range_hi = (unsigned)__ldcg(p.wstart + wid + 1);
+    // ... and the worker's FIRST unit record, from where it would be under either deal (both addresses lie inside the
+    // workspace whatever the plan did): the static deal's copy, or unit number `wid` of the dynamic deal
+    const int4 rec_s0 = __ldcg(p.wrec + 2 * wid), rec_s1 = __ldcg(p.wrec + 2 * wid + 1);
+    const int first_item = wid / p.pool.num_kv_heads;
+    const int4 rec_d0 = __ldcg(p.items + 2 * first_item), rec_d1 = __ldcg(p.items + 2 * first_item + 1);
+    if (!HI) {
+        if (threadIdx.x < WARPS) grp_cnt[threadIdx.x] = 0;
+        __syncthreads();  // the only block-wide barrier of the kernel, before any work (the loads above are in flight)
+    }
     if ((unsigned)hdr_a.x != kMagic || hdr_a.y != p.batch) {  // no plan for this batch: refuse, touch nothing
         if (threadIdx.x == 0) atomicOr(&hdr->error_flags, 2);
         return;
@@ -729,14 +776,16 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
     const int Hkv = p.pool.num_kv_heads;
     const int G = p.group;
     const bool static_deal = hdr_c.y == 1;
-    if (static_deal && (int)(gridDim.x * WARPS) < hdr_c.z) {  // planned for more workers than this launch has
+    // planned for more workers than this launch has (static), or for another number (dynamic: the first units are
+    // dealt by worker number)
+    if (static_deal ? (int)(gridDim.x * WARPS) < hdr_c.z : (int)(gridDim.x * WARPS) != hdr_c.z) {
         if (threadIdx.x == 0) atomicOr(&hdr->error_flags, 2);
         return;
     }
     // static deal: this worker's unit records are [my_next, my_end).  Lane l keeps record win_base + l in registers
     // (a window of 32 records, refilled when it runs out), so that claiming a unit is a shuffle, not a load.
-    unsigned my_next = static_deal ? range_lo : 0u, my_end = static_deal ? range_hi : 0u;
-    unsigned win_base = my_next;
+    unsigned my_next = static_deal ? range_lo + 1u : 0u, my_end = static_deal ? range_hi : 0u;
+    unsigned win_base = static_deal ? range_lo : 0u;
     int4 win_a = make_int4(0, 0, 0, 0), win_b = make_int4(0, 0, 0, 0);
     auto load_window = [&]() {
         const unsigned i = win_base + (unsigned)lane;
@@ -746,15 +795,17 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
         }
     };
     if (static_deal) load_window();
-    const unsigned total_units = static_deal ? my_end : (unsigned)hdr_a.z * (unsigned)Hkv;
+    const unsigned total_units = static_deal ? my_end : (unsigned)hdr_c.w;
     const bool row0 = g < G, row1 = HI && (g + 8) < G;
 
     // Claiming the next unit is a chain of three dependent global accesses (counter ->
     // unit descriptor -> block ids).  It is cut into three steps that run one per tile
     // iteration, so that each step finds the previous one's result already landed.
-    int fstage = 0;  // 0 claim, 1 read descriptor, 2 read block ids, 3 done
+    // The first unit needs no claim: its record came with the header (stage 2 = fetch its block ids).
+    const bool first_valid = static_deal ? range_lo < range_hi : (unsigned)wid < total_units;
+    int fstage = first_valid ? 2 : 3;  // 0 claim, 1 read descriptor, 2 read block ids, 3 done
     unsigned f_idx = 0;
-    int4 f_it = make_int4(0, 0, 0, 0), f_it1 = make_int4(0, 0, 0, 0);
+    int4 f_it = static_deal ? rec_s0 : rec_d0, f_it1 = static_deal ? rec_s1 : rec_d1;
     auto fetch_step = [&](WorkMeta &m) {
         if (fstage == 0 && static_deal) {
             // the record comes out of the window by shuffle; only the block ids are fetched (asynchronously: they
@@ -864,7 +915,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
     bool failed = false;
 
     WorkMeta nxt;
-    nxt.valid = false;
+    nxt.valid = first_valid;
+    nxt.h = wid - first_item * Hkv;  // dynamic deal: unit `wid` = (item wid / Hkv, head wid % Hkv); static: from the record
     while (fstage < 3) fetch_step(nxt);
     while (nxt.valid) {
         const WorkMeta cur = nxt;
@@ -1139,67 +1191,142 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
                 }
             }
         } else {
-            RowMap map;
-            if (static_deal) {
-                map = RowMap{2 * (int64_t)cur.prow, 2, 1, G, 0};  // cur.prow = first owner of this (sequence, head)
-            } else {
-                map = RowMap{(int64_t)cur.prow - cur.split, 1, 0, p.num_q_heads, hq0};
-            }
-            const int64_t e0 = map.elem_row(cur.split, 0);
-            float *po = p.part_o + e0 * kD;
-            float *pl = p.lse + e0;
-#pragma unroll
-            for (int n = 0; n < 16; ++n) {
-                if (row0)
-                    __stcg(reinterpret_cast<float2 *>(po + (int64_t)g * kD + n * 8 + 2 * t),
-                           make_float2(oacc[n][0] * inv0, oacc[n][1] * inv0));
-                if (row1)
-                    __stcg(reinterpret_cast<float2 *>(po + (int64_t)(g + 8) * kD + n * 8 + 2 * t),
-                           make_float2(oacc[n][2] * inv1, oacc[n][3] * inv1));
-            }
-            if (t == 0) {
-                if (row0) __stcg(pl + g, log2f(l0) + m0);
-                if (row1) __stcg(pl + g + 8, log2f(l1) + m1);
-            }
-            __threadfence();
-            __syncwarp();
-            // Announce the piece; whoever announces last merges.  With many pieces (static deal only) the pieces form
-            // groups of F: the last piece of a group folds the group into its first row, and the last GROUP to finish
-            // folds those rows into the output, so no warp ever reads more than F + pieces/F rows in a row.
-            const int F = static_deal ? merge_fan_in(cur.nsplit) : cur.nsplit;
-            int *cnt = p.arrive + (int64_t)cur.b * Hkv + cur.h;
-            bool last = true;
-            int top_n = cur.nsplit, top_step = 1;
-            if (F < cur.nsplit) {
-                const int grp = cur.split / F;
-                const int gsize = min(F, cur.nsplit - grp * F);
-                // counter of the group: one per partial row, indexed by the row of the group's first piece
-                int *gc = p.garrive + (map.base + (int64_t)(grp * F) * map.stride + (grp == 0 ? map.first_off : 0));
-                int old = 0;
-                if (lane == 0) old = atomicAdd(gc, 1);
-                old = __shfl_sync(0xffffffffu, old, 0);
-                last = old == gsize - 1;
-                if (last) {
-                    __threadfence();
-                    if (lane == 0) *gc = 0;
-                    if (gsize > 1) {
-                        merge_rows<false>(p, cur.b, hq0, G, map, grp * F, 1, gsize, lane);
+            // Announce a piece (or a block's group of pieces) of a cut (sequence, head) whose partial row is in the
+            // workspace; whoever announces last merges.  With many rows the rows form groups of F: the last row of a
+            // group folds the group into its first row, and the last GROUP to finish folds those rows into the
+            // output, so no warp ever reads more than F + rows/F rows in a row.
+            auto announce = [&](const RowMap &map, int split, int nsplit, bool two_level) {
+                const int F = two_level ? merge_fan_in(nsplit) : nsplit;
+                int *cnt = p.arrive + (int64_t)cur.b * Hkv + cur.h;
+                bool last = true;
+                int top_n = nsplit, top_step = 1;
+                if (F < nsplit) {
+                    const int grp = split / F;
+                    const int gsize = min(F, nsplit - grp * F);
+                    // counter of the group: one per partial row, indexed by the row of the group's first piece
+                    int *gc = p.garrive + (map.base + (int64_t)(grp * F) * map.stride + (grp == 0 ? map.first_off : 0));
+                    int old = 0;
+                    if (lane == 0) old = atomicAdd(gc, 1);
+                    old = __shfl_sync(0xffffffffu, old, 0);
+                    last = old == gsize - 1;
+                    if (last) {
                         __threadfence();
-                        __syncwarp();
+                        if (lane == 0) *gc = 0;
+                        if (gsize > 1) {
+                            merge_rows<false>(p, cur.b, hq0, G, map, grp * F, 1, gsize, lane);
+                            __threadfence();
+                            __syncwarp();
+                        }
+                    }
+                    top_n = (nsplit + F - 1) / F;
+                    top_step = F;
+                }
+                if (last) {
+                    int old = 0;
+                    if (lane == 0) old = atomicAdd(cnt, 1);
+                    old = __shfl_sync(0xffffffffu, old, 0);
+                    if (old == top_n - 1) {  // every row of this (sequence, kv head) is in the workspace
+                        __threadfence();
+                        if (lane == 0) *cnt = 0;
+                        merge_rows<true>(p, cur.b, hq0, G, map, 0, top_step, top_n, lane);
                     }
                 }
-                top_n = (cur.nsplit + F - 1) / F;
-                top_step = F;
-            }
-            if (last) {
-                int old = 0;
-                if (lane == 0) old = atomicAdd(cnt, 1);
-                old = __shfl_sync(0xffffffffu, old, 0);
-                if (old == top_n - 1) {  // every piece (group) of this (sequence, kv head) is in the workspace
-                    __threadfence();
-                    if (lane == 0) *cnt = 0;
-                    merge_rows<true>(p, cur.b, hq0, G, map, 0, top_step, top_n, lane);
+            };
+
+            if (static_deal && !HI) {
+                // ---- CTA-local merge through shared memory (see parked_piece) ----
+                const int f = cur.prow, l = f + cur.nsplit - 1;      // owners (worker numbers) of the first / last piece
+                const int cta0 = (int)blockIdx.x * WARPS;
+                const int wlo = max(f, cta0) - cta0, whi = min(l, cta0 + WARPS - 1) - cta0;  // this block's pieces
+                const int gsz = whi - wlo + 1;
+                __syncwarp();  // every lane is done reading the last tile: the ring may be written
+                float *mine = parked_piece<WARPS, STAGES, TMA>(smem, warp, cur.split == 0);
+#pragma unroll
+                for (int n = 0; n < 16; ++n)
+                    if (row0)
+                        *reinterpret_cast<float2 *>(mine + g * kD + n * 8 + 2 * t) =
+                            make_float2(oacc[n][0] * inv0, oacc[n][1] * inv0);
+                if (t == 0 && row0) mine[8 * kD + g] = log2f(l0) + m0;
+                __syncwarp();
+                bool group_last = true;
+                if (gsz > 1) {
+                    int old = 0;
+                    if (lane == 0) {
+                        __threadfence_block();
+                        old = atomicAdd(&grp_cnt[wlo], 1);
+                    }
+                    old = __shfl_sync(0xffffffffu, old, 0);
+                    group_last = old == gsz - 1;
                 }
+                if (group_last) {
+                    __threadfence_block();
+                    const int cta_f = f / WARPS, ng = l / WARPS - cta_f + 1;  // blocks this (sequence, head) spans
+                    const int gi = (int)blockIdx.x - cta_f;
+                    // rows of the global merge: block c owns rows 2c (a (sequence, head) entering it) and 2c + 1 (one
+                    // leaving it), so group gi of a (sequence, head) starting in block cta_f has row 2 (cta_f + gi) + (gi == 0)
+                    const RowMap map{2 * (int64_t)cta_f, 2, 1, G, 0};
+                    for (int r = 0; r < G; ++r) {
+                        float m = -INFINITY;
+                        for (int x = wlo; x <= whi; ++x)
+                            m = fmaxf(m, parked_piece<WARPS, STAGES, TMA>(smem, x, cta0 + x == f)[8 * kD + r]);
+                        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                        float wsum = 0.f;
+                        for (int x = wlo; x <= whi; ++x) {
+                            const float *pp = parked_piece<WARPS, STAGES, TMA>(smem, x, cta0 + x == f);
+                            const float e = exp2f(pp[8 * kD + r] - m);
+                            const float4 v = *reinterpret_cast<const float4 *>(pp + r * kD + lane * 4);
+                            acc.x += e * v.x; acc.y += e * v.y; acc.z += e * v.z; acc.w += e * v.w;
+                            wsum += e;
+                        }
+                        const float inv = 1.f / wsum;
+                        if (ng == 1) {  // the whole (sequence, head) lies in this block: this is the output
+                            __half2 h01 = __floats2half2_rn(acc.x * inv, acc.y * inv);
+                            __half2 h23 = __floats2half2_rn(acc.z * inv, acc.w * inv);
+                            uint2 pk;
+                            pk.x = *reinterpret_cast<uint32_t *>(&h01);
+                            pk.y = *reinterpret_cast<uint32_t *>(&h23);
+                            const int64_t at =
+                                (int64_t)cur.b * p.out_row_stride + p.out_col_off + (int64_t)(hq0 + r) * kD + lane * 4;
+                            for (int o = 0; o < p.n_out; ++o) *reinterpret_cast<uint2 *>(p.out[o] + at) = pk;
+                        } else {
+                            const int64_t e = map.elem_row(gi, r);
+                            __stcg(reinterpret_cast<float4 *>(p.part_o + e * kD + lane * 4),
+                                   make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv));
+                            if (lane == 0) __stcg(p.lse + e, log2f(wsum) + m);
+                        }
+                    }
+                    if (ng > 1) {
+                        __threadfence();
+                        __syncwarp();
+                        announce(map, gi, ng, true);
+                    }
+                }
+            } else {
+                RowMap map;
+                if (static_deal) {
+                    map = RowMap{2 * (int64_t)cur.prow, 2, 1, G, 0};  // cur.prow = first owner of this (sequence, head)
+                } else {
+                    map = RowMap{(int64_t)cur.prow - cur.split, 1, 0, p.num_q_heads, hq0};
+                }
+                const int64_t e0 = map.elem_row(cur.split, 0);
+                float *po = p.part_o + e0 * kD;
+                float *pl = p.lse + e0;
+#pragma unroll
+                for (int n = 0; n < 16; ++n) {
+                    if (row0)
+                        __stcg(reinterpret_cast<float2 *>(po + (int64_t)g * kD + n * 8 + 2 * t),
+                               make_float2(oacc[n][0] * inv0, oacc[n][1] * inv0));
+                    if (row1)
+                        __stcg(reinterpret_cast<float2 *>(po + (int64_t)(g + 8) * kD + n * 8 + 2 * t),
+                               make_float2(oacc[n][2] * inv1, oacc[n][3] * inv1));
+                }
+                if (t == 0) {
+                    if (row0) __stcg(pl + g, log2f(l0) + m0);
+                    if (row1) __stcg(pl + g + 8, log2f(l1) + m1);
+                }
+                __threadfence();
+                __syncwarp();
+                announce(map, cur.split, cur.nsplit, static_deal);
             }
         }
     }
@@ -1213,7 +1340,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
         const unsigned workers = gridDim.x * WARPS;
         const unsigned d = atomicAdd(&hdr->done_counter, 1u);
         if (d == workers - 1) {
-            hdr->work_counter = 0;
+            hdr->work_counter = hdr->counter_init;
             hdr->done_counter = 0;
             if (p.n_ready) {  // every worker's stores are behind its fence and its count: tell the destinations
                 __threadfence_system();
@@ -1334,7 +1461,9 @@ __global__ void attn_decode_plain_kernel(const __grid_constant__ PoolView pool, 
 // ------------------------------------------------------------------ host side
 template <int WARPS, int STAGES, bool HI, bool TMA>
 static cudaError_t launch_decode_one(const AttnParams &p, const TmaMaps &tm, int sm_count, cudaStream_t s) {
-    const int smem = WARPS * STAGES * kStageBytes + (TMA ? WARPS * STAGES * 8 : 0);
+    // rings (+ TMA barriers) + for groups of up to 8 query heads the head slots and counters of the CTA-local merge
+    const int smem = WARPS * STAGES * kStageBytes + (TMA ? WARPS * STAGES * 8 : 0) +
+                     (HI ? 0 : WARPS * kSlotBytes + WARPS * (int)sizeof(int));
     static std::atomic<bool> configured[64];  // per device; setting the attribute twice is harmless
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1361,7 +1490,6 @@ static cudaError_t launch_decode(const AttnParams &p, const TmaMaps *tm, int sm_
 static cudaError_t launch_decode_configured(const AttnParams &p, const TmaMaps *tm, int sms, cudaStream_t s) {
     const int w = decode_warps();
     if (w == 6) return launch_decode<6, 4>(p, tm, sms, s);
-    if (w == 7) return launch_decode<7, 4>(p, tm, sms, s);
     return launch_decode<8, 3>(p, tm, sms, s);
 }
 
@@ -1430,6 +1558,7 @@ static void launch_plan(char *ws, const WsLayout &L, const int32_t *seq_lens, co
     a.items_tmp = (int4 *)(ws + L.items_tmp);
     a.arrive = (int *)(ws + L.arrive);
     a.wstart = (int *)(ws + L.wstart);
+    a.wrec = (int4 *)(ws + L.wrec);
     a.garrive = (int *)(ws + L.garrive);
     a.seq_lens = seq_lens;
     a.seq_ids = seq_ids;
@@ -1458,6 +1587,7 @@ static void fill_workspace_params(AttnParams &p, char *ws, const WsLayout &L) {
     p.items = (const int4 *)(ws + L.items);
     p.arrive = (int *)(ws + L.arrive);
     p.wstart = (const int *)(ws + L.wstart);
+    p.wrec = (const int4 *)(ws + L.wrec);
     p.garrive = (int *)(ws + L.garrive);
     p.lse = (float *)(ws + L.lse);
     p.part_o = (float *)(ws + L.part_o);

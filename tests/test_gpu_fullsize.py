@@ -85,7 +85,7 @@ def test_baseline_decode_config_full_size(name, balance, deal):
         torch.cuda.synchronize()
     finally:
         check(lib.mkv_attn_configure(-1, -1, -1.0, 1.5, -1), "mkv_attn_configure")
-        check(lib.mkv_attn_set_static_deal(1, -1, 8), "mkv_attn_set_static_deal")
+        check(lib.mkv_attn_set_static_deal(1, -1, 1), "mkv_attn_set_static_deal")
     bm = job.bm
     lens = job.lens_dev
     # integers: every sequence owns exactly ceil(len/16) blocks, all distinct, bitmap consistent

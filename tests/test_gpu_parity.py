@@ -187,7 +187,7 @@ def test_split_rule_extremes(balance, shape, deal):
         o, kp, vp = H.run_decode_step(H.device_case(c))
     finally:
         check(lib.mkv_attn_configure(-1, -1, -1.0, 1.5, -1), "mkv_attn_configure")
-        check(lib.mkv_attn_set_static_deal(1, 3, 8), "mkv_attn_set_static_deal")
+        check(lib.mkv_attn_set_static_deal(1, 3, 1), "mkv_attn_set_static_deal")
     ex = O.paged_attention_exact(c["q"], kp, vp, c["block_table"], c["seq_ids"], c["seq_lens"], 0, c["scale"],
                                  c["num_blocks_org"], 0)
     _close(o, ex)
@@ -215,7 +215,7 @@ def test_many_short_sequences_per_worker(Hq, Hkv, deal):
     try:
         o, kp, vp = H.run_decode_step(H.device_case(c))
     finally:
-        check(lib.mkv_attn_set_static_deal(1, -1, 8), "mkv_attn_set_static_deal")
+        check(lib.mkv_attn_set_static_deal(1, -1, 1), "mkv_attn_set_static_deal")
     ex = O.paged_attention_exact(c["q"], kp, vp, c["block_table"], c["seq_ids"], c["seq_lens"], 0, c["scale"],
                                  c["num_blocks_org"], 0)
     _close(o, ex)
@@ -291,7 +291,7 @@ def test_random_batches_fast_path_against_plain_kernel(seed, deal):
             if force_plain:
                 check(lib.mkv_attn_configure(-1, -1, -1.0, -1.0, DEFAULT_LOADER), "mkv_attn_configure")
         outs.append((o, k2, v2))
-    check(lib.mkv_attn_set_static_deal(1, 3, 8), "mkv_attn_set_static_deal")
+    check(lib.mkv_attn_set_static_deal(1, 3, 1), "mkv_attn_set_static_deal")
     (o_fast, k_fast, v_fast), (o_plain, k_plain, v_plain) = outs
     for a, b in zip(k_fast + v_fast, k_plain + v_plain):
         assert torch.equal(a, b), "appended pools differ"
@@ -436,16 +436,18 @@ def test_plan_kernel_follows_the_stated_rule(seed):
         raw = ws.tensor.cpu().numpy()
     finally:
         check(lib.mkv_attn_configure(-1, -1, -1.0, 1.5, -1), "mkv_attn_configure")
-        check(lib.mkv_attn_set_static_deal(1, 3, 8), "mkv_attn_set_static_deal")
+        check(lib.mkv_attn_set_static_deal(1, 3, 1), "mkv_attn_set_static_deal")
     hdr = raw[:64].view(np.int32)
-    magic, batch, n_items, chunk, _, _, flags, n_rows, cap, mode, n_workers, n_units = [int(x) for x in hdr[:12]]
+    magic, batch, n_items, chunk, counter, _, flags, n_rows, cap, mode, n_workers, n_units, counter_init = \
+        [int(x) for x in hdr[:13]]
     off_items, _, off_wstart, _, _, _, cap_items, cap_units, max_workers, workers = [int(x) for x in lay]
     assert magic == 0x4d4b5631 and batch == B and flags == 0 and cap == cap_items
     exp_chunk, exp_items, exp_rows = H.plan_rule(lens, Hkv, cap, sms, balance)
     longest = (int(lens.max()) + 15) // 16
     if longest <= ratio * exp_chunk:        # not skewed: chunks from the shared counter (cut or not)
         assert mode == 0 and (chunk, n_items, n_rows) == (exp_chunk, exp_items, exp_rows)
-        assert n_units == n_items * Hkv
+        assert n_units == n_items * Hkv and n_workers == workers
+        assert counter == counter_init == min(n_units, workers)     # worker w starts on unit w without a claim
         return
     W, wstart, units = H.static_deal(lens, Hkv, workers, cap_items * Hq, G, unit_cost=unit_cost)
     assert B * Hkv + W <= cap_units
