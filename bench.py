@@ -1058,30 +1058,53 @@ def reference_gpu_column(job, steps):
         return {"unavailable": f"{type(e).__name__}: {str(e)[:300]}"}
 
 
-def headshard_column(ctx, K, W, layers=8):
+def headshard_column(world, K, W, layers=8, timeout_s=180):
     """The head-sharded CodeLlama-34B variant at the current world size (BASELINE configs[4]): every rank holds
     Hkv / N kv heads of all 512 * N sequences; the output shards are all-gathered per layer (NCCL), or pushed into
-    every rank's full-width matrix from the attention epilogue.  `layers` of the model's 48 layers are run (the per-layer
-    cost does not depend on the layer count; this bounds memory and time next to the main workload)."""
-    import morphserve_b200
-    out = {"layers_run": layers, "layers_of_model": 48}
-    if 8 % ctx.world != 0:
-        return {"unavailable": f"8 kv heads do not divide over {ctx.world} ranks"}
-    morphserve_b200.set_fused_decode_append(False)
-    try:
-        for name in ("codellama-34b-gqa-decode-headshard", "codellama-34b-gqa-decode-headshard-push"):
-            base = dict(WORKLOADS[name], L=layers)
-            ww = shard_workload(base, ctx.rank, ctx.world)
+    every rank's full-width matrix from the attention epilogue, each rank then waiting for the others' ready flags.
+    `layers` of the model's 48 layers are run (the per-layer cost does not depend on the layer count; this bounds
+    memory and time next to the main workload).
+
+    Called by rank 0 only, after the main job has released its memory, while the other ranks wait at a barrier: each
+    form runs as its OWN torchrun job (fresh processes, fresh communicators) under a hard time limit, so that trouble
+    in this side column - a collective that never completes, say - costs the column and never the main line."""
+    import signal
+    import subprocess
+    out = {"layers_run": layers, "layers_of_model": 48, "how": "separate torchrun job per form, bounded time"}
+    if 8 % world != 0:
+        return {"unavailable": f"8 kv heads do not divide over {world} ranks"}
+    env = {k: v for k, v in os.environ.items()
+           if not (k in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "LOCAL_WORLD_SIZE", "GROUP_RANK", "ROLE_RANK", "ROLE_NAME",
+                         "ROLE_WORLD_SIZE", "GROUP_WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT", "OMP_NUM_THREADS")
+                   or k.startswith("TORCHELASTIC") or k.startswith("TORCH_NCCL") or k.startswith("PET_"))}
+    env["NCCL_NVLS_ENABLE"] = "0"
+    port = 29700 + os.getpid() % 200
+    for i, name in enumerate(("codellama-34b-gqa-decode-headshard", "codellama-34b-gqa-decode-headshard-push")):
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world),
+               "--master-addr", "127.0.0.1", "--master-port", str(port + i), os.path.join(ROOT, "bench.py"),
+               "--gpus", str(world), "--workload", name, "--layers", str(layers), "--steps", str(K), "--warmup", str(W),
+               "--no-e2e", "--no-cpu", "--no-extras", "--min-seconds", "0"]
+        try:
+            proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env,
+                                    start_new_session=True)
             try:
-                r = run_decode(ctx, ww, name, K, W, False, min_seconds=0.0, with_roofline=False)
-                out[name] = {"value": r["value"], "unit": "tokens/s", "ms_per_step": r["ms_per_step"],
-                             "ms_per_layer": r["ms_per_step"] / layers,
-                             "tokens_per_s_at_48_layers": r["value"] * layers / 48}
-            except Exception as e:
-                out[name] = {"unavailable": f"{type(e).__name__}: {str(e)[:300]}"}
-            torch.cuda.empty_cache()
-    finally:
-        morphserve_b200.set_fused_decode_append(True)
+                stdout, stderr = proc.communicate(timeout=timeout_s)
+            except subprocess.TimeoutExpired:
+                os.killpg(proc.pid, signal.SIGKILL)         # the job's own process group, nothing else
+                proc.communicate()
+                out[name] = {"unavailable": f"no result within {timeout_s} s"}
+                continue
+            lines = [ln for ln in stdout.splitlines() if ln.startswith('{"metric')]
+            if proc.returncode != 0 or not lines:
+                why = [ln.strip() for ln in stderr.splitlines() if "Error" in ln or "error" in ln]
+                out[name] = {"unavailable": f"exit {proc.returncode}: {why[-1][:200] if why else ''}"}
+                continue
+            r = json.loads(lines[-1])
+            out[name] = {"value": r["value"], "unit": "tokens/s", "ms_per_step": r["ms_per_step"],
+                         "ms_per_layer": r["ms_per_step"] / layers,
+                         "tokens_per_s_at_48_layers": r["value"] * layers / 48}
+        except Exception as e:
+            out[name] = {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
     return out
 
 
@@ -1098,6 +1121,8 @@ def main():
     ap.add_argument("--no-extras", action="store_true",
                     help="default workload only: skip the further columns (drop-in defaults, the reference's kernels on "
                          "this GPU, the other workloads, the head-sharded variant)")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="decode workloads: run this many layers instead of the model's (what the head-sharded column does)")
     ap.add_argument("--min-seconds", type=float, default=2.0,
                     help="repeat the timed block of --steps steps (from the same starting state) until this much time "
                          "has been measured; the median block is reported")
@@ -1115,6 +1140,8 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     base = WORKLOADS[args.workload]
+    if args.layers > 0 and "L" in base:
+        base = dict(base, L=args.layers)
     if base.get("prefill"):
         assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
         torch.cuda.set_device(local_rank)
@@ -1252,7 +1279,16 @@ def main():
         extras["other_workloads"] = others
         torch.cuda.empty_cache()
     if default_run and world > 1:
-        extras["headshard"] = headshard_column(ctx, K=3, W=2)
+        # rank 0 runs the column's own jobs; the others wait on the HOST (a key in the rendezvous store), so that no
+        # collective kernel of this job spins on the GPUs the column is measured on
+        import datetime
+        torch.cuda.synchronize()
+        store = dist.distributed_c10d._get_default_store()
+        if rank == 0:
+            extras["headshard"] = headshard_column(world, K=3, W=2)
+            store.set("mkv_headshard_done", "1")
+        else:
+            store.wait(["mkv_headshard_done"], datetime.timedelta(seconds=600))
 
     if rank == 0:
         line = {

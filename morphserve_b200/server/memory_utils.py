@@ -59,8 +59,9 @@ def attach_kvcache_chunk(engine, k_cache_new: torch.Tensor, v_cache_new: torch.T
 def if_kv_cache_unused(engine, layer_id=None) -> bool:
     """True when the LAST chunk holds no live block (server/memory_utils.py:529-544)."""
     model = engine.model
-    kv_cache_index = len(model.k_cache_new) - 1
-    assert kv_cache_index >= 0, f"[Engine] Layer {layer_id} is not quantized, no KV cache tensors to free"
+    last = len(model.k_cache_new) - 1
+    assert last >= 0, f"no elastic KV chunk is attached (layer {layer_id}): nothing to check"
+    kv_cache_index = last
     n = model.kv_cache_new_block_size
     start = model.gpu_block_manager.num_blocks_org + n * kv_cache_index
     return bool(model.gpu_block_manager.is_block_free[start:start + n].all())
@@ -69,10 +70,10 @@ def if_kv_cache_unused(engine, layer_id=None) -> bool:
 def free_kv_cache_tensors(engine, layer_id=None) -> None:
     """Drop the last chunk's tensors (server/memory_utils.py:602-613)."""
     model = engine.model
-    kv_cache_index = len(model.k_cache_new) - 1
-    assert kv_cache_index >= 0, f"[Engine] Layer {layer_id} is not quantized, no KV cache tensors to free"
-    del model.k_cache_new[kv_cache_index]
-    del model.v_cache_new[kv_cache_index]
+    last = len(model.k_cache_new) - 1
+    assert last >= 0, f"no elastic KV chunk is attached (layer {layer_id}): nothing to drop"
+    del model.k_cache_new[last]
+    del model.v_cache_new[last]
 
 
 def release_last_kvcache_chunk(engine, layer_id=None) -> bool:

@@ -501,3 +501,32 @@ def test_launch_without_a_matching_plan_touches_nothing():
     O.store_kvcache_decode(c["k_new"], c["v_new"], kpo, vpo, c["block_table"], c["seq_ids"], c["seq_lens"], 0, 40, 0)
     ex = O.paged_attention_exact(c["q"], kpo, vpo, c["block_table"], c["seq_ids"], c["seq_lens"], 0, c["scale"], 40, 0)
     _close(o.cpu().numpy().reshape(ex.shape), ex)
+
+
+def test_reused_infer_state_with_lengths_updated_in_place_is_planned_again():
+    """A caller may keep ONE LlamaInferState object and update ``decoding_seq_lens`` in place from step to step.  The
+    kernel takes the lengths from the plan, so a plan kept from the previous step would silently attend over the old
+    lengths: a call whose layer number is not above the previous call's starts a new step and must plan afresh.
+    Step two changes the lengths drastically (a 30-token sequence becomes 900 tokens long and the other way round)."""
+    from morphserve_b200 import paged_attention
+    lens1 = np.array([30, 900, 64, 17, 333, 5], dtype=np.int32)
+    lens2 = np.array([900, 30, 65, 300, 2, 512], dtype=np.int32)
+    B, Hq, Hkv, L = len(lens1), 8, 2, 2
+    nb = int(((np.maximum(lens1, lens2) + 15) // 16).sum()) + 4
+    c = cases.build_decode_case(seed=99, B=B, Hq=Hq, Hkv=Hkv, D=128, bs=16, L=L, layer=0, num_blocks_org=nb,
+                                dtype=np.float16, lens=np.maximum(lens1, lens2))
+    d = H.device_case(c)
+    mc, ec = H.cfgs(d, d["block_table_t"].shape[1])
+    lens_t = H.to_dev(lens1.copy())
+    st = H.decode_state(d, d["seq_ids_t"], lens_t)
+    st.max_decoding_len = int(max(lens1.max(), lens2.max()))
+    kp, vp = [p for p in c["k_pools"]], [p for p in c["v_pools"]]
+    for lens in (lens1, lens2):
+        lens_t.copy_(H.to_dev(lens))                       # in place: same tensor, same infer state object
+        for layer in range(L):
+            o = torch.zeros((B, Hq * 128), dtype=torch.float16, device="cuda")
+            paged_attention(d["q_t"], d["k_pools_t"][0], d["v_pools_t"][0], [], [], d["block_table_t"], mc, ec, st, layer, o)
+            torch.cuda.synchronize()
+            ex = O.paged_attention_exact(c["q"], kp, vp, c["block_table"], c["seq_ids"], lens, layer, c["scale"],
+                                         c["num_blocks_org"], 0)
+            _close(o.cpu().numpy().reshape(ex.shape), ex)
