@@ -424,6 +424,27 @@ int mkv_remap_block_table(int device, void *stream, int32_t *block_table, int64_
                           int64_t num_rows, const int32_t *num_allocated, const int64_t *src_ids,
                           const int64_t *dst_ids, int64_t n);
 
+/*
+ * Compaction without a host round trip (three launches: plan, copy, remap).
+ * mkv_compact_plan: every live block with id >= target, ascending, is paired with the first free ids below target,
+ * ascending (src_ids / dst_ids, device arrays of `capacity` entries; capacity >= num_blocks - target always
+ * suffices).  The bitmap is updated - destinations used, sources free - only when every source found a destination.
+ * result (device, 4 x int64): [0] pairs to move, 0 when refused; [1] 1 when refused (too few free ids below target or
+ * more sources than capacity), nothing changed; [2] live ids found at or above target; [3] free ids found below it
+ * (the search stops once it has enough).  The reference has no counterpart: its release rule needs a tail that is
+ * already empty (server/memory_utils.py:529-544).
+ * mkv_copy_blocks_counted / mkv_remap_block_table_counted: as the calls above, with the pair count read on the
+ * device from *n_dev (result[0] of the plan), at most `capacity`; the launch is sized for `capacity`.
+ */
+int mkv_compact_plan(int device, void *stream, uint8_t *bitmap, int64_t num_blocks, int64_t target,
+                     int64_t *src_ids /* device */, int64_t *dst_ids /* device */, int64_t capacity,
+                     int64_t *result /* device [4] */);
+int mkv_copy_blocks_counted(int device, void *stream, const mkv_pool *pool, const int64_t *src_ids /* device */,
+                            const int64_t *dst_ids /* device */, int64_t capacity, const int64_t *n_dev /* device */);
+int mkv_remap_block_table_counted(int device, void *stream, int32_t *block_table, int64_t table_stride,
+                                  int64_t num_rows, const int32_t *num_allocated, const int64_t *src_ids,
+                                  const int64_t *dst_ids, int64_t capacity, const int64_t *n_dev /* device */);
+
 /* ---- swap -------------------------------------------------------------- */
 /*
  * Block copies between the device pool and the host swap space

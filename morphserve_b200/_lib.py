@@ -78,6 +78,9 @@ SIGNATURES = {
                               C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(_i64)]),
     "mkv_copy_blocks": (_i, [_i, _vp, _pool, _vp, _vp, _i64]),
     "mkv_remap_block_table": (_i, [_i, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _i64]),
+    "mkv_compact_plan": (_i, [_i, _vp, _vp, _i64, _i64, _vp, _vp, _i64, _vp]),
+    "mkv_copy_blocks_counted": (_i, [_i, _vp, _pool, _vp, _vp, _i64, _vp]),
+    "mkv_remap_block_table_counted": (_i, [_i, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _i64, _vp]),
     "mkv_swap_blocks": (_i, [_i, _vp, _pool, _vp, _vp, _i64, C.POINTER(_i64), C.POINTER(_i64), _i64, _i,
                              C.POINTER(_i64)]),
     "mkv_swap_blocks_pinned": (_i, [_i, _vp, _pool, _vp, _vp, _i64, _vp, _vp, _i64, _i]),

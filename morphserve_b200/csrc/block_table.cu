@@ -121,6 +121,62 @@ __global__ void __launch_bounds__(kThreads) bitmap_select_kernel(uint8_t *__rest
     }
 }
 
+// Compaction plan as ONE launch with no host round trip.  Rule (the reference has no compaction: its release needs a
+// tail that is already empty, server/memory_utils.py:529-544): every live block with id >= target, ascending, moves to
+// the first free ids below target, ascending.  src_ids/dst_ids receive the pairs; the bitmap is updated (destinations
+// used, sources free) only when every source has a destination.  result[0] = pairs to move (0 when refused),
+// result[1] = 1 when refused (too few free ids below target, or more sources than `capacity`), result[2] = live ids
+// found at or above target, result[3] = free ids found below target (the search stops once it has enough).
+__global__ void __launch_bounds__(kThreads) compact_plan_kernel(uint8_t *__restrict__ bitmap, int64_t total,
+                                                              int64_t target, int64_t *__restrict__ src_ids,
+                                                              int64_t *__restrict__ dst_ids, int64_t capacity,
+                                                              int64_t *__restrict__ result) {
+    __shared__ int warp_sums[33];
+    int64_t found[2] = {0, 0};
+#pragma unroll 1
+    for (int pass = 0; pass < 2; ++pass) {
+        const int64_t lo = pass == 0 ? target : 0, hi = pass == 0 ? total : target;
+        const uint8_t want = pass == 0 ? 0 : 1;  // live above the target, free below it
+        int64_t *out = pass == 0 ? src_ids : dst_ids;
+        const int64_t max_out = pass == 0 ? capacity : min(found[0], capacity);
+        int64_t carry = 0;
+        for (int64_t base = lo; base < hi; base += (int64_t)kThreads * kPerThread) {
+            if (pass == 1 && carry >= found[0]) break;  // uniform across the block
+            const int64_t i0 = base + (int64_t)threadIdx.x * kPerThread;
+            unsigned mask = 0;
+#pragma unroll
+            for (int j = 0; j < kPerThread; ++j) {
+                const int64_t i = i0 + j;
+                if (i < hi && (bitmap[i] != 0) == (want != 0)) mask |= 1u << j;
+            }
+            int sum;
+            const int off = block_exclusive_scan(__popc(mask), sum, warp_sums);
+            int64_t pos = carry + off;
+            while (mask) {
+                const int j = __ffs(mask) - 1;
+                mask &= mask - 1;
+                if (pos < max_out) out[pos] = i0 + j;
+                ++pos;
+            }
+            carry += sum;
+        }
+        found[pass] = carry;
+    }
+    __syncthreads();  // the pairs written above are read by other threads of this block below
+    const bool ok = found[0] <= capacity && found[1] >= found[0];
+    if (ok)
+        for (int64_t i = threadIdx.x; i < found[0]; i += kThreads) {
+            bitmap[dst_ids[i]] = 0;
+            bitmap[src_ids[i]] = 1;
+        }
+    if (threadIdx.x == 0) {
+        result[0] = ok ? found[0] : 0;
+        result[1] = ok ? 0 : 1;
+        result[2] = found[0];
+        result[3] = found[1];
+    }
+}
+
 // allocate_blocks_for_seqs (worker/block_manager.py:87-112) as ONE launch with no host round trip:
 // need per sequence -> first-fit ascending selection of sum(need) free ids (the order of
 // torch.nonzero(is_block_free)[:n], :75) -> rows and counts updated in batch order.  Nothing is changed
@@ -351,6 +407,19 @@ int mkv_bitmap_select(int device, void *stream, uint8_t *bitmap, int64_t lo, int
     if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
     bitmap_select_kernel<<<1, kThreads, 0, (cudaStream_t)stream>>>(bitmap, lo, hi, want, max_out, flip, out_ids,
                                                                   out_count, out_total);
+    MKV_LAUNCH_CHECK();
+    return MKV_OK;
+}
+
+int mkv_compact_plan(int device, void *stream, uint8_t *bitmap, int64_t num_blocks, int64_t target,
+                     int64_t *src_ids, int64_t *dst_ids, int64_t capacity, int64_t *result) {
+    if (num_blocks < 0 || target < 0 || target > num_blocks || capacity < 0) return MKV_ERR_SHAPE;
+    if (!result || (num_blocks > 0 && !bitmap)) return MKV_ERR_NULL;
+    if (capacity > 0 && (!src_ids || !dst_ids)) return MKV_ERR_NULL;
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return set_cuda_error(guard.err);
+    compact_plan_kernel<<<1, kThreads, 0, (cudaStream_t)stream>>>(bitmap, num_blocks, target, src_ids, dst_ids,
+                                                                 capacity, result);
     MKV_LAUNCH_CHECK();
     return MKV_OK;
 }

@@ -18,7 +18,9 @@ __global__ void __launch_bounds__(kCopyThreads) copy_blocks_kernel(const __grid_
                                                                   const int64_t *__restrict__ src_ids,
                                                                   const int64_t *__restrict__ dst_ids, int64_t n,
                                                                   int slices_per_block, char *host_k, char *host_v,
-                                                                  int64_t host_blocks) {
+                                                                  int64_t host_blocks,
+                                                                  const int64_t *__restrict__ n_dev) {
+    if (n_dev) n = min(n, *n_dev);  // pair count decided on the device (compaction plan); n is then the capacity
     const int64_t items = n * 2 * slices_per_block;
     const int64_t vec_per_block = pool.block_bytes / 16;
     for (int64_t item = blockIdx.x; item < items; item += gridDim.x) {
@@ -69,7 +71,9 @@ __global__ void __launch_bounds__(kCopyThreads) copy_blocks_kernel(const __grid_
 __global__ void remap_block_table_kernel(int32_t *__restrict__ block_table, int64_t table_stride, int64_t num_rows,
                                          const int32_t *__restrict__ num_allocated,
                                          const int64_t *__restrict__ src_ids, const int64_t *__restrict__ dst_ids,
-                                         int64_t n) {
+                                         int64_t n, const int64_t *__restrict__ n_dev) {
+    if (n_dev) n = min(n, *n_dev);
+    if (n <= 0) return;
     const int lane = threadIdx.x & 31;
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
@@ -97,8 +101,8 @@ using namespace mkv;
 
 extern "C" {
 
-int mkv_copy_blocks(int device, void *stream, const mkv_pool *pool, const int64_t *src_ids,
-                    const int64_t *dst_ids, int64_t n) {
+static int copy_blocks_launch(int device, void *stream, const mkv_pool *pool, const int64_t *src_ids,
+                              const int64_t *dst_ids, int64_t n, const int64_t *n_dev) {
     PoolView pv;
     int st = validate_pool(pool, &pv);
     if (st) return st;
@@ -117,9 +121,20 @@ int mkv_copy_blocks(int device, void *stream, const mkv_pool *pool, const int64_
     int64_t grid = (int64_t)sms * 8;  // 8 x 256 threads resident per SM
     if (grid > items) grid = items;
     copy_blocks_kernel<0><<<(unsigned)grid, kCopyThreads, 0, (cudaStream_t)stream>>>(pv, src_ids, dst_ids, n, slices,
-                                                                                     nullptr, nullptr, 0);
+                                                                                     nullptr, nullptr, 0, n_dev);
     MKV_LAUNCH_CHECK();
     return MKV_OK;
+}
+
+int mkv_copy_blocks(int device, void *stream, const mkv_pool *pool, const int64_t *src_ids,
+                    const int64_t *dst_ids, int64_t n) {
+    return copy_blocks_launch(device, stream, pool, src_ids, dst_ids, n, nullptr);
+}
+
+int mkv_copy_blocks_counted(int device, void *stream, const mkv_pool *pool, const int64_t *src_ids,
+                            const int64_t *dst_ids, int64_t capacity, const int64_t *n_dev) {
+    if (!n_dev) return MKV_ERR_NULL;
+    return copy_blocks_launch(device, stream, pool, src_ids, dst_ids, capacity, n_dev);
 }
 
 int mkv_swap_blocks_pinned(int device, void *stream, const mkv_pool *pool, void *k_swap, void *v_swap,
@@ -150,17 +165,17 @@ int mkv_swap_blocks_pinned(int device, void *stream, const mkv_pool *pool, void 
     if (grid > items) grid = items;
     if (is_swap_in)
         copy_blocks_kernel<1><<<(unsigned)grid, kCopyThreads, 0, (cudaStream_t)stream>>>(
-            pv, src_ids, dst_ids, n, slices, (char *)k_swap, (char *)v_swap, num_swap_blocks);
+            pv, src_ids, dst_ids, n, slices, (char *)k_swap, (char *)v_swap, num_swap_blocks, nullptr);
     else
         copy_blocks_kernel<2><<<(unsigned)grid, kCopyThreads, 0, (cudaStream_t)stream>>>(
-            pv, src_ids, dst_ids, n, slices, (char *)k_swap, (char *)v_swap, num_swap_blocks);
+            pv, src_ids, dst_ids, n, slices, (char *)k_swap, (char *)v_swap, num_swap_blocks, nullptr);
     MKV_LAUNCH_CHECK();
     return MKV_OK;
 }
 
-int mkv_remap_block_table(int device, void *stream, int32_t *block_table, int64_t table_stride,
-                          int64_t num_rows, const int32_t *num_allocated, const int64_t *src_ids,
-                          const int64_t *dst_ids, int64_t n) {
+static int remap_launch(int device, void *stream, int32_t *block_table, int64_t table_stride, int64_t num_rows,
+                        const int32_t *num_allocated, const int64_t *src_ids, const int64_t *dst_ids, int64_t n,
+                        const int64_t *n_dev) {
     if (n < 0 || num_rows < 0 || table_stride < 1) return MKV_ERR_SHAPE;
     if (n == 0 || num_rows == 0) return MKV_OK;
     if (!block_table || !num_allocated || !src_ids || !dst_ids) return MKV_ERR_NULL;
@@ -170,9 +185,24 @@ int mkv_remap_block_table(int device, void *stream, int32_t *block_table, int64_
     int64_t grid = ceil_div64(num_rows, threads / 32);
     if (grid > 148 * 8) grid = 148 * 8;
     remap_block_table_kernel<<<(unsigned)grid, threads, 0, (cudaStream_t)stream>>>(
-        block_table, table_stride, num_rows, num_allocated, src_ids, dst_ids, n);
+        block_table, table_stride, num_rows, num_allocated, src_ids, dst_ids, n, n_dev);
     MKV_LAUNCH_CHECK();
     return MKV_OK;
+}
+
+int mkv_remap_block_table(int device, void *stream, int32_t *block_table, int64_t table_stride,
+                          int64_t num_rows, const int32_t *num_allocated, const int64_t *src_ids,
+                          const int64_t *dst_ids, int64_t n) {
+    return remap_launch(device, stream, block_table, table_stride, num_rows, num_allocated, src_ids, dst_ids, n,
+                        nullptr);
+}
+
+int mkv_remap_block_table_counted(int device, void *stream, int32_t *block_table, int64_t table_stride,
+                                  int64_t num_rows, const int32_t *num_allocated, const int64_t *src_ids,
+                                  const int64_t *dst_ids, int64_t capacity, const int64_t *n_dev) {
+    if (!n_dev) return MKV_ERR_NULL;
+    return remap_launch(device, stream, block_table, table_stride, num_rows, num_allocated, src_ids, dst_ids,
+                        capacity, n_dev);
 }
 
 }  // extern "C"

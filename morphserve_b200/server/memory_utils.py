@@ -94,11 +94,12 @@ def release_last_kvcache_chunk(engine, layer_id=None) -> bool:
     return True
 
 
-def compact_kvcache(engine, target_num_blocks: int) -> int:
-    """Move every live block with id >= ``target_num_blocks`` below it and remap the
-    block table (rule in the module docstring).  Returns the number of blocks
-    moved, or -1 - with nothing changed - when the low region has too few free
-    blocks.  One host synchronisation (the move count sizes the launches)."""
+def compact_kvcache_nosync(engine, target_num_blocks: int) -> torch.Tensor:
+    """Compaction with no host round trip: plan (one block scans the bitmap, pairs sources with destinations and
+    updates the bitmap), block copy and table remap are enqueued back to back, the pair count travelling through
+    device memory.  Returns the plan's device record, int64[4]: pairs moved (0 when refused), 1 when refused because
+    the low region has too few free blocks (nothing changed), live blocks found at or above the target, free blocks
+    found below it.  Capturable in a CUDA graph; `compact_kvcache` is this plus one read of the record."""
     model = engine.model
     bm = model.gpu_block_manager
     free = bm.is_block_free
@@ -108,33 +109,31 @@ def compact_kvcache(engine, target_num_blocks: int) -> int:
         raise RuntimeError(f"compaction target {T} outside the pool of {total} blocks")
     dev, stream = device_and_stream(free)
     device = free.device
-    n_hi = total - T
-    src = torch.empty((max(n_hi, 1),), dtype=torch.int64, device=device)
-    counts = torch.empty((4,), dtype=torch.int64, device=device)
-    # live ids >= T, ascending
-    check(lib.mkv_bitmap_select(dev, stream, free.data_ptr(), T, total, 0, n_hi, 0, src.data_ptr(),
-                                counts[0:].data_ptr(), counts[1:].data_ptr()), "mkv_bitmap_select")
-    # how many free ids < T exist (count only)
-    check(lib.mkv_bitmap_select(dev, stream, free.data_ptr(), 0, T, 1, 0, 0, None,
-                                counts[2:].data_ptr(), counts[3:].data_ptr()), "mkv_bitmap_select")
-    n_src, _, _, n_free_lo = counts.tolist()
-    if n_src == 0:
-        return 0
-    if n_free_lo < n_src:
-        return -1
-    dst = torch.empty((n_src,), dtype=torch.int64, device=device)
-    # first n_src free ids < T, ascending; mark them used
-    check(lib.mkv_bitmap_select(dev, stream, free.data_ptr(), 0, T, 1, n_src, 1, dst.data_ptr(), None, None),
-          "mkv_bitmap_select")
-    pool = make_pool(model.k_cache, model.v_cache, model.k_cache_new, model.v_cache_new,
-                     bm.num_blocks_org, model.kv_cache_new_block_size)
-    check(lib.mkv_copy_blocks(dev, stream, pool, src.data_ptr(), dst.data_ptr(), n_src), "mkv_copy_blocks")
-    check(lib.mkv_remap_block_table(dev, stream, bm.block_table.data_ptr(), bm.block_table.stride(0),
-                                    bm.block_table.shape[0], bm.num_seq_allocated_blocks.data_ptr(),
-                                    src.data_ptr(), dst.data_ptr(), n_src), "mkv_remap_block_table")
-    check(lib.mkv_bitmap_scatter(dev, stream, free.data_ptr(), total, src.data_ptr(), n_src, 1),
-          "mkv_bitmap_scatter")
-    return n_src
+    capacity = min(total - T, T)               # more sources than ids below the target can never be served
+    pairs = torch.empty((2, max(capacity, 1)), dtype=torch.int64, device=device)
+    result = torch.empty((4,), dtype=torch.int64, device=device)
+    src, dst = pairs[0], pairs[1]
+    check(lib.mkv_compact_plan(dev, stream, free.data_ptr(), total, T, src.data_ptr(), dst.data_ptr(), capacity,
+                               result.data_ptr()), "mkv_compact_plan")
+    if capacity > 0:
+        pool = make_pool(model.k_cache, model.v_cache, model.k_cache_new, model.v_cache_new,
+                         bm.num_blocks_org, model.kv_cache_new_block_size)
+        check(lib.mkv_copy_blocks_counted(dev, stream, pool, src.data_ptr(), dst.data_ptr(), capacity,
+                                          result.data_ptr()), "mkv_copy_blocks_counted")
+        check(lib.mkv_remap_block_table_counted(dev, stream, bm.block_table.data_ptr(), bm.block_table.stride(0),
+                                                bm.block_table.shape[0], bm.num_seq_allocated_blocks.data_ptr(),
+                                                src.data_ptr(), dst.data_ptr(), capacity, result.data_ptr()),
+              "mkv_remap_block_table_counted")
+    return result
+
+
+def compact_kvcache(engine, target_num_blocks: int) -> int:
+    """Move every live block with id >= ``target_num_blocks`` below it and remap the
+    block table (rule in the module docstring).  Returns the number of blocks
+    moved, or -1 - with nothing changed - when the low region has too few free
+    blocks.  The host reads the outcome once, after all of the work is enqueued."""
+    moved, refused, _, _ = compact_kvcache_nosync(engine, target_num_blocks).tolist()
+    return -1 if refused else moved
 
 
 def shrink_kvcache(engine, num_chunks_to_release: int) -> int:

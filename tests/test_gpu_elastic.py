@@ -203,6 +203,43 @@ def test_release_refused_while_last_chunk_is_live():
     tw.check()
 
 
+def test_compaction_without_a_host_round_trip_replayed_from_a_cuda_graph():
+    """compact_kvcache_nosync keeps the pair count on the device, so the whole compaction (plan, block copy, table
+    remap) can be captured once and replayed: first replay moves the two live blocks of the chunk, the second finds
+    nothing to move, and a replay on a full low region is refused with nothing changed."""
+    import torch
+    from morphserve_b200.server import memory_utils as MU
+    tw = Twin(2, 2, 128, 16, 8, max_seqs=16, mbps=8, seed=5)
+    tw.expand(4)
+    for s in range(5):
+        tw.admit(s, 32)          # ids 0..9: the low region (8 blocks) is full, two blocks live in the chunk
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        rec = MU.compact_kvcache_nosync(tw.engine, 8)          # warm-up outside the capture: refused
+        side.synchronize()
+        assert rec.tolist() == [0, 1, 2, 0]
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            rec = MU.compact_kvcache_nosync(tw.engine, 8)
+    torch.cuda.current_stream().wait_stream(side)
+    g.replay()
+    torch.cuda.synchronize()
+    assert rec.tolist() == [0, 1, 2, 0]
+    tw.check()                                                   # refused: bitmap, table and pools untouched
+    tw.free([0])                                                 # frees ids 0 and 1
+    g.replay()
+    torch.cuda.synchronize()
+    assert rec.tolist() == [2, 0, 2, 2]
+    assert O.compact(tw.obm, tw.ok, tw.ov, 8, 4) == 2
+    tw.check()
+    g.replay()
+    torch.cuda.synchronize()
+    assert rec.tolist() == [0, 0, 0, 0]                          # nothing above the target any more
+    tw.check()
+    assert MU.release_last_kvcache_chunk(tw.engine)
+
+
 @pytest.mark.parametrize("pinned", [False, True])
 def test_swap_roundtrip_and_chunk_addressing(pinned):
     from morphserve_b200 import swiftllm_c
