@@ -96,7 +96,6 @@ struct Tuning {
     std::atomic<int> static_mode{1};   // 0 never deal statically, 1 when a sequence must be cut, 2 whenever possible
     std::atomic<int> unit_cost{3};     // static deal: tiles that starting a unit is worth
     std::atomic<int> static_ratio{1};  // mode 1: static when the longest sequence exceeds this many chunks
-    std::atomic<int> pdl{2};           // programmatic dependent launch: 0 off, 1 wait first, 2 metadata before the wait
     std::atomic<double> item_factor{4.0};    // work units per worker warp that bound the dynamic item list
     std::atomic<double> split_balance{1.5};  // see plan_balance()
     std::once_flag once;
@@ -125,7 +124,6 @@ static Tuning &tuning() {
         t.loader = kDefaultLoader;
         if (const char *e = getenv("MKV_ATTN_LOADER")) t.loader = strcmp(e, "cpasync") == 0 ? 0 : 1;
         if (const char *e = getenv("MKV_ATTN_STATIC")) t.static_mode = atoi(e);
-        if (const char *e = getenv("MKV_ATTN_PDL")) t.pdl = std::max(0, std::min(2, atoi(e)));
         if (const char *e = getenv("MKV_ATTN_UNIT_COST")) t.unit_cost = std::max(0, std::min(64, atoi(e)));
         if (const char *e = getenv("MKV_ATTN_STATIC_RATIO")) t.static_ratio = std::max(1, std::min(1 << 20, atoi(e)));
     });
@@ -591,10 +589,6 @@ struct AttnParams {
     int *garrive;       // static deal: arrival counters of the piece groups of a two-level merge
     float *lse;
     float *part_o;
-    // Programmatic dependent launch: 1 = wait for the kernel in front before anything is read; 2 = the plan and the
-    // block table are older than the kernel in front, so the plan header, this worker's records and its first block
-    // ids are requested BEFORE the wait (they then travel while the kernel in front drains).
-    int pdl;
 };
 
 // Tensor maps of the pool segments for the TMA loader: segment s of K (and of V) as a 2-D fp16 tensor
@@ -730,10 +724,6 @@ struct WorkMeta {
     int ids;               // lane l: block id of tile l of the item
 };
 
-// Grid dependency control (programmatic dependent launch).  Both are no-ops in a launch without the attribute.
-__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
-__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
-
 // HI: the GQA group has more than 8 query heads, so rows 8-15 of the tensor-core tile carry data.
 // For G <= 8 (every Llama shape) their softmax, rescale and write-out work is compiled out.
 template <int WARPS, int STAGES, bool HI, bool TMA>
@@ -748,7 +738,6 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
     const uint32_t bars = smem_u32(smem) + WARPS * STAGES * kStageBytes + warp * (STAGES * 8);
 
     WsHeader *hdr = p.hdr;
-    if (p.pdl != 2) griddep_wait();
     // Everything the plan left for this launch, requested in ONE round trip before any of it is looked at: the
     // header's first and third 16 bytes (magic, batch, n_items, chunk | cap_items, mode, n_workers, n_units) and,
     // for the static deal, this worker's range of unit records.
@@ -929,9 +918,6 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
     nxt.valid = first_valid;
     nxt.h = wid - first_item * Hkv;  // dynamic deal: unit `wid` = (item wid / Hkv, head wid % Hkv); static: from the record
     while (fstage < 3) fetch_step(nxt);
-    if (p.pdl == 2) griddep_wait();
-    // from here on the launch behind this one may take the SMs that fall free (it waits for this grid's end itself)
-    griddep_launch_dependents();
     while (nxt.valid) {
         const WorkMeta cur = nxt;
         nxt.valid = false;  // until the next claim lands, `nxt` is this unit: nothing may be prefetched from it
@@ -1487,17 +1473,8 @@ static cudaError_t launch_decode_one(const AttnParams &p, const TmaMaps &tm, int
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
     }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)sm_count);
-    cfg.blockDim = dim3(WARPS * 32);
-    cfg.dynamicSmemBytes = (size_t)smem;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = p.pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, attn_decode_f16_kernel<WARPS, STAGES, HI, TMA>, p, tm);
+    attn_decode_f16_kernel<WARPS, STAGES, HI, TMA><<<sm_count, WARPS * 32, smem, s>>>(p, tm);
+    return cudaGetLastError();
 }
 
 template <int WARPS, int STAGES>
@@ -1572,8 +1549,6 @@ static bool fast_path_ok(const PoolView &pv, int num_q_heads, const void *q, con
     return true;
 }
 
-static std::atomic<void *> g_last_planned{nullptr};  // EXPERIMENT: workspace of the last plan launch
-
 // One plan launch for `ws` (laid out by L).  `workers` = worker warps of the decode launch that will follow.
 static void launch_plan(char *ws, const WsLayout &L, const int32_t *seq_lens, const int32_t *seq_ids, int batch,
                         int num_q_heads, int num_kv_heads, int block_size, int sm_count, int workers, cudaStream_t s) {
@@ -1603,7 +1578,6 @@ static void launch_plan(char *ws, const WsLayout &L, const int32_t *seq_lens, co
     a.static_ratio = tuning().static_ratio.load(std::memory_order_relaxed);
     a.balance = plan_balance(sm_count, num_kv_heads);
     attn_plan_kernel<<<1, 1024, 0, s>>>(a);
-    g_last_planned.store(ws, std::memory_order_relaxed);
 }
 
 static cudaError_t builtin_scratch_address(int device, void **out);  // defined with the array, at the end of the file
@@ -1763,11 +1737,6 @@ static int attention_decode_impl(int device, void *stream, const void *q, void *
     p.cur_layer = cur_layer;
     p.scale_log2 = scale_log2;
     fill_workspace_params(p, ws, L);
-    {
-        const int mode = tuning().pdl.load(std::memory_order_relaxed);
-        const bool fresh = g_last_planned.exchange(nullptr, std::memory_order_relaxed) == (void *)ws;
-        p.pdl = (mode == 2 && fresh) ? 1 : mode;
-    }
 
     TmaMaps tm;
     const bool use_tma = make_tma_maps(pv, &tm);
@@ -2015,7 +1984,6 @@ int mkv_paged_attention_decode_noalloc(int device, void *stream, const void *q, 
     p.group = num_q_heads / pv.num_kv_heads;
     p.cur_layer = cur_layer;
     p.scale_log2 = scale_log2;
-    p.pdl = tuning().pdl.load(std::memory_order_relaxed) ? 1 : 0;  // the plan was launched just above: wait first
     fill_workspace_params(p, ws, L);
     TmaMaps tm;
     const bool use_tma = make_tma_maps(pv, &tm);
