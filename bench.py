@@ -57,6 +57,8 @@ WORKLOADS = {
     "llama3-8b-gqa-decode-2layer-uniform": dict(cfg=3, B=256, Hq=32, Hkv=8, L=2, min_len=768, max_len=768, free_frac=0.10),
     # prefill scatter of store_kvcache: 32 prompts of up to 2048 tokens into a fragmented pool, 4 layers
     "kv-prefill": dict(cfg=3, prefill=True, L=4, Hq=32, Hkv=8, n_seqs=32, max_len=2048),
+    # four times the prompt tokens: shows how much of the figure above is the launch's start and end
+    "kv-prefill-large": dict(cfg=3, prefill=True, L=4, Hq=32, Hkv=8, n_seqs=128, max_len=2048),
     # block swap between the pool and the host swap space (Llama-3-8B block = 2 x 1 MiB): 1024 blocks per direction
     "kv-swap": dict(cfg=3, swap=True, L=32, Hq=32, Hkv=8, nb=4096, n_swap=1024),
     # the same with 4 layers (blocks of 2 x 128 KiB, pool 1 GB) for profiler captures

@@ -22,7 +22,10 @@ bool rope_fused_rounding() {
     return v != 0;
 }
 
-// fp16 rows: one thread per 8-element piece of the low half of one head (16-byte loads).
+// fp16 rows: one thread per 8-element piece of the low half of one head (16-byte loads), kRopeUnroll pieces per
+// loop pass with all of their loads issued before the first store (4 x 16 B of rows in flight per thread: with two,
+// a full SM held 64 KiB in flight, which is about what 1/148 of the HBM bandwidth needs and leaves no slack).
+constexpr int kRopeUnroll = 2;
 __global__ void rope_f16_kernel(__half *__restrict__ q, __half *__restrict__ k, const __half *__restrict__ cos_t,
                                 const __half *__restrict__ sin_t, int64_t num_tokens, int num_q_heads,
                                 int num_kv_heads, int head_dim, bool fused) {
@@ -30,21 +33,36 @@ __global__ void rope_f16_kernel(__half *__restrict__ q, __half *__restrict__ k, 
     const int pieces = half_dim >> 3;
     const int heads = num_q_heads + num_kv_heads;
     const int64_t total = num_tokens * heads * pieces;
-    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
-         idx += (int64_t)gridDim.x * blockDim.x) {
-        const int piece = (int)(idx % pieces);
-        const int64_t r = idx / pieces;
-        const int head = (int)(r % heads);
-        const int64_t tok = r / heads;
-        __half *row = head < num_q_heads ? q + (tok * num_q_heads + head) * head_dim
-                                         : k + (tok * num_kv_heads + (head - num_q_heads)) * head_dim;
-        uint4 x0 = *reinterpret_cast<const uint4 *>(row + piece * 8);
-        uint4 x1 = *reinterpret_cast<const uint4 *>(row + half_dim + piece * 8);
-        const uint4 c = __ldg(reinterpret_cast<const uint4 *>(cos_t + tok * half_dim + piece * 8));
-        const uint4 s = __ldg(reinterpret_cast<const uint4 *>(sin_t + tok * half_dim + piece * 8));
-        rope_rotate8(x0, x1, c, s, fused);
-        *reinterpret_cast<uint4 *>(row + piece * 8) = x0;
-        *reinterpret_cast<uint4 *>(row + half_dim + piece * 8) = x1;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t base = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; base < total; base += stride * kRopeUnroll) {
+        __half *row[kRopeUnroll];
+        uint4 x0[kRopeUnroll], x1[kRopeUnroll], c[kRopeUnroll], s[kRopeUnroll];
+        int piece[kRopeUnroll];
+#pragma unroll
+        for (int u = 0; u < kRopeUnroll; ++u) {
+            const int64_t idx = base + u * stride;
+            if (idx >= total) {
+                row[u] = nullptr;
+                continue;
+            }
+            piece[u] = (int)(idx % pieces);
+            const int64_t r = idx / pieces;
+            const int head = (int)(r % heads);
+            const int64_t tok = r / heads;
+            row[u] = head < num_q_heads ? q + (tok * num_q_heads + head) * head_dim
+                                        : k + (tok * num_kv_heads + (head - num_q_heads)) * head_dim;
+            x0[u] = *reinterpret_cast<const uint4 *>(row[u] + piece[u] * 8);
+            x1[u] = *reinterpret_cast<const uint4 *>(row[u] + half_dim + piece[u] * 8);
+            c[u] = __ldg(reinterpret_cast<const uint4 *>(cos_t + tok * half_dim + piece[u] * 8));
+            s[u] = __ldg(reinterpret_cast<const uint4 *>(sin_t + tok * half_dim + piece[u] * 8));
+        }
+#pragma unroll
+        for (int u = 0; u < kRopeUnroll; ++u) {
+            if (row[u] == nullptr) continue;
+            rope_rotate8(x0[u], x1[u], c[u], s[u], fused);
+            *reinterpret_cast<uint4 *>(row[u] + piece[u] * 8) = x0[u];
+            *reinterpret_cast<uint4 *>(row[u] + half_dim + piece[u] * 8) = x1[u];
+        }
     }
 }
 
