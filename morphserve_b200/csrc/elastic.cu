@@ -12,9 +12,9 @@ constexpr int kCopyThreads = 256;
 // blocks per SM (24 per SM: 5.95 TB/s).
 constexpr int kVecPool = 2, kVecHost = 8;
 template <int MODE>
-constexpr int vec_per_thread() { return MODE == 0 ? kVecPool : kVecHost; }
+__host__ __device__ constexpr int vec_per_thread() { return MODE == 0 ? kVecPool : kVecHost; }
 template <int MODE>
-constexpr int slice_bytes() { return kCopyThreads * vec_per_thread<MODE>() * 16; }
+__host__ __device__ constexpr int slice_bytes() { return kCopyThreads * vec_per_thread<MODE>() * 16; }
 
 // Work item = (pair, K|V, slice).  grid-stride over items; each thread issues
 // all its loads before its stores.
