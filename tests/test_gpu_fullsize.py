@@ -137,6 +137,15 @@ def _block_checksums(pool):
     return out
 
 
+def _gather_blocks(pools, ids, nb_org, chunk):
+    """Bytes of the given blocks ([n, block bytes] uint8), wherever their segment lies."""
+    out = torch.empty((len(ids), pools[0][0].numel() * 2), dtype=torch.uint8, device=pools[0].device)
+    for i, b in enumerate(ids):
+        seg, row = O.locate_block(int(b), nb_org, max(chunk, 1))
+        out[i] = pools[seg][row].reshape(-1).view(torch.uint8)
+    return out
+
+
 def test_elastic_resize_trace_full_size():
     """Elastic trace at full size (Llama-3-8B pool shape): 8192 -> 16384 blocks, release 40 % by compaction,
     100 decode steps of batch 128."""
@@ -254,6 +263,8 @@ def test_elastic_resize_trace_full_size():
     before_k = torch.cat([_block_checksums(p) for p in pk])
     before_v = torch.cat([_block_checksums(p) for p in pv])
     src, dst = O.compaction_plan(obm.is_block_free, target)
+    src_bytes_k = _gather_blocks(pk, src, nb_org, chunk)            # 2 x 3.6 GiB: the blocks about to move, byte for byte
+    src_bytes_v = _gather_blocks(pv, src, nb_org, chunk)
     moved = MU.compact_kvcache(engine, target)
     assert moved == len(src) > 0
     remap = dict(zip(src.tolist(), dst.tolist()))
@@ -274,6 +285,10 @@ def test_elastic_resize_trace_full_size():
         keep = torch.ones_like(before, dtype=torch.bool)
         keep[dst_t] = False
         assert torch.equal(after[keep], before[keep]), "a block that was not a destination changed"
+    assert torch.equal(_gather_blocks(pk, dst, nb_org, chunk), src_bytes_k), "moved K blocks differ from their sources"
+    assert torch.equal(_gather_blocks(pv, dst, nb_org, chunk), src_bytes_v), "moved V blocks differ from their sources"
+    assert torch.equal(_gather_blocks(pk, src, nb_org, chunk), src_bytes_k), "a source block was written"
+    del src_bytes_k, src_bytes_v
     for _ in range(release):                                     # 16384 -> 10240 by the reference's rule
         assert MU.release_last_kvcache_chunk(engine)
         O.release_last_chunk(obm, chunk)
