@@ -164,6 +164,35 @@ class KVCacheModelState:
                 self.k_cache_new, self.v_cache_new)
 
     @torch.inference_mode()
+    def swap_seqs_nosync(self, seq_ids: torch.Tensor, is_swap_in: bool) -> torch.Tensor:
+        """The same move with no host round trip (pinned swap space only): the source manager's ids stay on the
+        GPU (``gather_allocated_blocks_and_free_nosync``), the destination manager allocates with its one-launch
+        kernel, and one copy kernel moves the blocks, skipping the unused tail of both id lists.  ``seq_ids`` is an
+        int32 CUDA tensor.  Returns the device-side block count (int64 [1]); it is also added to
+        ``block_swap_device``.  If the destination has too few free blocks nothing is copied - the id list the copy
+        reads is cleared beforehand and the allocation then leaves it untouched - and the next look at the
+        destination's ``num_free_blocks`` raises, as for every sync-free allocation."""
+        if not (self.k_swap.is_pinned() and self.v_swap.is_pinned()):
+            raise RuntimeError("swap_seqs_nosync needs a pinned swap space (pin_swap=True)")
+        assert seq_ids.dtype == torch.int32 and seq_ids.is_cuda and seq_ids.is_contiguous()
+        src_bm = self.cpu_block_manager if is_swap_in else self.gpu_block_manager
+        dst_bm = self.gpu_block_manager if is_swap_in else self.cpu_block_manager
+        seq_lengths = (src_bm.get_num_allocated_blocks(seq_ids.long()) * self.engine_config.block_size).to(torch.int32)
+        src_ids, count = src_bm.gather_allocated_blocks_and_free_nosync(seq_ids)
+        n = min(src_ids.shape[0], dst_bm.is_block_free.shape[0])
+        dst_bm.prepare_nosync(seq_ids.shape[0])
+        dst_bm._alloc_ids[:n].fill_(-1)
+        dst_bm.allocate_blocks_for_seqs_nosync(seq_ids, seq_lengths)
+        dst_ids = dst_bm._alloc_ids[:n]
+        if getattr(self, "block_swap_device", None) is None:
+            self.block_swap_device = torch.zeros((1,), dtype=torch.int64, device=seq_ids.device)
+        self.block_swap_device += count
+        swiftllm_c.swap_blocks_chunk_list(
+            src_ids[:n], dst_ids, is_swap_in, self.gpu_block_manager.num_blocks_org, self.kv_cache_new_block_size,
+            self.k_cache, self.v_cache, self.k_swap, self.v_swap, self.k_cache_new, self.v_cache_new)
+        return count
+
+    @torch.inference_mode()
     def swap_in_seqs(self, seq_ids_list):
         """Move the blocks of the given sequences from the host swap space to the GPU pool."""
         self._swap(seq_ids_list, True)

@@ -96,6 +96,13 @@ def test_host_side_argument_validation(L):
     assert lib.mkv_copy_blocks(0, None, C.byref(p), None, None, 0) == 0
     assert lib.mkv_remap_block_table(0, None, None, 4, 4, None, None, None, 2) == -1
     assert lib.mkv_block_need(0, None, 1, 8, 1, 1, 4, 0, 1, 1) == -2
+    # compaction without a host round trip: target outside the bitmap, no result record, no pair arrays, no count
+    assert lib.mkv_compact_plan(0, None, 1, 8, 9, 1, 1, 4, 1) == -2
+    assert lib.mkv_compact_plan(0, None, 1, 8, 4, 1, 1, 4, None) == -1
+    assert lib.mkv_compact_plan(0, None, 1, 8, 4, None, None, 4, 1) == -1
+    assert lib.mkv_copy_blocks_counted(0, None, C.byref(p), 1, 1, 4, None) == -1
+    assert lib.mkv_copy_blocks_counted(0, None, C.byref(p), None, None, 0, 1) == 0
+    assert lib.mkv_remap_block_table_counted(0, None, 1, 4, 4, 1, 1, 1, 2, None) == -1
 
 
 def test_swap_validates_ids_on_the_host(L):

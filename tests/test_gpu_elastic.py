@@ -383,11 +383,13 @@ def test_layer_slab_replace_and_restore_round_trip():
         assert t.dtype == torch.float16 and t.cpu().numpy().tobytes() == a.tobytes(), name
 
 
+@pytest.mark.parametrize("sync_free", [False, True])
 @pytest.mark.parametrize("with_chunks", [False, True])
-def test_model_level_swap_out_and_in_against_oracle(with_chunks):
+def test_model_level_swap_out_and_in_against_oracle(with_chunks, sync_free):
     """KVCacheModelState (the KV half of the reference's LlamaModel: worker/model.py:176-227, :468-550): sequences
     are swapped out, others admitted, the first swapped back in - block managers, pools and swap space in lockstep
-    with the oracle's managers and its swap rule."""
+    with the oracle's managers and its swap rule.  ``sync_free``: the same moves through ``swap_seqs_nosync`` (ids
+    and counts stay on the GPU)."""
     from types import SimpleNamespace
     from morphserve_b200 import KVCacheModelState
     rs = np.random.RandomState(5 + with_chunks)
@@ -445,28 +447,64 @@ def test_model_level_swap_out_and_in_against_oracle(with_chunks):
             assert t.cpu().numpy().tobytes() == a.tobytes()
         assert m.k_swap.numpy().tobytes() == ks_or.tobytes() and m.v_swap.numpy().tobytes() == vs_or.tobytes()
 
+    def swap_out(ids):
+        if sync_free:
+            m.swap_seqs_nosync(H.to_dev(np.asarray(ids, dtype=np.int32)), False)
+        else:
+            m.swap_out_seqs(ids)
+
+    def swap_in(ids):
+        if sync_free:
+            m.swap_seqs_nosync(H.to_dev(np.asarray(ids, dtype=np.int32)), True)
+        else:
+            m.swap_in_seqs(ids)
+
     if with_chunks:     # three resident sequences fill most of the original pool: the rest spills into the chunks
         both_allocate([9, 10, 11], [192, 192, 192])
     both_allocate([0, 1, 2, 3, 4, 5], [100, 30, 64, 60, 17, 90] if with_chunks else [100, 30, 64, 120, 17, 90])
     if with_chunks:
         assert int(m.gpu_block_manager.block_table[:6].max()) >= nb, "the case must reach the elastic chunks"
     check_all()
-    m.swap_out_seqs([1, 3, 4])
+    swap_out([1, 3, 4])
     oracle_swap([1, 3, 4], False)
     check_all()
     both_allocate([6, 7], [70, 33])                       # takes some of the freed blocks
-    m.swap_out_seqs([0])
+    swap_out([0])
     oracle_swap([0], False)
-    m.swap_in_seqs([3, 1])
+    swap_in([3, 1])
     oracle_swap([3, 1], True)
     check_all()
     m.free_seqs_resources([2, 4])
     g_or.free_blocks_for_seqs(np.array([2, 4], dtype=np.int32))
     c_or.free_blocks_for_seqs(np.array([2, 4], dtype=np.int32))
-    m.swap_in_seqs([0])
+    swap_in([0])
     oracle_swap([0], True)
     check_all()
-    assert m.block_swap == (28 if with_chunks else 36)
+    assert (int(m.block_swap_device) if sync_free else m.block_swap) == (28 if with_chunks else 36)
+    if sync_free:
+        # a swap-in the GPU pool cannot hold: nothing is copied, the sequence's swap blocks are released like the
+        # reference releases them before its allocation fails, and the failure is raised at the next look
+        gbm = m.gpu_block_manager
+
+        def fill_gpu_pool(rows):
+            for sid in rows:                          # a row holds 12 blocks: spread what is free over spare rows
+                take = min(cols - int(gbm.num_seq_allocated_blocks[sid]), int(gbm.num_free_blocks))
+                if take > 0:
+                    have = int(gbm.num_seq_allocated_blocks[sid])
+                    gbm.allocate_blocks_for_seqs(H.to_dev(np.array([sid], dtype=np.int32)),
+                                                 H.to_dev(np.array([16 * (have + take)], dtype=np.int32)))
+            assert int(gbm.num_free_blocks) == 0
+
+        fill_gpu_pool([8, 2, 4])
+        swap_out([1])
+        before = [t.clone() for t in [m.k_cache] + m.k_cache_new + [m.v_cache] + m.v_cache_new]
+        fill_gpu_pool([8, 2, 4, 7])                   # takes the two blocks the swap-out freed
+        swap_in([1])
+        torch.cuda.synchronize()
+        for t, b in zip([m.k_cache] + m.k_cache_new + [m.v_cache] + m.v_cache_new, before):
+            assert t.view(torch.int16).equal(b.view(torch.int16))
+        with pytest.raises(RuntimeError, match="No enough free blocks"):
+            int(m.gpu_block_manager.num_free_blocks)
 
 
 @pytest.mark.parametrize("sync_free", [False, True])
