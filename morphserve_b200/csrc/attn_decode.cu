@@ -34,6 +34,7 @@
 // own bulk copy (mbarrier), which gives up after about a second and reports it.
 #include <algorithm>
 #include <atomic>
+#include <type_traits>
 #include <mutex>
 
 #include <cuda.h>  // CUtensorMap and its enums (types only: the encoder is fetched from the driver at run time)
@@ -637,77 +638,89 @@ struct RowMap {
 // Merge of `n` partial rows (pieces s0, s0 + step, ...) of one (sequence, kv head): for each of the G query
 // heads, o = sum_s 2^(lse_s - m) o_s / sum_s 2^(lse_s - m).  FINAL: the result is the attention output (fp16,
 // every destination matrix).  Otherwise it replaces the partial row of piece s0 (normalised, with its own lse),
-// one level of a two-level merge.  Loads are issued in batches (2 heads x 8 rows) before any of them is used, so a
-// merge costs a couple of L2 round trips instead of one per load.
-template <bool FINAL>
-__device__ __forceinline__ void merge_rows(const AttnParams &p, int b, int hq0, int G, const RowMap &map, int s0,
-                                           int step, int n, int lane) {
-    constexpr int SB = 8;
-    for (int r = 0; r < G; r += 2) {
-        const bool two = (r + 1) < G;
-        const int ra = r, rb = two ? r + 1 : r;
-        float ma = -INFINITY, mb = -INFINITY, wa = 0.f, wb = 0.f;
-        float4 acca = make_float4(0.f, 0.f, 0.f, 0.f), accb = make_float4(0.f, 0.f, 0.f, 0.f);
+// one level of a two-level merge.  Loads are issued in batches (4 heads x 4 rows) before any of them is used: the
+// usual merge - two to four rows of a group of four query heads - is one L2 round trip.
+template <bool FINAL, int SB /* rows per batch of loads */>
+__device__ __forceinline__ void merge_rows_batched(const AttnParams &p, int b, int hq0, int G, const RowMap &map,
+                                                   int s0, int step, int n, int lane) {
+    constexpr int HP = 4;  // query heads per pass
+    for (int r = 0; r < G; r += HP) {
+        int rr[HP];
+#pragma unroll
+        for (int h = 0; h < HP; ++h) rr[h] = min(r + h, G - 1);  // a short last pass repeats its last head
+        float m[HP], w[HP];
+        float4 acc[HP];
+#pragma unroll
+        for (int h = 0; h < HP; ++h) {
+            m[h] = -INFINITY;
+            w[h] = 0.f;
+            acc[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
         for (int i0 = 0; i0 < n; i0 += SB) {
-            float la[SB], lb[SB];
-            float4 va[SB], vb[SB];
+            float l[HP][SB];
+            float4 v[HP][SB];
 #pragma unroll
             for (int i = 0; i < SB; ++i) {
                 const bool ok = (i0 + i) < n;
                 const int sp = s0 + (ok ? i0 + i : i0) * step;
-                const int64_t ea = map.elem_row(sp, ra), eb = map.elem_row(sp, rb);
-                la[i] = __ldcg(p.lse + ea);
-                lb[i] = __ldcg(p.lse + eb);
-                va[i] = __ldcg(reinterpret_cast<const float4 *>(p.part_o + ea * kD + lane * 4));
-                vb[i] = __ldcg(reinterpret_cast<const float4 *>(p.part_o + eb * kD + lane * 4));
-                if (!ok) {
-                    la[i] = -INFINITY;
-                    lb[i] = -INFINITY;
+#pragma unroll
+                for (int h = 0; h < HP; ++h) {
+                    const int64_t e = map.elem_row(sp, rr[h]);
+                    l[h][i] = __ldcg(p.lse + e);
+                    v[h][i] = __ldcg(reinterpret_cast<const float4 *>(p.part_o + e * kD + lane * 4));
+                    if (!ok) l[h][i] = -INFINITY;
                 }
             }
-            float na = ma, nb = mb;
 #pragma unroll
-            for (int i = 0; i < SB; ++i) {
-                na = fmaxf(na, la[i]);
-                nb = fmaxf(nb, lb[i]);
-            }
-            const float sa = exp2f(ma - na), sb = exp2f(mb - nb);  // 0 on the first batch (m = -inf)
-            acca.x *= sa; acca.y *= sa; acca.z *= sa; acca.w *= sa; wa *= sa;
-            accb.x *= sb; accb.y *= sb; accb.z *= sb; accb.w *= sb; wb *= sb;
+            for (int h = 0; h < HP; ++h) {
+                float nm = m[h];
 #pragma unroll
-            for (int i = 0; i < SB; ++i) {
-                const float ea = exp2f(la[i] - na), eb = exp2f(lb[i] - nb);  // 0 for the padding entries
-                acca.x += ea * va[i].x; acca.y += ea * va[i].y; acca.z += ea * va[i].z; acca.w += ea * va[i].w;
-                accb.x += eb * vb[i].x; accb.y += eb * vb[i].y; accb.z += eb * vb[i].z; accb.w += eb * vb[i].w;
-                wa += ea;
-                wb += eb;
+                for (int i = 0; i < SB; ++i) nm = fmaxf(nm, l[h][i]);
+                const float sc = exp2f(m[h] - nm);  // 0 on the first batch (m = -inf)
+                acc[h].x *= sc; acc[h].y *= sc; acc[h].z *= sc; acc[h].w *= sc;
+                w[h] *= sc;
+#pragma unroll
+                for (int i = 0; i < SB; ++i) {
+                    const float e = exp2f(l[h][i] - nm);  // 0 for the padding entries
+                    acc[h].x += e * v[h][i].x; acc[h].y += e * v[h][i].y;
+                    acc[h].z += e * v[h][i].z; acc[h].w += e * v[h][i].w;
+                    w[h] += e;
+                }
+                m[h] = nm;
             }
-            ma = na;
-            mb = nb;
         }
 #pragma unroll
-        for (int side = 0; side < 2; ++side) {
-            if (side == 1 && !two) break;
-            const float4 acc = side ? accb : acca;
-            const float w = side ? wb : wa, m = side ? mb : ma;
-            const int rr = side ? rb : ra;
-            const float inv = 1.f / w;
+        for (int h = 0; h < HP; ++h) {
+            if (r + h >= G) break;
+            const float inv = 1.f / w[h];
             if (FINAL) {
-                __half2 h01 = __floats2half2_rn(acc.x * inv, acc.y * inv);
-                __half2 h23 = __floats2half2_rn(acc.z * inv, acc.w * inv);
+                __half2 h01 = __floats2half2_rn(acc[h].x * inv, acc[h].y * inv);
+                __half2 h23 = __floats2half2_rn(acc[h].z * inv, acc[h].w * inv);
                 uint2 pk;
                 pk.x = *reinterpret_cast<uint32_t *>(&h01);
                 pk.y = *reinterpret_cast<uint32_t *>(&h23);
-                const int64_t at = (int64_t)b * p.out_row_stride + p.out_col_off + (int64_t)(hq0 + rr) * kD + lane * 4;
+                const int64_t at =
+                    (int64_t)b * p.out_row_stride + p.out_col_off + (int64_t)(hq0 + rr[h]) * kD + lane * 4;
                 for (int o = 0; o < p.n_out; ++o) *reinterpret_cast<uint2 *>(p.out[o] + at) = pk;
             } else {
-                const int64_t e = map.elem_row(s0, rr);
+                const int64_t e = map.elem_row(s0, rr[h]);
                 __stcg(reinterpret_cast<float4 *>(p.part_o + e * kD + lane * 4),
-                       make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv));
-                if (lane == 0) __stcg(p.lse + e, log2f(w) + m);
+                       make_float4(acc[h].x * inv, acc[h].y * inv, acc[h].z * inv, acc[h].w * inv));
+                if (lane == 0) __stcg(p.lse + e, log2f(w[h]) + m[h]);
             }
         }
     }
+}
+
+// The merge runs on ONE warp at the end of a launch, where every instruction is on the critical path: the usual case
+// (a (sequence, head) that spans two thread blocks: two rows) gets a body without padding.
+template <bool FINAL>
+__device__ __forceinline__ void merge_rows(const AttnParams &p, int b, int hq0, int G, const RowMap &map, int s0,
+                                           int step, int n, int lane) {
+    if (n <= 2)
+        merge_rows_batched<FINAL, 2>(p, b, hq0, G, map, s0, step, n, lane);
+    else
+        merge_rows_batched<FINAL, 4>(p, b, hq0, G, map, s0, step, n, lane);
 }
 
 // Pieces per group of a two-level merge: one level up to 8 pieces, otherwise about the square root of the count.
@@ -1284,36 +1297,62 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attn_decode_f16_kernel(const __
                     // rows of the global merge: block c owns rows 2c (a (sequence, head) entering it) and 2c + 1 (one
                     // leaving it), so group gi of a (sequence, head) starting in block cta_f has row 2 (cta_f + gi) + (gi == 0)
                     const RowMap map{2 * (int64_t)cta_f, 2, 1, G, 0};
-                    for (int r = 0; r < G; ++r) {
-                        float m = -INFINITY;
-                        for (int x = wlo; x <= whi; ++x)
-                            m = fmaxf(m, parked_piece<WARPS, STAGES, TMA>(smem, x, cta0 + x == f)[8 * kD + r]);
-                        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                        float wsum = 0.f;
-                        for (int x = wlo; x <= whi; ++x) {
-                            const float *pp = parked_piece<WARPS, STAGES, TMA>(smem, x, cta0 + x == f);
-                            const float e = exp2f(pp[8 * kD + r] - m);
-                            const float4 v = *reinterpret_cast<const float4 *>(pp + r * kD + lane * 4);
-                            acc.x += e * v.x; acc.y += e * v.y; acc.z += e * v.z; acc.w += e * v.w;
-                            wsum += e;
+                    // Every piece's row is requested before any is used.  NP bounds the pieces (2, 4 or all the block's
+                    // warps): this runs on one warp at the end of the launch, so padding is time on the critical path.
+                    auto fold = [&](auto np_tag) {
+                        constexpr int NP = decltype(np_tag)::value;
+                        const float *pp[NP];
+#pragma unroll
+                        for (int k = 0; k < NP; ++k) {
+                            const int xc = min(wlo + k, whi);  // entries behind whi re-read a real piece, weight 0
+                            pp[k] = parked_piece<WARPS, STAGES, TMA>(smem, xc, cta0 + xc == f);
                         }
-                        const float inv = 1.f / wsum;
-                        if (ng == 1) {  // the whole (sequence, head) lies in this block: this is the output
-                            __half2 h01 = __floats2half2_rn(acc.x * inv, acc.y * inv);
-                            __half2 h23 = __floats2half2_rn(acc.z * inv, acc.w * inv);
-                            uint2 pk;
-                            pk.x = *reinterpret_cast<uint32_t *>(&h01);
-                            pk.y = *reinterpret_cast<uint32_t *>(&h23);
-                            const int64_t at =
-                                (int64_t)cur.b * p.out_row_stride + p.out_col_off + (int64_t)(hq0 + r) * kD + lane * 4;
-                            for (int o = 0; o < p.n_out; ++o) *reinterpret_cast<uint2 *>(p.out[o] + at) = pk;
-                        } else {
-                            const int64_t e = map.elem_row(gi, r);
-                            __stcg(reinterpret_cast<float4 *>(p.part_o + e * kD + lane * 4),
-                                   make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv));
-                            if (lane == 0) __stcg(p.lse + e, log2f(wsum) + m);
+                        for (int r = 0; r < G; ++r) {
+                            float ls[NP];
+                            float4 vs[NP];
+#pragma unroll
+                            for (int k = 0; k < NP; ++k) {
+                                ls[k] = pp[k][8 * kD + r];
+                                vs[k] = *reinterpret_cast<const float4 *>(pp[k] + r * kD + lane * 4);
+                            }
+                            float m = -INFINITY;
+#pragma unroll
+                            for (int k = 0; k < NP; ++k) {
+                                if (wlo + k > whi) ls[k] = -INFINITY;  // not a piece of this (sequence, head)
+                                m = fmaxf(m, ls[k]);
+                            }
+                            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                            float wsum = 0.f;
+#pragma unroll
+                            for (int k = 0; k < NP; ++k) {
+                                const float e = exp2f(ls[k] - m);  // 0 for the entries that are not pieces
+                                acc.x += e * vs[k].x; acc.y += e * vs[k].y; acc.z += e * vs[k].z; acc.w += e * vs[k].w;
+                                wsum += e;
+                            }
+                            const float inv = 1.f / wsum;
+                            if (ng == 1) {  // the whole (sequence, head) lies in this block: this is the output
+                                __half2 h01 = __floats2half2_rn(acc.x * inv, acc.y * inv);
+                                __half2 h23 = __floats2half2_rn(acc.z * inv, acc.w * inv);
+                                uint2 pk;
+                                pk.x = *reinterpret_cast<uint32_t *>(&h01);
+                                pk.y = *reinterpret_cast<uint32_t *>(&h23);
+                                const int64_t at = (int64_t)cur.b * p.out_row_stride + p.out_col_off +
+                                                   (int64_t)(hq0 + r) * kD + lane * 4;
+                                for (int o = 0; o < p.n_out; ++o) *reinterpret_cast<uint2 *>(p.out[o] + at) = pk;
+                            } else {
+                                const int64_t e = map.elem_row(gi, r);
+                                __stcg(reinterpret_cast<float4 *>(p.part_o + e * kD + lane * 4),
+                                       make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv));
+                                if (lane == 0) __stcg(p.lse + e, log2f(wsum) + m);
+                            }
                         }
-                    }
+                    };
+                    if (gsz <= 2)
+                        fold(std::integral_constant<int, 2>{});
+                    else if (gsz <= 4)
+                        fold(std::integral_constant<int, 4>{});
+                    else
+                        fold(std::integral_constant<int, WARPS>{});
                     if (ng > 1) {
                         __threadfence();
                         __syncwarp();
