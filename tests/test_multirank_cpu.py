@@ -85,3 +85,17 @@ def test_head_sharding_needs_divisible_heads():
     import bench
     with pytest.raises(ValueError):
         bench.shard_workload(bench.WORKLOADS["codellama-34b-gqa-decode-headshard"], 0, 3)
+
+
+def test_head_shard_column_fails_soft_without_gpus():
+    """The head-sharded side column of `bench.py --gpus N` runs as jobs of its own under a time limit.  Here, without a
+    GPU, each job ends with an error: the column must come back as a record of "unavailable" entries, never raise, and
+    refuse a rank count that does not divide the 8 KV heads without starting anything."""
+    import bench
+    assert "unavailable" in bench.headshard_column(3, K=1, W=1)
+    if torch.cuda.is_available():
+        return                                    # with GPUs present the jobs would really run: covered on the GPU box
+    out = bench.headshard_column(2, K=1, W=1, layers=1, timeout_s=240)
+    assert out["layers_run"] == 1 and out["layers_of_model"] == 48
+    for name in ("codellama-34b-gqa-decode-headshard", "codellama-34b-gqa-decode-headshard-push"):
+        assert "unavailable" in out[name] and "value" not in out[name], out[name]
