@@ -723,9 +723,11 @@ __device__ __forceinline__ void merge_rows(const AttnParams &p, int b, int hq0, 
         merge_rows_batched<FINAL, 4>(p, b, hq0, G, map, s0, step, n, lane);
 }
 
-// Pieces per group of a two-level merge: one level up to 8 pieces, otherwise about the square root of the count.
+// Pieces per group of a two-level merge: one level up to 16 pieces (four batches of row loads cost less than a second
+// level's counter, fence and extra pass: measured on a sequence whose heads span 9-10 thread blocks), otherwise about
+// the square root of the count.
 __device__ __forceinline__ int merge_fan_in(int nsplit) {
-    if (nsplit <= 8) return nsplit;
+    if (nsplit <= 16) return nsplit;
     int f = 8;
     while (f * f < nsplit) ++f;
     return f;
